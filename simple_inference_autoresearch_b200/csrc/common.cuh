@@ -1,0 +1,76 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Conventions used by every unit in this folder:
+//  * Entry points are `extern "C" int siar_<name>(..., void* stream)`; they launch
+//    on the given stream and return the cudaError_t of the launch as an int.
+//  * A batch of sequences is described by three int32 device arrays:
+//      slot_ids[B]   cache slot of each sequence,
+//      q_start[B+1]  first packed row of each sequence's new tokens,
+//      base_len[B]   tokens the sequence already holds in the cache.
+//    Row t of sequence b sits at absolute position base_len[b] + (t - q_start[b]).
+//  * Keys and values live in pages of `page_tokens` positions:
+//      pool[page][kv_head][page_tokens][head_dim],
+//    and block_table[slot * max_pages + p] names the page of positions
+//    [p * page_tokens, (p + 1) * page_tokens) of that slot.
+//  * Reductions run in an order that depends only on the row itself (its width,
+//    its absolute key positions), never on what else is in the batch.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace siar {
+
+enum StatusBits : int {
+  kStatusTokenOutOfRange = 1,
+  kStatusWaitExpired = 2,
+  kStatusBadPage = 4,
+};
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+// Largest b in [0, B) with q_start[b] <= t (q_start is non-decreasing, q_start[0] == 0).
+__device__ __forceinline__ int find_sequence(const int* __restrict__ q_start, int B, int t) {
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (q_start[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum in a fixed order: lane tree inside each warp, then warp 0 adds
+// the per-warp sums in warp order.  `scratch` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarps; ++w) total += scratch[w];
+  return total;
+}
+
+}  // namespace siar

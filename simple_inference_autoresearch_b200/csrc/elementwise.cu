@@ -1,0 +1,224 @@
+// Memory-bound kernels of the decoder: embedding gather, fused residual-add +
+// RMSNorm, rotary position encoding fused with the cache write, SwiGLU, row
+// gather, and the per-step length bookkeeping.  All arithmetic is 32-bit; only
+// loads and stores touch the storage dtype.
+//
+// Formulas (reference files are cited by their path inside the reference project):
+//  * embedding           x[t] = W[ids[t]]                        ops/embedding.py:62-65
+//  * add + RMSNorm       r = r + delta (fp32); y = r * rsqrt(mean(r^2) + eps) * w
+//                                                                kernels/add_rmsnorm_kernel.py:86-103
+//  * rotary (split-half) out_i = x_i cos - x_{i+D/2} sin; out_{i+D/2} = x_{i+D/2} cos + x_i sin
+//                                                                kernels/rope_kernel.py:143-152
+//    with angle = position * inv_freq[i] formed in fp32           ops/rope.py:108-118
+//  * cache write         K[slot, pos] = rotated k, V[slot, pos] = v   model/kv_cache.py:178-179
+//  * SwiGLU              f = gate * sigmoid(gate) * up             kernels/swiglu_kernel.py:139-140
+#include "common.cuh"
+
+namespace siar {
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                    float* __restrict__ out, int H, int V, int* __restrict__ status) {
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) atomicOr(status, kStatusTokenOutOfRange);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)t * H + j] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)t * H + j] = to_f32(row[j]);
+}
+
+// ------------------------------------------------------------------ row gather
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,
+                                   float* __restrict__ dst, int H) {
+  const int r = blockIdx.x;
+  const float* s = src + (size_t)rows[r] * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) dst[(size_t)r * H + j] = s[j];
+}
+
+// ------------------------------------------------------------------ add + RMSNorm
+// One block per row.  Pass 1 forms r = residual + delta in fp32, stores it and
+// accumulates the sum of squares; pass 2 re-reads the stored row (same thread,
+// same addresses) and writes the normed output.
+template <typename TOut, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+                                   const TW* __restrict__ weight, TOut* __restrict__ out, int H, float eps) {
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  if (delta != nullptr) {
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+      float r = residual[base + j] + delta[base + j];
+      residual[base + j] = r;
+      ss += r * r;
+    }
+  } else {
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+      float r = residual[base + j];
+      ss += r * r;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)H + eps);
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float r = residual[base + j];
+    out[base + j] = from_f32<TOut>(r * inv * to_f32(weight[j]));
+  }
+}
+
+// ------------------------------------------------------------------ rotary + cache write
+// grid (N, Hq + 2*Hkv); one block per (token, head of the fused qkv row).
+// q heads are rotated in place, k heads are rotated into the cache, v heads are
+// copied into the cache.  inv_freq == nullptr means "no rotation".
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ inv_freq,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                     const int* __restrict__ block_table, const int* __restrict__ slot_ids,
+                                     const int* __restrict__ q_start, const int* __restrict__ base_len,
+                                     int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
+                                     int n_pages, int write_kv, int* __restrict__ status) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;
+  const int b = find_sequence(q_start, B, t);
+  const int pos = base_len[b] + (t - q_start[b]);
+  const int half = D >> 1;
+  T* row = qkv + (size_t)t * (Hq + 2 * Hkv) * D + (size_t)head * D;
+
+  T* dst = nullptr;
+  if (head >= Hq) {
+    if (!write_kv) return;
+    const int slot = slot_ids[b];
+    const int page = block_table[(size_t)slot * max_pages + pos / page_tokens];
+    if (page < 0 || page >= n_pages) {
+      if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+      return;
+    }
+    const int kvh = (head - Hq) % Hkv;
+    T* pool = (head < Hq + Hkv) ? k_pool : v_pool;
+    dst = pool + (((size_t)page * Hkv + kvh) * page_tokens + (pos % page_tokens)) * D;
+  }
+
+  if (head < Hq + Hkv) {  // q or k: rotate
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float a = to_f32(row[i]), c = to_f32(row[i + half]);
+      float oa = a, oc = c;
+      if (inv_freq != nullptr) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        oa = a * cs - c * sn;
+        oc = c * cs + a * sn;
+      }
+      if (dst != nullptr) {
+        dst[i] = from_f32<T>(oa);
+        dst[i + half] = from_f32<T>(oc);
+      } else {
+        row[i] = from_f32<T>(oa);
+        row[i + half] = from_f32<T>(oc);
+      }
+    }
+  } else {  // v: copy
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = row[i];
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  const size_t row = blockIdx.x;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= I) return;
+  const float g = to_f32(gu[row * 2 * I + j]);
+  const float u = to_f32(gu[row * 2 * I + I + j]);
+  const float s = g / (1.f + expf(-g));
+  out[row * I + j] = from_f32<T>(s * u);
+}
+
+// ------------------------------------------------------------------ bookkeeping
+// base_len[b] += q_start[b+1] - q_start[b]; used by the captured decode step so
+// that a replay sees the lengths the previous replay left.
+__global__ void advance_lengths_kernel(int* __restrict__ base_len, const int* __restrict__ q_start, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) base_len[b] += q_start[b + 1] - q_start[b];
+}
+
+}  // namespace siar
+
+using namespace siar;
+
+#define LAUNCH_END() return (int)cudaGetLastError()
+
+extern "C" int siar_embed_gather(int is_bf16, const int* tokens, const void* table, float* out, int N, int H,
+                                 int V, int* status, void* stream) {
+  if (N == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (is_bf16)
+    embed_gather_kernel<__nv_bfloat16><<<N, 256, 0, s>>>(tokens, (const __nv_bfloat16*)table, out, H, V, status);
+  else
+    embed_gather_kernel<float><<<N, 256, 0, s>>>(tokens, (const float*)table, out, H, V, status);
+  LAUNCH_END();
+}
+
+extern "C" int siar_gather_rows(const float* src, const int* rows, float* dst, int R, int H, void* stream) {
+  if (R == 0) return 0;
+  gather_rows_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(src, rows, dst, H);
+  LAUNCH_END();
+}
+
+extern "C" int siar_add_rmsnorm(int out_bf16, int weight_bf16, float* residual, const float* delta,
+                                const void* weight, void* out, int N, int H, float eps, void* stream) {
+  if (N == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = H >= 2048 ? 512 : 256;
+  if (out_bf16 && weight_bf16)
+    add_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16><<<N, threads, 0, s>>>(
+        residual, delta, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, H, eps);
+  else if (out_bf16)
+    add_rmsnorm_kernel<__nv_bfloat16, float><<<N, threads, 0, s>>>(residual, delta, (const float*)weight,
+                                                                  (__nv_bfloat16*)out, H, eps);
+  else if (weight_bf16)
+    add_rmsnorm_kernel<float, __nv_bfloat16><<<N, threads, 0, s>>>(residual, delta, (const __nv_bfloat16*)weight,
+                                                                  (float*)out, H, eps);
+  else
+    add_rmsnorm_kernel<float, float><<<N, threads, 0, s>>>(residual, delta, (const float*)weight, (float*)out, H,
+                                                          eps);
+  LAUNCH_END();
+}
+
+extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq, void* k_pool, void* v_pool,
+                                  const int* block_table, const int* slot_ids, const int* q_start,
+                                  const int* base_len, int N, int B, int Hq, int Hkv, int D, int page_tokens,
+                                  int max_pages, int n_pages, int write_kv, int* status, void* stream) {
+  if (N == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(N, Hq + 2 * Hkv);
+  const int threads = D >= 128 ? 64 : 32;
+  if (is_bf16)
+    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(
+        (__nv_bfloat16*)qkv, inv_freq, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids,
+        q_start, base_len, B, Hq, Hkv, D, page_tokens, max_pages, n_pages, write_kv, status);
+  else
+    rope_kv_write_kernel<float><<<grid, threads, 0, s>>>((float*)qkv, inv_freq, (float*)k_pool, (float*)v_pool,
+                                                        block_table, slot_ids, q_start, base_len, B, Hq, Hkv, D,
+                                                        page_tokens, max_pages, n_pages, write_kv, status);
+  LAUNCH_END();
+}
+
+extern "C" int siar_swiglu(int is_bf16, const void* gu, void* out, int N, int I, void* stream) {
+  if (N == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(N, (I + 255) / 256);
+  if (is_bf16)
+    swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+  else
+    swiglu_kernel<float><<<grid, 256, 0, s>>>((const float*)gu, (float*)out, I);
+  LAUNCH_END();
+}
+
+extern "C" int siar_advance_lengths(int* base_len, const int* q_start, int B, void* stream) {
+  if (B == 0) return 0;
+  advance_lengths_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(base_len, q_start, B);
+  LAUNCH_END();
+}

@@ -1,0 +1,263 @@
+"""The engine: a model, its cache, the step function and token sampling on one GPU.
+
+``step`` is the one function everything else is built on: it takes a batch of
+sequences with unequal numbers of new tokens (whole prompts, or one token each,
+or any mix), runs exactly those tokens as one packed batch against the cache and
+returns float32 logits at the wanted places.  The reference's counterpart is
+``LlamaModel.forward(token_ids (B, T), start_pos)`` (model/llama.py:137-199),
+which needs a rectangular batch at one shared position and returns the last
+position only.
+
+``run`` adds the draw of the next token for the generation loop; for steps of
+one token per sequence it replays a captured CUDA graph that holds the whole
+step, the sampling and the length bookkeeping (the reference captures its decode
+forward the same way, model/cuda_graph_decode.py:118-143, with one position for
+the whole batch and sampling outside the graph).
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.sequence_cache import SequenceCache, round_up
+from ..kernels import ops
+from ..sampling.params import SamplingParams, request_seed
+from . import generation
+from .batch import BatchMeta, StepEntry
+from .model import DecoderModel
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, max_batch: int = 8, max_seq_len: Optional[int] = None,
+                 max_tokens: Optional[int] = None, max_slots: Optional[int] = None, page_tokens: int = 64,
+                 use_cuda_graph: bool = True):
+        self.model = model
+        self.device = model.device
+        self._cuda = self.device.type == "cuda"   # kernels refuse anything else at their first launch
+        max_seq_len = int(max_seq_len or model.spec.max_position)
+        if max_seq_len > model.spec.max_position:
+            raise ValueError(f"max_seq_len {max_seq_len} exceeds the model's max_position_embeddings "
+                             f"{model.spec.max_position}")
+        self.max_batch = int(max_batch)
+        if max_tokens is None:
+            max_tokens = self.max_batch * round_up(max_seq_len, page_tokens)
+        self.cache = SequenceCache(model.cache_needs, int(max_tokens), int(max_slots or self.max_batch),
+                                   max_seq_len, model.dtype, self.device, page_tokens)
+        self.max_seq_len = self.cache.max_seq_len
+        self.use_cuda_graph = bool(use_cuda_graph)
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self._graph_state: Optional[_GraphBuffers] = None
+
+    # ------------------------------------------------------------------ slots
+    def open(self) -> int:
+        return self.cache.alloc()
+
+    def close(self, slot: int) -> None:
+        self.cache.free(slot)
+        if self._graph_state is not None:
+            self._graph_state.invalidate()
+
+    def fits(self, token_counts: Sequence[int]) -> bool:
+        c = self.cache
+        free_pages = min(len(g.pages) for g in c.groups if hasattr(g, "pages")) if any(
+            hasattr(g, "pages") for g in c.groups) else c.n_pages
+        pages = sum(-(-n // c.page_tokens) for n in token_counts)
+        return len(token_counts) <= len(c.slots) and pages <= free_pages
+
+    # ------------------------------------------------------------------ the step function
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries' tokens as one batch from the cache; returns float32
+        logits ``[sum(len(e.want)), vocab]`` in the order of the entries and of
+        each entry's ``want``."""
+        slots = [e.slot for e in entries]
+        q_lens = [len(e.tokens) for e in entries]
+        self.cache.reserve(slots, q_lens)
+        base = [self.cache.length(s) for s in slots]
+        meta = BatchMeta.build(entries, base, self.device)
+        logits = self.model.forward(meta, self.cache)
+        self.cache.commit(slots, q_lens)
+        if self._graph_state is not None:
+            self._graph_state.invalidate()
+        return logits
+
+    # ------------------------------------------------------------------ sampling
+    def _sampling_arrays(self, requests: Sequence[generation.Request]):
+        n = len(requests)
+        f = np.empty(2 * n, dtype=np.float32)
+        i = np.empty(2 * n, dtype=np.int32)
+        s = np.empty(n, dtype=np.int64)
+        for j, r in enumerate(requests):
+            f[j], f[n + j] = r.params.temperature, r.params.top_p
+            i[j], i[n + j] = r.params.top_k, len(r.output)
+            s[j] = request_seed(r.params.seed, r.index)
+        return f, i, s
+
+    def _upload(self, array: np.ndarray) -> torch.Tensor:
+        t = torch.from_numpy(array)
+        return t.pin_memory().to(self.device, non_blocking=True) if self._cuda else t
+
+    def sample(self, logits: torch.Tensor, requests: Sequence[generation.Request]) -> torch.Tensor:
+        n = len(requests)
+        f, i, s = self._sampling_arrays(requests)
+        fd, idev, sd = self._upload(f), self._upload(i), self._upload(s)
+        return ops.sample(logits, fd[:n], idev[:n], fd[n:], sd, idev[n:], advance_index=False)
+
+    # ------------------------------------------------------------------ backend of the generation loop
+    def run(self, requests: Sequence[generation.Request], new_tokens: Sequence[Sequence[int]]) -> List[int]:
+        decode = all(len(t) == 1 for t in new_tokens)
+        if decode and self.use_cuda_graph and self._cuda:
+            return self._run_graph(requests, new_tokens)
+        entries = [StepEntry(r.slot, t, [len(t) - 1]) for r, t in zip(requests, new_tokens)]
+        logits = self.step(entries)
+        toks = self.sample(logits, requests)
+        out = toks.cpu().tolist()
+        ops.check_status(self.device)
+        return out
+
+    def _run_graph(self, requests, new_tokens) -> List[int]:
+        slots = [r.slot for r in requests]
+        b = len(slots)
+        self.cache.reserve(slots, [1] * b)
+        if self._graph_state is None:
+            self._graph_state = _GraphBuffers(self, max(self.max_batch, b))
+        st = self._graph_state
+        if st.capacity < b:
+            self._graph_state = st = _GraphBuffers(self, b)
+        longest = max(self.cache.length(s) for s in slots) + 1
+        bucket = 1024
+        while bucket < longest:
+            bucket *= 2
+        bucket = min(bucket, self.max_seq_len)
+        if st.slots != slots or st.bucket != bucket:
+            st.upload(requests, [t[0] for t in new_tokens], bucket)
+        key = (b, bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph(self, st, b, bucket)
+        g.replay()
+        st.host_tokens[:b].copy_(st.tokens[:b], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.cache.commit(slots, [1] * b)
+        out = st.host_tokens[:b].tolist()
+        ops.check_status(self.device)
+        return out
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts: Sequence[Sequence[int]], params=SamplingParams(), max_new_tokens=128,
+                 stop_token_ids: Optional[Iterable[int]] = None, ignore_eos: bool = False,
+                 on_token: Optional[Callable[[int, int], None]] = None, return_stats: bool = False):
+        """Generates for every prompt (lists of token ids); returns the new tokens
+        of each, and with ``return_stats`` also a dict with the keys of the
+        reference's stats (generate.py:227-237)."""
+        stop = set() if ignore_eos else set(self.model.spec.stop_token_ids)
+        if stop_token_ids is not None:
+            stop |= {int(t) for t in stop_token_ids}
+        timings: dict = {}
+        if self._cuda:
+            torch.cuda.reset_peak_memory_stats(self.device)
+        t0 = time.perf_counter()
+        reqs = generation.generate(self, prompts, params, max_new_tokens, stop, on_token, timings)
+        if self._cuda:
+            torch.cuda.synchronize(self.device)
+        wall = time.perf_counter() - t0
+        outs = [r.output for r in reqs]
+        if not return_stats:
+            return outs
+        prefill = timings.get("prefill_s", [])
+        decode = timings.get("decode_s", [])
+        new = sum(len(o) for o in outs)
+        tpot = (sum(decode) / len(decode)) if decode else 0.0
+        stats = {
+            "prompt_tokens": sum(len(p) for p in prompts),
+            "new_tokens": new,
+            "ttft_ms": round(1e3 * prefill[0], 2) if prefill else 0.0,
+            "tpot_ms": round(1e3 * tpot, 3),
+            "prefill_ms": round(1e3 * sum(prefill), 2),
+            "decode_tok_s": round(sum(timings.get("decode_seqs", [])) / sum(decode), 1) if decode and sum(decode) > 0 else 0.0,
+            "total_wall_ms": round(1e3 * wall, 2),
+            "total_tok_s": round((sum(len(p) for p in prompts) + new) / wall, 1) if wall > 0 else 0.0,
+            "peak_vram_gb": round(torch.cuda.max_memory_allocated(self.device) / 1e9, 2) if self._cuda else 0.0,
+            "finish_reasons": [r.finish_reason for r in reqs],
+        }
+        return outs, stats
+
+
+class _GraphBuffers:
+    """Static device buffers the captured decode step reads and writes."""
+
+    def __init__(self, engine: Engine, capacity: int):
+        dev = engine.device
+        self.capacity = capacity
+        z = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)  # noqa: E731
+        self.tokens = z(capacity, torch.int32)
+        self.slot_ids = z(capacity, torch.int32)
+        self.q_start = torch.arange(capacity + 1, dtype=torch.int32, device=dev)
+        self.base_len = z(capacity, torch.int32)
+        self.want_rows = torch.arange(capacity, dtype=torch.int32, device=dev)
+        self.temperature = z(capacity, torch.float32)
+        self.top_p = z(capacity, torch.float32)
+        self.top_k = z(capacity, torch.int32)
+        self.draw_index = z(capacity, torch.int32)
+        self.seeds = z(capacity, torch.int64)
+        self.host_tokens = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.engine = engine
+        self.slots: Optional[List[int]] = None
+        self.bucket = 0
+
+    def invalidate(self) -> None:
+        self.slots = None
+
+    def upload(self, requests, tokens: Sequence[int], bucket: int) -> None:
+        eng = self.engine
+        b = len(requests)
+        f, i, s = eng._sampling_arrays(requests)
+        ints = np.concatenate([np.asarray(tokens, dtype=np.int32),
+                               np.asarray([r.slot for r in requests], dtype=np.int32),
+                               np.asarray([eng.cache.length(r.slot) for r in requests], dtype=np.int32), i])
+        ints_d, f_d, s_d = eng._upload(ints), eng._upload(f), eng._upload(s)
+        self.tokens[:b].copy_(ints_d[0:b])
+        self.slot_ids[:b].copy_(ints_d[b:2 * b])
+        self.base_len[:b].copy_(ints_d[2 * b:3 * b])
+        self.top_k[:b].copy_(ints_d[3 * b:4 * b])
+        self.draw_index[:b].copy_(ints_d[4 * b:5 * b])
+        self.temperature[:b].copy_(f_d[:b])
+        self.top_p[:b].copy_(f_d[b:])
+        self.seeds[:b].copy_(s_d)
+        self.slots = [r.slot for r in requests]
+        self.bucket = bucket
+
+
+class _DecodeGraph:
+    """One captured decode step for ``b`` sequences and keys up to ``bucket``."""
+
+    def __init__(self, engine: Engine, st: _GraphBuffers, b: int, bucket: int):
+        self.engine, self.st, self.b = engine, st, b
+        meta = BatchMeta(st.slot_ids[:b], st.q_start[:b + 1], st.base_len[:b], st.tokens[:b], st.want_rows[:b],
+                         n_seqs=b, n_tokens=b, n_want=b, max_q_len=1, max_kv_len=bucket, want_is_identity=True)
+        self.meta = meta
+        # One eager pass loads every kernel before the capture.  It writes the same
+        # keys and values the first replay writes again and advances nothing.
+        self._body(advance=False)
+        torch.cuda.current_stream().synchronize()
+        before = ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body(advance=True)
+        self.kernels = ops.launch_count - before
+        ops.launch_count = before
+
+    def _body(self, advance: bool) -> None:
+        eng, st, b = self.engine, self.st, self.b
+        logits = eng.model.forward(self.meta, eng.cache)
+        ops.sample(logits, st.temperature[:b], st.top_k[:b], st.top_p[:b], st.seeds[:b], st.draw_index[:b],
+                   advance_index=advance, out=st.tokens[:b] if advance else None)
+        if advance:
+            ops.advance_lengths(st.base_len[:b], st.q_start[:b + 1], b)
+
+    def replay(self) -> None:
+        self.graph.replay()
+        ops.launch_count += self.kernels

@@ -1,0 +1,282 @@
+"""Python face of the CUDA kernels: one function per kernel (or fused pair).
+
+Each function checks shapes and dtypes on the host, allocates the output with
+torch (torch is only the allocator here) and launches the kernel on torch's
+current stream through the unit's C entry point.  Nothing here computes with
+torch, and nothing falls back to the CPU: a tensor that is not on a CUDA device,
+or an extension that cannot be built, raises.
+
+The parts call these functions through the module (``ops.linear(...)``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+# ------------------------------------------------------------------ plumbing
+#: kernels launched through this module since import (graph replays add what the graph holds)
+launch_count = 0
+
+_signatures = {
+    "elementwise": {
+        "siar_embed_gather": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+        "siar_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "siar_add_rmsnorm": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+        "siar_rope_kv_write": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p, c_void_p],
+        "siar_swiglu": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "siar_advance_lengths": [c_void_p, c_void_p, c_int, c_void_p],
+    },
+    "gemm_simt": {
+        "siar_gemm_nt_simt": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "attention": {
+        "siar_attn_prefill": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "siar_attn_decode": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                             c_void_p],
+        "siar_attn_decode_chunk": [],
+        "siar_attn_max_head_dim": [],
+    },
+    "sampling": {
+        "siar_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_void_p, c_void_p],
+    },
+}
+_bound = {}
+
+
+def _fn(unit: str, name: str):
+    key = (unit, name)
+    f = _bound.get(key)
+    if f is None:
+        lib = build.load_unit(unit)
+        f = getattr(lib, name)
+        f.argtypes = _signatures[unit][name]
+        f.restype = c_int
+        _bound[key] = f
+    return f
+
+
+def _launch(unit: str, name: str, *args, kernels: int = 1) -> None:
+    global launch_count
+    err = _fn(unit, name)(*args)
+    if err != 0:
+        raise RuntimeError(f"{name} failed to launch: CUDA error {err} (see cudaError_t); "
+                           "sizes the kernel refuses are reported as cudaErrorInvalidValue (1)")
+    launch_count += kernels
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("this library runs on a CUDA device only (no CPU path); got a "
+                               f"{t.device} tensor of shape {tuple(t.shape)}")
+
+
+def _is_bf16(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return 1
+    if dtype == torch.float32:
+        return 0
+    raise TypeError(f"compute dtype must be bfloat16 or float32, got {dtype}")
+
+
+# ------------------------------------------------------------------ status word
+_status = {}
+
+STATUS_MESSAGES = {
+    1: "a token id outside [0, vocab_size) was fed",
+    2: "a bounded device-side wait expired",
+    4: "a cache write met a position without a page",
+}
+
+
+def status_word(device) -> torch.Tensor:
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[key] = t
+    return t
+
+
+def check_status(device) -> None:
+    """Reads the device status word (synchronises) and raises if a kernel flagged an error."""
+    t = status_word(device)
+    v = int(t.item())
+    if v:
+        t.zero_()
+        what = [m for bit, m in STATUS_MESSAGES.items() if v & bit] or [f"status {v}"]
+        raise RuntimeError("a kernel reported: " + "; ".join(what))
+
+
+# ------------------------------------------------------------------ kernels
+def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """float32 [N, H] rows of ``table`` picked by int32 ``tokens``."""
+    _need_cuda(tokens, table)
+    assert tokens.dtype == torch.int32 and tokens.dim() == 1 and table.dim() == 2 and table.is_contiguous()
+    n, (v, h) = tokens.numel(), table.shape
+    out = torch.empty((n, h), dtype=torch.float32, device=table.device)
+    _launch("elementwise", "siar_embed_gather", _is_bf16(table.dtype), _ptr(tokens), _ptr(table), _ptr(out),
+            n, h, v, _ptr(status_word(table.device)), _stream())
+    return out
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _need_cuda(src, rows)
+    assert src.dtype == torch.float32 and src.dim() == 2 and src.is_contiguous() and rows.dtype == torch.int32
+    out = torch.empty((rows.numel(), src.shape[1]), dtype=torch.float32, device=src.device)
+    _launch("elementwise", "siar_gather_rows", _ptr(src), _ptr(rows), _ptr(out), rows.numel(), src.shape[1],
+            _stream())
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """residual += delta (if given), returns rmsnorm(residual) * weight in ``out_dtype``."""
+    _need_cuda(residual, delta, weight)
+    assert residual.dtype == torch.float32 and residual.dim() == 2 and residual.is_contiguous()
+    n, h = residual.shape
+    assert weight.shape == (h,) and weight.is_contiguous()
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.shape == residual.shape and delta.is_contiguous()
+    out = torch.empty((n, h), dtype=out_dtype, device=residual.device)
+    _launch("elementwise", "siar_add_rmsnorm", _is_bf16(out_dtype), _is_bf16(weight.dtype), _ptr(residual),
+            _ptr(delta), _ptr(weight), _ptr(out), n, h, float(eps), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y[M, N] = x[M, K] @ w[N, K]^T with 32-bit accumulation."""
+    _need_cuda(x, w)
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
+    assert x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous()
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if out_dtype not in (torch.float32, x.dtype):
+        raise TypeError(f"linear: output dtype {out_dtype} with input dtype {x.dtype}")
+    if x.dtype == torch.bfloat16:
+        from . import gemm_tc
+        if gemm_tc.try_linear(x, w, out):
+            return out
+    _launch("gemm_simt", "siar_gemm_nt_simt", _is_bf16(x.dtype), int(out_dtype == torch.float32), _ptr(x),
+            _ptr(w), _ptr(out), m, n, k, 1, _stream())
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, meta, n_heads: int, n_kv_heads: int,
+                  head_dim: int, write_kv: bool = True) -> None:
+    """Rotates the q (in place) and k heads of the fused ``qkv`` rows by their
+    positions and writes k and v into the pages of ``kv`` (a cache entry)."""
+    _need_cuda(qkv, inv_freq, kv.k)
+    n = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert qkv.dtype == kv.k.dtype and n == meta.n_tokens
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2
+    assert kv.k.shape[1:] == (n_kv_heads, kv.page_tokens, head_dim)
+    _launch("elementwise", "siar_rope_kv_write", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(inv_freq), _ptr(kv.k),
+            _ptr(kv.v), _ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len), n,
+            meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1],
+            kv.k.shape[0], int(write_kv), _ptr(status_word(qkv.device)), _stream())
+
+
+_attn_consts = {}
+
+
+def attention_limits() -> dict:
+    if not _attn_consts:
+        lib = build.load_unit("attention")
+        _attn_consts["decode_chunk"] = lib.siar_attn_decode_chunk()
+        _attn_consts["max_head_dim"] = lib.siar_attn_max_head_dim()
+    return _attn_consts
+
+
+def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Raises for sizes the attention kernels refuse (never a wrong result)."""
+    if head_dim % 16 or head_dim <= 0 or head_dim > 256:
+        raise ValueError(f"attention kernels take head_dim in steps of 16 up to 256, got {head_dim}")
+    if n_heads % n_kv_heads:
+        raise ValueError(f"num heads {n_heads} is not a multiple of kv heads {n_kv_heads}")
+
+
+def decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int) -> int:
+    chunk = attention_limits()["decode_chunk"]
+    chunks = (max_kv_len + chunk - 1) // chunk
+    return n_seqs * n_heads * chunks * (head_dim + 2)
+
+
+def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
+    """Causal attention of the new tokens' (already rotated) queries over the
+    cache entry ``kv``; returns [N, n_heads * head_dim] in qkv's dtype."""
+    _need_cuda(qkv, kv.k)
+    check_attention_sizes(n_heads, n_kv_heads, head_dim)
+    n = qkv.shape[0]
+    out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    common = (_ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len))
+    if meta.is_decode:
+        scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len),
+                              dtype=torch.float32, device=qkv.device)
+        _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
+                _ptr(out), _ptr(scratch), meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens,
+                kv.block_table.shape[1], meta.max_kv_len, float(scale), _stream(), kernels=2)
+    else:
+        _launch("attention", "siar_attn_prefill", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
+                _ptr(out), meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1],
+                meta.max_q_len, float(scale), _stream())
+    return out
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for rows laid out as [gate (I) | up (I)]."""
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0 and gate_up.is_contiguous()
+    n, two_i = gate_up.shape
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _launch("elementwise", "siar_swiglu", _is_bf16(gate_up.dtype), _ptr(gate_up), _ptr(out), n, two_i // 2,
+            _stream())
+    return out
+
+
+def advance_lengths(base_len: torch.Tensor, q_start: torch.Tensor, n_seqs: int) -> None:
+    _need_cuda(base_len, q_start)
+    _launch("elementwise", "siar_advance_lengths", _ptr(base_len), _ptr(q_start), n_seqs, _stream())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seeds: torch.Tensor, draw_index: torch.Tensor, advance_index: bool = False,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token id per row of float32 ``logits`` [R, V]; per-row options are
+    device arrays (temperature f32, top_k i32, top_p f32, seeds i64, draw_index i32)."""
+    _need_cuda(logits, temperature, top_k, top_p, seeds, draw_index)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    r, v = logits.shape
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32
+    assert top_k.dtype == torch.int32 and draw_index.dtype == torch.int32 and seeds.dtype == torch.int64
+    for t in (temperature, top_k, top_p, seeds, draw_index):
+        assert t.numel() >= r
+    if out is None:
+        out = torch.empty(r, dtype=torch.int32, device=logits.device)
+    _launch("sampling", "siar_sample", _ptr(logits), r, v, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+            _ptr(seeds), _ptr(draw_index), int(advance_index), _ptr(out), _stream())
+    return out

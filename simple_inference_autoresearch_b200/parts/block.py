@@ -1,0 +1,60 @@
+"""Pre-norm residual block: ``x += mixer(norm1(x)); x += ffn(norm2(x))``.
+
+The adds are threaded the way the reference threads them (model/block.py:154-183):
+each sublayer's output is left *pending* and added inside the next norm's kernel,
+so no separate add is launched; the last block's pending delta is resolved by the
+model's final norm (model/llama.py:194).  A first block that receives no pending
+delta only norms (model/block.py:164-166).
+"""
+
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, PartSpec, TensorSpec
+
+
+@BLOCKS.register("prenorm")
+class PreNormBlock(Block):
+    """``mixer``, ``feed_forward``, ``mixer_norm`` and ``ffn_norm`` are PartSpecs whose
+    ``params`` may hold a ``prefix`` relative to this block's prefix."""
+
+    def __init__(self, prefix: str, position, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                 ffn_norm: PartSpec):
+        super().__init__(prefix)
+
+        def sub(registry, spec: PartSpec, **ctx):
+            params = dict(spec.params)
+            params["prefix"] = prefix + params.get("prefix", "")
+            return registry.build(PartSpec(spec.kind, params), **ctx)
+
+        self.mixer_norm = sub(NORMS, mixer_norm)
+        self.mixer = sub(MIXERS, mixer, position=position)
+        self.ffn_norm = sub(NORMS, ffn_norm)
+        self.ffn = sub(FEED_FORWARDS, feed_forward)
+        self._parts = [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [s for p in self._parts for s in p.tensor_specs()]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for p in self._parts:
+            p.load(tensors)
+
+    def extension_units(self):
+        return tuple(u for p in self._parts for u in p.extension_units())
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, ctx, residual, pending, cache_entry, writes_cache: bool = True):
+        if pending is None:
+            h = self.mixer_norm.norm(ctx, residual)
+        else:
+            h = self.mixer_norm.add_norm(ctx, residual, pending)
+        a = self.mixer.forward(ctx, h, cache_entry, writes_cache)
+        h = self.ffn_norm.add_norm(ctx, residual, a)
+        m = self.ffn.forward(ctx, h)
+        return residual, m

@@ -1,0 +1,50 @@
+"""SwiGLU feed-forward.
+
+    gu = x [W_gate; W_up]^T      (one product; rows [0, I) gate, [I, 2I) up)
+    f  = silu(gate) * up,  silu(g) = g * sigmoid(g)
+    m  = f W_down^T
+
+as the reference's MLP (ops/mlp.py:98-129,179-214; kernels/swiglu_kernel.py:139-140).
+The activation is computed in 32-bit from the stored ``gu`` and rounded once.
+"""
+
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from ..kernels import ops
+from .base import FEED_FORWARDS, FeedForward, TensorSpec
+
+
+@FEED_FORWARDS.register("swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, init_std: float = 0.02):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.init_std = init_std
+        self.w_gate_up: torch.Tensor = None
+        self.w_down: torch.Tensor = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, i, p, s = self.hidden_size, self.intermediate_size, self.prefix, self.init_std
+        return [
+            TensorSpec(p + "gate_proj.weight", (i, h), std=s),
+            TensorSpec(p + "up_proj.weight", (i, h), std=s),
+            TensorSpec(p + "down_proj.weight", (h, i), std=s),
+        ]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]],
+                                   dim=0).contiguous()
+        self.w_down = tensors[p + "down_proj.weight"].contiguous()
+
+    def extension_units(self):
+        return ("elementwise", "gemm_simt", "gemm_tc")
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(x, self.w_gate_up, ctx.dtype)
+        f = ops.swiglu(gu)
+        return ops.linear(f, self.w_down, torch.float32)
