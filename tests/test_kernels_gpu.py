@@ -1,0 +1,313 @@
+"""Each CUDA kernel alone against its plain restatement (tests/emulated_kernels.py),
+at sizes other than the engine's: widths and vocabularies that are no power of
+two, head sizes in steps of 16, any number of heads and groups, lengths that
+cross page, tile and chunk boundaries."""
+
+import math
+
+import pytest
+import torch
+
+from simple_inference_autoresearch_b200.cache import SequenceCache
+from simple_inference_autoresearch_b200.engine.batch import BatchMeta, StepEntry
+from simple_inference_autoresearch_b200.kernels import ops
+from simple_inference_autoresearch_b200.parts.base import KVNeed
+from tests import emulated_kernels as emu
+from tests import plain_llama
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,h,v", [(1, 64, 256), (7, 80, 331), (33, 4096, 1000)])
+def test_embed(dtype, n, h, v):
+    table = rnd(v, h, dtype=dtype)
+    tokens = torch.randint(0, v, (n,), dtype=torch.int32)
+    out = ops.embed(tokens.to(DEV), table.to(DEV))
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), emu.embed(tokens, table), rtol=0, atol=0)
+
+
+def test_embed_flags_bad_token():
+    table = rnd(16, 32).to(DEV)
+    ops.embed(torch.tensor([3, 16], dtype=torch.int32, device=DEV), table)
+    with pytest.raises(RuntimeError, match="token id outside"):
+        ops.check_status(DEV)
+    ops.check_status(DEV)  # cleared
+
+
+def test_gather_rows():
+    src = rnd(9, 331)
+    rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32)
+    out = ops.gather_rows(src.to(DEV), rows.to(DEV))
+    torch.testing.assert_close(out.cpu(), emu.gather_rows(src, rows), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,h,eps", [(1, 64, 1e-5), (5, 80, 1e-6), (3, 331, 1e-5), (2, 4096, 1e-5), (2, 5000, 1e-3)])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_add_rmsnorm(out_dtype, w_dtype, n, h, eps, with_delta):
+    res = rnd(n, h, seed=1)
+    delta = rnd(n, h, seed=2) if with_delta else None
+    w = (1 + rnd(h, seed=3, scale=0.1)).to(w_dtype)
+    res_ref = res.clone()
+    ref = emu.add_rmsnorm(res_ref, None if delta is None else delta.clone(), w, eps, out_dtype)
+    res_d = res.to(DEV)
+    out = ops.add_rmsnorm(res_d, None if delta is None else delta.to(DEV), w.to(DEV), eps, out_dtype)
+    torch.testing.assert_close(res_d.cpu(), res_ref, rtol=0, atol=0)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-6)
+    else:
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-3)
+
+
+def test_rmsnorm_rows_do_not_depend_on_batch():
+    h = 331
+    res = rnd(6, h, seed=4)
+    w = (1 + rnd(h, seed=5, scale=0.1))
+    whole = ops.add_rmsnorm(res.to(DEV), None, w.to(DEV), 1e-5, torch.float32).cpu()
+    for i in range(6):
+        one = ops.add_rmsnorm(res[i:i + 1].contiguous().to(DEV), None, w.to(DEV), 1e-5, torch.float32).cpu()
+        assert torch.equal(one[0], whole[i])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 37, 80), (70, 331, 96), (5, 256, 64), (16, 130, 264), (3, 64, 20),
+                                   (130, 65, 176), (8, 512, 1024), (17, 40, 8)])
+def test_linear(dtype, m, n, k):
+    x = rnd(m, k, dtype=dtype, seed=1)
+    w = rnd(n, k, dtype=dtype, seed=2, scale=0.1)
+    for out_dtype in {torch.float32, dtype}:
+        out = ops.linear(x.to(DEV), w.to(DEV), out_dtype)
+        ref = emu.linear(x, w, torch.float32)
+        if dtype == torch.float32:
+            torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-5)
+        elif out_dtype == torch.float32:
+            torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
+        else:
+            torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_linear_fp32_rows_do_not_depend_on_batch():
+    x = rnd(70, 96, seed=1)
+    w = rnd(331, 96, seed=2, scale=0.1).to(DEV)
+    whole = ops.linear(x.to(DEV), w, torch.float32).cpu()
+    for i in (0, 13, 69):
+        one = ops.linear(x[i:i + 1].contiguous().to(DEV), w, torch.float32).cpu()
+        assert torch.equal(one[0], whole[i])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    gu = rnd(5, 2 * 176, dtype=dtype, scale=2.0)
+    out = ops.swiglu(gu.to(DEV))
+    ref = emu.swiglu(gu)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **(dict(rtol=1e-5, atol=1e-6)
+                               if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)))
+
+
+# ----------------------------------------------------------------------------- attention over the cache
+def make_cache(n_kv, d, dtype, device, max_tokens=4096, max_slots=8, max_seq_len=2048):
+    return SequenceCache([KVNeed(n_kv, d)], max_tokens, max_slots, max_seq_len, dtype, device)
+
+
+def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None):
+    """Fills two caches (GPU kernel / CPU restatement) with the same history through
+    rope_kv_write, then compares rope + attention of a last step."""
+    torch.manual_seed(seed)
+    caches = {dev: make_cache(hkv, d, dtype, dev) for dev in ("cpu", DEV)}
+    backends = {"cpu": emu, DEV: ops}
+    inv_freq = plain_llama.rope_inv_freq(d, theta, None)
+    b = len(q_lens)
+    width = (hq + 2 * hkv) * d
+    slots = {dev: [c.alloc() for _ in range(b)] for dev, c in caches.items()}
+    # a decoy slot in between so that slot ids and pages are not the identity
+    hist = [rnd(max(n, 1), width, dtype=dtype, seed=10 + i) for i, n in enumerate(lens_before)]
+    new = [rnd(n, width, dtype=dtype, seed=50 + i) for i, n in enumerate(q_lens)]
+    if boost is not None:
+        # one far key whose score stands out for the last query of `seq` (no rotation,
+        # so that the key can simply be a multiple of the query of head 0)
+        seq, key_pos, scale = boost
+        inv_freq = None
+        hist[seq][key_pos, hq * d:(hq + 1) * d] = (new[seq][-1, :d].float() * scale).to(dtype)
+    outs = {}
+    for dev in ("cpu", DEV):
+        c, be = caches[dev], backends[dev]
+        live = [(i, s) for i, s in enumerate(slots[dev]) if lens_before[i] > 0]
+        if live:
+            ent = [StepEntry(s, [0] * lens_before[i]) for i, s in live]
+            c.reserve([s for _, s in live], [lens_before[i] for i, _ in live])
+            meta = BatchMeta.build(ent, [0] * len(live), dev)
+            qkv = torch.cat([hist[i] for i, _ in live]).to(dev)
+            be.rope_kv_write(qkv, None if inv_freq is None else inv_freq.to(dev), c.entry(0), meta, hq, hkv, d, True)
+            c.commit([s for _, s in live], [lens_before[i] for i, _ in live])
+        ent = [StepEntry(s, [0] * q_lens[i]) for i, s in enumerate(slots[dev])]
+        c.reserve(slots[dev], q_lens)
+        meta = BatchMeta.build(ent, list(lens_before), dev)
+        qkv = torch.cat(new).to(dev)
+        be.rope_kv_write(qkv, None if inv_freq is None else inv_freq.to(dev), c.entry(0), meta, hq, hkv, d, True)
+        out = be.attention(qkv, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d))
+        outs[dev] = (out.cpu().float(), qkv.cpu().float(), c.entry(0).k.cpu().float(), c.entry(0).v.cpu().float())
+    t = tol(dtype)
+    torch.testing.assert_close(outs[DEV][1], outs["cpu"][1], **t)   # rotated q (and untouched k, v columns)
+    torch.testing.assert_close(outs[DEV][2], outs["cpu"][2], **t)   # cached k
+    torch.testing.assert_close(outs[DEV][3], outs["cpu"][3], **t)   # cached v
+    torch.testing.assert_close(outs[DEV][0], outs["cpu"][0], **t)
+    return outs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (8, 8, 64), (8, 2, 128), (2, 1, 80)])
+def test_attention_prefill_sizes(dtype, hq, hkv, d):
+    run_attention_case(dtype, hq, hkv, d, lens_before=[0, 0, 0], q_lens=[5, 70, 33])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_prefill_continues_from_cache(dtype):
+    run_attention_case(dtype, 6, 2, 48, lens_before=[63, 0, 130], q_lens=[3, 65, 1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (8, 8, 64), (8, 2, 128), (12, 1, 32)])
+def test_attention_decode_sizes(dtype, hq, hkv, d):
+    # lengths around the page (64), tile (32) and chunk (256) edges, and position 0
+    run_attention_case(dtype, hq, hkv, d, lens_before=[0, 63, 255, 256, 600], q_lens=[1, 1, 1, 1, 1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("key_pos", [0, 31, 255, 256, 511])
+def test_attention_decode_finds_a_far_key(dtype, key_pos):
+    hq, hkv, d = 4, 2, 32
+    outs = run_attention_case(dtype, hq, hkv, d, lens_before=[700], q_lens=[1], boost=(0, key_pos, 8.0))
+    # head 0's softmax is all but one-hot on that key: its output is that key's value row
+    v_row = rnd(700, (hq + 2 * hkv) * d, dtype=dtype, seed=10)[key_pos, (hq + hkv) * d:(hq + hkv + 1) * d].float()
+    torch.testing.assert_close(outs[DEV][0][0, :d], v_row, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_prefill_finds_a_far_key(dtype):
+    run_attention_case(dtype, 4, 2, 32, lens_before=[300], q_lens=[40], boost=(0, 7, 8.0))
+
+
+def test_decode_and_prefill_kernels_agree():
+    """One new token through the prefill kernel and through the split decode
+    kernel: same keys, different reduction order, so equal beyond rounding."""
+    hq, hkv, d, n = 6, 2, 48, 517
+    c = make_cache(hkv, d, torch.float32, DEV)
+    inv_freq = plain_llama.rope_inv_freq(d, 10000.0, None).to(DEV)
+    s = c.alloc()
+    width = (hq + 2 * hkv) * d
+    hist = rnd(n, width, seed=1).to(DEV)
+    c.reserve([s], [n])
+    ops.rope_kv_write(hist, inv_freq, c.entry(0), BatchMeta.build([StepEntry(s, [0] * n)], [0], DEV), hq, hkv, d)
+    c.commit([s], [n])
+    c.reserve([s], [1])
+    new = rnd(1, width, seed=2).to(DEV)
+    meta = BatchMeta.build([StepEntry(s, [0])], [n], DEV)
+    ops.rope_kv_write(new, inv_freq, c.entry(0), meta, hq, hkv, d)
+    dec = ops.attention(new, c.entry(0), meta, hq, hkv, d, 0.2)
+    meta.is_decode = False
+    pre = ops.attention(new, c.entry(0), meta, hq, hkv, d, 0.2)
+    torch.testing.assert_close(dec, pre, rtol=1e-5, atol=1e-6)
+
+
+def test_attention_refuses_sizes_it_cannot_take():
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.check_attention_sizes(4, 2, 24)
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.check_attention_sizes(4, 2, 512)
+    with pytest.raises(ValueError, match="multiple"):
+        ops.check_attention_sizes(5, 2, 32)
+
+
+def test_rope_without_rotation_only_copies():
+    hq, hkv, d = 2, 1, 16
+    c = make_cache(hkv, d, torch.float32, DEV)
+    s = c.alloc()
+    c.reserve([s], [3])
+    qkv = rnd(3, (hq + 2 * hkv) * d).to(DEV)
+    before = qkv.clone()
+    ops.rope_kv_write(qkv, None, c.entry(0), BatchMeta.build([StepEntry(s, [0, 0, 0])], [0], DEV), hq, hkv, d)
+    assert torch.equal(qkv, before)
+    page = int(c.entry(0).block_table[s, 0])
+    assert torch.equal(c.entry(0).k[page, 0, :3], before[:, hq * d:(hq + 1) * d])
+    assert torch.equal(c.entry(0).v[page, 0, :3], before[:, (hq + 1) * d:])
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample_case(logits, temperature, top_k, top_p, seed, index):
+    r, v = logits.shape
+    dev = lambda x, dt: torch.tensor(x, dtype=dt, device=DEV)  # noqa: E731
+    out = ops.sample(logits.to(DEV), dev(temperature, torch.float32), dev(top_k, torch.int32),
+                     dev(top_p, torch.float32), dev(seed, torch.int64), dev(index, torch.int32))
+    return out.cpu().tolist()
+
+
+@pytest.mark.parametrize("v", [256, 331, 5000])
+def test_sample_greedy_is_argmax_with_lowest_index_on_ties(v):
+    logits = rnd(4, v, seed=3)
+    logits[1, 7] = logits[1, 200] = 9.0
+    got = sample_case(logits, [0.0] * 4, [0] * 4, [1.0] * 4, [1, 2, 3, 4], [0] * 4)
+    assert got == [int(torch.argmax(logits[i])) for i in range(4)]
+    assert got[1] == 7
+
+
+@pytest.mark.parametrize("v", [256, 331, 3000])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 5, 1.0), (0.7, 50, 0.9), (1.3, 0, 0.6),
+                                                     (1.0, 1, 1.0), (0.5, 40, 0.0), (1.0, 100000, 0.95)])
+def test_sample_matches_plain_sampler(v, temperature, top_k, top_p):
+    rows = 6
+    logits = rnd(rows, v, seed=11, scale=2.0)
+    seeds = [1234567 + 17 * i for i in range(rows)]
+    idx = [0, 1, 2, 3, 40, 41]
+    got = sample_case(logits, [temperature] * rows, [top_k] * rows, [top_p] * rows, seeds, idx)
+    for i in range(rows):
+        u = plain_llama.counter_uniform(seeds[i], idx[i])
+        want = plain_llama.sample(logits[i], temperature, top_k, top_p, u)
+        if got[i] != want:
+            # u may sit within rounding of a boundary of the cumulative distribution
+            probs = plain_llama.kept_probabilities(logits[i], temperature, top_k, top_p)
+            cdf = torch.cumsum(probs, 0)
+            assert probs[got[i]] > 0, "drew a token outside the kept set"
+            lo = cdf[got[i]] - probs[got[i]]
+            assert lo - 1e-5 <= u <= cdf[got[i]] + 1e-5, (got[i], want, u, float(lo), float(cdf[got[i]]))
+
+
+def test_sample_top_k_keeps_exactly_k_and_ties_go_to_lower_ids():
+    v = 300
+    logits = torch.zeros(1, v)
+    logits[0, [5, 9, 100]] = 3.0
+    logits[0, [50, 60, 70, 80]] = 2.0        # four tied at the 4th..7th rank, k = 5 keeps 50 and 60
+    seen = set()
+    for i in range(200):
+        seen.add(sample_case(logits, [1.0], [5], [1.0], [99], [i])[0])
+    assert seen <= {5, 9, 100, 50, 60} and {5, 9, 100} <= seen and seen & {50, 60}
+
+
+def test_sample_frequencies_follow_the_distribution():
+    v = 331
+    logits = rnd(1, v, seed=5, scale=1.5)
+    n = 4000
+    big = logits.repeat(n, 1)
+    got = sample_case(big, [0.9] * n, [0] * n, [1.0] * n, [7] * n, list(range(n)))
+    probs = plain_llama.kept_probabilities(logits[0], 0.9, 0, 1.0)
+    freq = torch.bincount(torch.tensor(got), minlength=v).double() / n
+    assert (freq - probs).abs().max() < 0.02
+
+
+def test_sample_same_request_same_draw_in_any_batch():
+    logits = rnd(5, 500, seed=8)
+    alone = sample_case(logits[2:3], [0.8], [0], [1.0], [42], [3])[0]
+    batch = sample_case(logits, [0.8] * 5, [0] * 5, [1.0] * 5, [1, 2, 42, 4, 5], [0, 0, 3, 0, 0])
+    assert batch[2] == alone
