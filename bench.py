@@ -1,0 +1,253 @@
+"""Decode and prefill throughput of the Llama-3.1-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with a
+2,048-token prompt in a cache sized for 4,096 tokens per sequence, timed on the
+device with CUDA events around K replays of the captured decode step; ``e2e`` is
+the same through ``Engine.run`` (the call the generation loop makes): host tokens
+in from pinned memory and sampled tokens back out every step.  ``prefill`` is one
+2,048-token prompt; ``points`` hold decode at batch 1 and 64; ``roofline`` compares
+the decode step with the bytes it has to read (each weight it uses once, plus the
+keys and values of the live sequences).  Weights are seeded random values of the
+real shape (there is no checkpoint offline); inputs exceed L2, so nothing stays
+cached between steps.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+PROMPT_TOKENS = 2048
+CONTEXT = 4096
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}, "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference's public API loads weights with huggingface_hub.snapshot_download "
+                          "(no network here), has no random-weights mode, and its kernels are Triton JIT"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import dataclasses
+
+    import torch
+
+    import simple_inference_autoresearch_b200 as siar
+    from simple_inference_autoresearch_b200.config import LlamaConfig, preset_path
+    from simple_inference_autoresearch_b200.engine import generation
+    from simple_inference_autoresearch_b200.kernels import ops
+
+    full = LlamaConfig.from_json(preset_path("llama-3.1-8b"))
+    cfg = dataclasses.replace(full, num_hidden_layers=args.layers) if args.layers else full
+    pk, pk_src = peaks()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+
+    loaded = siar.init_random(siar.build_model(cfg, torch.bfloat16, dev), seed=0)
+    model = loaded.model
+    max_b = max(args.batch, 1 if args.no_points else 64)
+    engine = siar.Engine(model, max_batch=max_b, max_seq_len=CONTEXT, use_cuda_graph=True)
+    gen = torch.Generator().manual_seed(0)
+    rand_tokens = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()  # noqa: E731
+
+    # ---------------------------------------------------------------- prefill, one prompt of 2,048 tokens
+    def prefill_once():
+        s = engine.open()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        toks = rand_tokens(PROMPT_TOKENS)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step([siar.StepEntry(s, toks, [PROMPT_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        engine.close(s)
+        return e0.elapsed_time(e1)
+
+    for _ in range(2):
+        prefill_once()
+    prefill_ms = statistics.median(prefill_once() for _ in range(3))
+    h, i, v, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    qkv_n = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    lin_params = L * (qkv_n * h + h * cfg.num_attention_heads * cfg.head_dim + 3 * h * i)
+    T = PROMPT_TOKENS
+    prefill_flops = 2 * T * lin_params + L * 4 * cfg.num_attention_heads * cfg.head_dim * T * T / 2 + 2 * v * h
+    prefill = {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---------------------------------------------------------------- decode at a batch size
+    kv_token_bytes = L * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    embed_bytes = v * h * 2
+    weight_bytes = model.weight_bytes() - embed_bytes * (0 if cfg.tie_word_embeddings else 1)
+
+    def decode_at(batch, steps, warmup, e2e):
+        slots_reqs = []
+        for b in range(batch):
+            r = generation.Request(rand_tokens(PROMPT_TOKENS), 10 ** 9, siar.SamplingParams(temperature=0.0), index=b)
+            r.slot = engine.open()
+            slots_reqs.append(r)
+        for g0 in range(0, batch, 8):   # real prefill, eight prompts to a step
+            grp = slots_reqs[g0:g0 + 8]
+            engine.step([siar.StepEntry(r.slot, r.prompt, []) for r in grp])
+        feed = [[1] for _ in slots_reqs]
+        for _ in range(warmup):
+            out = engine.run(slots_reqs, feed)
+            feed = [[t] for t in out]
+        # device-timed: K replays of the captured step (tokens, lengths and sampling stay on the device)
+        graph = engine._graphs[(batch, engine._graph_state.bucket)]
+        for r in slots_reqs:   # pages for the replays below
+            pass
+        engine.cache.reserve([r.slot for r in slots_reqs], [steps] * batch)
+        sampler = ClockSampler()
+        sampler.start()
+        before = ops.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        dev_ms = e0.elapsed_time(e1) / steps
+        launches = ops.launch_count - before
+        kv_mid = PROMPT_TOKENS + warmup + steps / 2
+        engine.cache.commit([r.slot for r in slots_reqs], [steps] * batch)
+        engine._graph_state.invalidate()
+        res = {"ms": dev_ms, "tok_s": batch / (dev_ms * 1e-3), "launches": launches,
+               "bytes": weight_bytes + batch * h * 2 + batch * kv_mid * kv_token_bytes}
+        if e2e:
+            feed = [[1] for _ in slots_reqs]
+            for _ in range(3):
+                out = engine.run(slots_reqs, feed)
+                feed = [[t] for t in out]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                out = engine.run(slots_reqs, feed)
+                feed = [[t] for t in out]
+            torch.cuda.synchronize()
+            res["e2e_tok_s"] = batch * steps / (time.perf_counter() - t0)
+        sampler.stop()
+        res["clocks"] = sampler.summary()
+        for r in slots_reqs:
+            engine.close(r.slot)
+        return res
+
+    head = decode_at(args.batch, args.steps, args.warmup, e2e=True)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_at(b, max(8, args.steps // 2), args.warmup, e2e=False)["tok_s"], 1)
+
+    achieved = head["bytes"] / (head["ms"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s @ batch 8 (Llama-3.1-8B shape, bf16, 2,048-token prompts, 4,096-token cache)",
+        "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+        "impl": "ours",
+        "config": {
+            "model": "llama-3.1-8b shape", "global_batch": args.batch, "seq_len": CONTEXT,
+            "prompt_tokens": PROMPT_TOKENS, "parallelism": "single GPU", "layers": L,
+            "layers_of_full_model": full.num_hidden_layers, "hidden_size": h, "intermediate_size": i,
+            "vocab_size": v, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "rope_theta": cfg.rope_theta, "rope_scaling": "llama3 factor 8",
+            "rms_norm_eps": cfg.rms_norm_eps, "tied_embeddings": cfg.tie_word_embeddings,
+            "l2": "inputs larger than L2 (weights + cache read every step)", "peaks": pk_src,
+        },
+        "e2e": {"value": round(head["e2e_tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
+                "d2h_bytes_per_step": 4 * args.batch + 4},
+        "gpu_launches": head["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk_src},
+        "points": points,
+        "clocks": head["clocks"],
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

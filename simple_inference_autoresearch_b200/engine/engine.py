@@ -133,7 +133,11 @@ class Engine:
             bucket *= 2
         bucket = min(bucket, self.max_seq_len)
         if st.slots != slots or st.bucket != bucket:
-            st.upload(requests, [t[0] for t in new_tokens], bucket)
+            st.upload(requests, bucket)
+        # the step's input tokens come from the host every step, as the caller gives them
+        for j, t in enumerate(new_tokens):
+            st.host_in[j] = t[0]
+        st.tokens[:b].copy_(st.host_in[:b], non_blocking=True)
         key = (b, bucket)
         g = self._graphs.get(key)
         if g is None:
@@ -204,6 +208,7 @@ class _GraphBuffers:
         self.draw_index = z(capacity, torch.int32)
         self.seeds = z(capacity, torch.int64)
         self.host_tokens = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.host_in = torch.zeros(capacity, dtype=torch.int32).pin_memory()
         self.engine = engine
         self.slots: Optional[List[int]] = None
         self.bucket = 0
@@ -211,19 +216,17 @@ class _GraphBuffers:
     def invalidate(self) -> None:
         self.slots = None
 
-    def upload(self, requests, tokens: Sequence[int], bucket: int) -> None:
+    def upload(self, requests, bucket: int) -> None:
         eng = self.engine
         b = len(requests)
         f, i, s = eng._sampling_arrays(requests)
-        ints = np.concatenate([np.asarray(tokens, dtype=np.int32),
-                               np.asarray([r.slot for r in requests], dtype=np.int32),
+        ints = np.concatenate([np.asarray([r.slot for r in requests], dtype=np.int32),
                                np.asarray([eng.cache.length(r.slot) for r in requests], dtype=np.int32), i])
         ints_d, f_d, s_d = eng._upload(ints), eng._upload(f), eng._upload(s)
-        self.tokens[:b].copy_(ints_d[0:b])
-        self.slot_ids[:b].copy_(ints_d[b:2 * b])
-        self.base_len[:b].copy_(ints_d[2 * b:3 * b])
-        self.top_k[:b].copy_(ints_d[3 * b:4 * b])
-        self.draw_index[:b].copy_(ints_d[4 * b:5 * b])
+        self.slot_ids[:b].copy_(ints_d[0:b])
+        self.base_len[:b].copy_(ints_d[b:2 * b])
+        self.top_k[:b].copy_(ints_d[2 * b:3 * b])
+        self.draw_index[:b].copy_(ints_d[3 * b:4 * b])
         self.temperature[:b].copy_(f_d[:b])
         self.top_p[:b].copy_(f_d[b:])
         self.seeds[:b].copy_(s_d)

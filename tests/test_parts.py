@@ -1,0 +1,260 @@
+"""The parts of a layer alone, the run order as data, and a toy mixer with state
+of its own that is registered, built and stepped without touching the library's
+files.  Every test runs on the GPU (``-m gpu``); the same bodies also run on the
+CPU with the kernels swapped for their plain restatements, which checks the
+Python side (wiring, cache, batching) where there is no GPU."""
+
+import math
+
+import pytest
+import torch
+
+import simple_inference_autoresearch_b200 as siar
+from simple_inference_autoresearch_b200 import StepEntry, registry
+from simple_inference_autoresearch_b200.config import LlamaConfig
+from simple_inference_autoresearch_b200.engine.batch import BatchMeta
+from simple_inference_autoresearch_b200.engine.model import DecoderModel, ModelSpec, ScheduleEntry, StepContext
+from simple_inference_autoresearch_b200.architectures.llama import llama_model_spec
+from simple_inference_autoresearch_b200.cache import SequenceCache
+from simple_inference_autoresearch_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS,
+                                                      Mixer, PartSpec, StateNeed, TensorSpec)
+from simple_inference_autoresearch_b200.weights import random_tensors
+from tests import emulated_kernels, plain_llama, tiny_configs
+
+DEVICES = [pytest.param("cpu", id="cpu-emulated"), pytest.param("cuda", marks=pytest.mark.gpu, id="gpu")]
+
+
+@pytest.fixture(params=DEVICES)
+def device(request, monkeypatch):
+    if request.param == "cpu":
+        emulated_kernels.install(monkeypatch)
+    return request.param
+
+
+def tensors_for(part, seed, dtype, device):
+    return {k: v.to(device) for k, v in random_tensors(part.tensor_specs(), seed, dtype).items()}
+
+
+def meta_for(device, q_lens, base_lens, slots):
+    return BatchMeta.build([StepEntry(s, [0] * n) for s, n in zip(slots, q_lens)], base_lens, device)
+
+
+# ----------------------------------------------------------------------------- parts alone
+def test_norm_part(device):
+    norm = NORMS.build(PartSpec("rmsnorm", {"prefix": "n.", "hidden_size": 80, "eps": 1e-6,
+                                            "weight_init": "ones_plus_normal"}))
+    assert [s.name for s in norm.tensor_specs()] == ["n.weight"]
+    w = tensors_for(norm, 1, torch.float32, device)
+    norm.load(w)
+    ctx = StepContext(torch.float32, None, None)
+    res = torch.randn(5, 80, generator=torch.Generator().manual_seed(0))
+    delta = torch.randn(5, 80, generator=torch.Generator().manual_seed(1))
+    r = res.clone().to(device)
+    out = norm.add_norm(ctx, r, delta.to(device))
+    torch.testing.assert_close(r.cpu(), res + delta)
+    torch.testing.assert_close(out.cpu(), plain_llama.rmsnorm(res + delta, w["n.weight"].cpu(), 1e-6),
+                               rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(norm.norm(ctx, r).cpu(), out.cpu())
+
+
+def test_position_part_matches_the_reference_frequencies():
+    for raw in (tiny_configs.TINY_A, tiny_configs.TINY_B):
+        d = raw.get("head_dim") or raw["hidden_size"] // raw["num_attention_heads"]
+        pos = POSITION_ENCODINGS.build(PartSpec("rotary", {"head_dim": d, "theta": raw["rope_theta"],
+                                                           "scaling": raw["rope_scaling"]}))
+        want = plain_llama.rope_inv_freq(d, raw["rope_theta"], raw["rope_scaling"])
+        assert torch.equal(pos.rotary().inv_freq, want)
+    assert POSITION_ENCODINGS.build(PartSpec("none")).rotary() is None
+
+
+def test_feed_forward_part(device):
+    ffn = FEED_FORWARDS.build(PartSpec("swiglu", {"prefix": "m.", "hidden_size": 80, "intermediate_size": 136}))
+    w = tensors_for(ffn, 2, torch.float32, device)
+    ffn.load(w)
+    x = torch.randn(7, 80, generator=torch.Generator().manual_seed(3))
+    out = ffn.forward(StepContext(torch.float32, None, None), x.to(device))
+    ref = plain_llama.swiglu_mlp(x, {k: v.cpu() for k, v in w.items()}, "m.")
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-6)
+
+
+def test_mixer_part_over_a_cache(device):
+    """The attention mixer alone: a prompt in one step, then two single tokens,
+    equals the plain attention block over the whole sequence."""
+    c = {"H": 80, "Hq": 6, "Hkv": 2, "D": 48}
+    pos = POSITION_ENCODINGS.build(PartSpec("rotary", {"head_dim": 48, "theta": 10000.0, "scaling": None}),
+                                   device=device)
+    mixer = MIXERS.build(PartSpec("gqa_attention", {"prefix": "a.", "hidden_size": 80, "n_heads": 6,
+                                                    "n_kv_heads": 2, "head_dim": 48}), position=pos)
+    w = tensors_for(mixer, 4, torch.float32, device)
+    mixer.load(w)
+    cache = SequenceCache([mixer.cache_need()], 256, 2, 128, torch.float32, device)
+    decoy, s = cache.alloc(), cache.alloc()
+    x = torch.randn(12, 80, generator=torch.Generator().manual_seed(5))
+    outs, done = [], 0
+    for n in (10, 1, 1):
+        cache.reserve([s], [n])
+        ctx = StepContext(torch.float32, meta_for(device, [n], [done], [s]), cache)
+        outs.append(mixer.forward(ctx, x[done:done + n].contiguous().to(device), cache.entry(0), True).cpu())
+        cache.commit([s], [n])
+        done += n
+    ref = plain_llama.attention_block(x, {k: v.cpu() for k, v in w.items()}, "a.", c,
+                                      plain_llama.rope_inv_freq(48, 10000.0, None))
+    torch.testing.assert_close(torch.cat(outs), ref, rtol=2e-5, atol=2e-6)
+
+
+def test_block_part_threads_the_residual(device):
+    cfg = LlamaConfig.from_dict(tiny_configs.TINY_C)
+    spec = llama_model_spec(cfg, norm_weight_init="ones_plus_normal")
+    pos = POSITION_ENCODINGS.build(spec.position, device=device)
+    blk = BLOCKS.build(spec.layers[1], position=pos)
+    w = tensors_for(blk, 6, torch.float32, device)
+    blk.load(w)
+    cache = SequenceCache([blk.cache_need()], 128, 1, 64, torch.float32, device)
+    s = cache.alloc()
+    cache.reserve([s], [9])
+    ctx = StepContext(torch.float32, meta_for(device, [9], [0], [s]), cache)
+    x = torch.randn(9, 80, generator=torch.Generator().manual_seed(7))
+    pending = torch.randn(9, 80, generator=torch.Generator().manual_seed(8))
+    residual, m = blk.forward(ctx, x.clone().to(device), pending.to(device), cache.entry(0), True)
+    c = plain_llama.parse_config(tiny_configs.TINY_C)
+    ref = plain_llama.block(x + pending, {k: v.cpu() for k, v in w.items()}, 1, c,
+                            plain_llama.rope_inv_freq(c["D"], c["theta"], None))
+    torch.testing.assert_close((residual + m).cpu(), ref, rtol=2e-5, atol=2e-6)
+
+
+# ----------------------------------------------------------------------------- the run order is data
+def test_schedule_may_repeat_a_layer_and_share_a_cache(device, tmp_path):
+    """Layer 0 runs twice (two cache entries of its own), and the last run reads
+    the cache that the run of layer 1 wrote instead of writing one."""
+    folder = tiny_configs.make_folder(tmp_path, "C", seed=3)
+    raw, w = tiny_configs.read_folder(folder)
+    cfg = LlamaConfig.from_dict(raw)
+    base = llama_model_spec(cfg)
+    sched = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(1, 1, writes_cache=False))
+    spec = ModelSpec(**{**base.__dict__, "schedule": sched})
+    model = DecoderModel(spec, torch.float32, device)
+    assert len(model.cache_needs) == 3
+    model.load({k: v.float().to(device) for k, v in w.items()})
+    eng = siar.Engine(model, max_batch=2, max_seq_len=128, use_cuda_graph=False)
+    toks = torch.randint(0, raw["vocab_size"], (45,), generator=torch.Generator().manual_seed(2)).tolist()
+    s = eng.open()
+    outs = [eng.step([StepEntry(s, toks[:30], range(30))])]
+    outs += [eng.step([StepEntry(s, [t], [0])]) for t in toks[30:]]
+    ref = plain_llama.forward(w, raw, toks, schedule=[(e.layer, e.cache_entry, e.writes_cache) for e in sched])
+    torch.testing.assert_close(torch.cat(outs).cpu(), ref, rtol=2e-5, atol=2e-5)
+    plain = plain_llama.forward(w, raw, toks)
+    assert (ref - plain).abs().max() > 1e-3     # the schedule really changes the function
+    for bad in ((ScheduleEntry(0, 0), ScheduleEntry(1, 0)),                        # two writers of one entry
+                (ScheduleEntry(0, 1, writes_cache=False), ScheduleEntry(1, 1)),     # read before write
+                (ScheduleEntry(5, 0),)):                                            # no such layer
+        with pytest.raises(ValueError):
+            DecoderModel(ModelSpec(**{**base.__dict__, "schedule": bad}), torch.float32, device)
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state of its own
+class RunningMeanMixer(Mixer):
+    """y_t = W * mean(x_0 .. x_t): per-sequence state = (sum [H], count [1]).
+    Written with torch ops; it stands for a mixer that is not attention."""
+
+    def __init__(self, prefix, position, hidden_size):
+        super().__init__(prefix)
+        self.h = hidden_size
+        self.w = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix + "w", (self.h, self.h), std=0.1)]
+
+    def load(self, tensors):
+        self.w = tensors[self.prefix + "w"]
+
+    def cache_need(self):
+        return StateNeed((self.h + 1,), "float32")
+
+    def forward(self, ctx, x, cache_entry, writes_cache=True):
+        m, st = ctx.meta, cache_entry.state
+        out = torch.empty(x.shape[0], self.h, dtype=torch.float32, device=x.device)
+        row = 0
+        for slot, n in zip(m.slots, m.q_lens):
+            xs = x[row:row + n].float()
+            sums = st[slot, :self.h] + torch.cumsum(xs, 0)
+            counts = st[slot, self.h] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+            out[row:row + n] = (sums / counts[:, None]) @ self.w.float().T
+            st[slot, :self.h] = sums[-1]
+            st[slot, self.h] = counts[-1]
+            row += n
+        return out
+
+
+def toy_spec(cfg_like, **_):
+    h, v = cfg_like.hidden_size, cfg_like.vocab_size
+    norm = lambda p: PartSpec("rmsnorm", {"prefix": p, "hidden_size": h, "eps": 1e-5})  # noqa: E731
+    attn = PartSpec("gqa_attention", {"prefix": "attn.", "hidden_size": h, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16})
+    toy = PartSpec("running_mean", {"prefix": "mix.", "hidden_size": h})
+    ffn = PartSpec("swiglu", {"prefix": "ffn.", "hidden_size": h, "intermediate_size": 40})
+    layer = lambda i, mixer: PartSpec("prenorm", {"prefix": f"l{i}.", "mixer": mixer, "feed_forward": ffn,  # noqa: E731
+                                                  "mixer_norm": norm("n1."), "ffn_norm": norm("n2.")})
+    return ModelSpec(architecture="ToyForCausalLM", vocab_size=v, hidden_size=h, max_position=128,
+                     embedding_name="emb", head_name=None,
+                     position=PartSpec("rotary", {"head_dim": 16, "theta": 10000.0, "scaling": None}),
+                     layers=(layer(0, toy), layer(1, attn), layer(2, toy)), final_norm=norm("nf."))
+
+
+def toy_plain(w, h, tokens):
+    """The toy model written out plainly, whole sequence, for comparison."""
+    x = w["emb"][torch.tensor(tokens)]
+    c = {"H": h, "Hq": 2, "Hkv": 1, "D": 16}
+    inv = plain_llama.rope_inv_freq(16, 10000.0, None)
+    for i in range(3):
+        p = f"l{i}."
+        hn = plain_llama.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+        if i == 1:
+            a = plain_llama.attention_block(hn, w, p + "attn.", c, inv)
+        else:
+            mean = torch.cumsum(hn, 0) / torch.arange(1, len(tokens) + 1)[:, None]
+            a = mean @ w[p + "mix.w"].T
+        x = x + a
+        x = x + plain_llama.swiglu_mlp(plain_llama.rmsnorm(x, w[p + "n2.weight"], 1e-5), w, p + "ffn.")
+    return plain_llama.rmsnorm(x, w["nf.weight"], 1e-5) @ w["emb"].T
+
+
+def test_toy_mixer_with_its_own_state_registers_builds_and_steps(device):
+    MIXERS.register("running_mean")(RunningMeanMixer)
+    registry.register_architecture("ToyForCausalLM", ("toy",), config_cls=LlamaConfig, spec_builder=toy_spec)
+    try:
+        class Cfg:
+            hidden_size, vocab_size = 32, 50
+        arch = registry.resolve({"architectures": ["ToyForCausalLM"]})
+        model = DecoderModel(arch.spec_builder(Cfg), torch.float32, device)
+        kinds = [type(n).__name__ for n in model.cache_needs]
+        assert kinds == ["StateNeed", "KVNeed", "StateNeed"]
+        w = random_tensors(model.tensor_specs(), 9, torch.float32)
+        model.load({k: v.to(device) for k, v in w.items()})
+        eng = siar.Engine(model, max_batch=3, max_seq_len=128, use_cuda_graph=False)
+        g = torch.Generator().manual_seed(4)
+        reqs = [torch.randint(0, 50, (n,), generator=g).tolist() for n in (20, 7, 33)]
+        for rounds in range(2):                 # second round reuses the slots: state must start from zero
+            slots = [eng.open() for _ in reqs]
+            got = [[] for _ in reqs]
+            heads = [len(r) - 5 for r in reqs]
+            out = eng.step([StepEntry(s, r[:h], range(h)) for s, r, h in zip(slots, reqs, heads)])
+            o = 0
+            for i, h in enumerate(heads):
+                got[i].append(out[o:o + h]); o += h
+            for k in range(5):
+                out = eng.step([StepEntry(s, [r[h + k]], [0]) for s, r, h in zip(slots, reqs, heads)])
+                for i in range(len(reqs)):
+                    got[i].append(out[i:i + 1])
+            for i, r in enumerate(reqs):
+                torch.testing.assert_close(torch.cat(got[i]).cpu(), toy_plain(w, 32, r), rtol=2e-5, atol=2e-5)
+            for s in slots:
+                eng.close(s)
+    finally:
+        MIXERS.unregister("running_mean")
+        registry.unregister_architecture("ToyForCausalLM")
+
+
+def test_unknown_part_kind_is_a_clear_error():
+    with pytest.raises(ValueError, match="unknown mixer kind 'nope'"):
+        MIXERS.build(PartSpec("nope"))
+    with pytest.raises(ValueError, match="already registered"):
+        MIXERS.register("gqa_attention")(RunningMeanMixer)

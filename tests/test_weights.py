@@ -1,0 +1,114 @@
+"""Weights by name: what is held in which dtype, and ONE error that lists all
+missing and unexpected tensors and wrong shapes (no GPU)."""
+
+import json
+
+import pytest
+import torch
+from safetensors.torch import load_file, save_file
+
+import simple_inference_autoresearch_b200 as siar
+from simple_inference_autoresearch_b200.weights import WeightError, write_model_folder
+from simple_inference_autoresearch_b200.weights.loader import INDEX_FILE, SINGLE_FILE
+from tests import tiny_configs
+
+
+def test_random_folder_has_the_checkpoint_names_and_is_reproducible(tmp_path):
+    a = tiny_configs.make_folder(tmp_path / "1", "A", seed=7)
+    b = tiny_configs.make_folder(tmp_path / "2", "A", seed=7)
+    c = tiny_configs.make_folder(tmp_path / "3", "A", seed=8)
+    wa, wb, wc = (load_file(str(f / SINGLE_FILE)) for f in (a, b, c))
+    names = set(wa)
+    assert "model.embed_tokens.weight" in names and "model.norm.weight" in names
+    assert "model.layers.1.self_attn.k_proj.weight" in names and "model.layers.0.mlp.down_proj.weight" in names
+    assert "lm_head.weight" not in names          # tied
+    assert len(names) == 1 + 2 * 9 + 1
+    assert all(torch.equal(wa[n], wb[n]) for n in names)
+    assert not torch.equal(wa["model.embed_tokens.weight"], wc["model.embed_tokens.weight"])
+    assert wa["model.layers.0.self_attn.q_proj.weight"].dtype == torch.bfloat16
+    assert abs(wa["model.embed_tokens.weight"].float().std().item() - 0.02) < 0.002
+    assert torch.all(wa["model.norm.weight"] == 1)
+    wB = load_file(str(tiny_configs.make_folder(tmp_path, "B") / SINGLE_FILE))
+    assert "lm_head.weight" in wB and not torch.all(wB["model.norm.weight"] == 1)
+    assert wB["model.layers.2.self_attn.k_proj.weight"].shape == (32, 96)
+    raw = json.loads((a / "config.json").read_text())
+    assert raw["architectures"] == ["LlamaForCausalLM"] and raw["num_hidden_layers"] == 2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_held_dtypes(tmp_path, dtype):
+    # norm weights stored in float32 stay float32; matrices take the compute dtype
+    folder = tiny_configs.make_folder(tmp_path, "B", vector_dtype=torch.float32)
+    m = siar.load_model(folder, device="cpu", dtype=dtype).model
+    assert m.embedding.dtype == dtype and m.head.dtype == dtype
+    assert m.layers[0].mixer.w_qkv.dtype == dtype and m.layers[0].mixer.w_qkv.shape == (5 * 32, 96)
+    assert m.layers[0].ffn.w_gate_up.shape == (512, 96)
+    assert m.layers[0].mixer_norm.weight.dtype == torch.float32
+    assert m.final_norm.weight.dtype == torch.float32
+    folder = tiny_configs.make_folder(tmp_path / "x", "B")
+    m = siar.load_model(folder, device="cpu", dtype=dtype).model
+    assert m.final_norm.weight.dtype == dtype
+    # merged weights are the checkpoint's rows in q, k, v / gate, up order
+    w = load_file(str(folder / SINGLE_FILE))
+    p = "model.layers.1.self_attn."
+    want = torch.cat([w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"]]).to(dtype)
+    assert torch.equal(m.layers[1].mixer.w_qkv, want)
+
+
+def test_tied_head_is_the_embedding(tmp_path):
+    m = siar.load_model(tiny_configs.make_folder(tmp_path, "A"), device="cpu", dtype=torch.float32).model
+    assert m.head.data_ptr() == m.embedding.data_ptr()
+    m = siar.load_model(tiny_configs.make_folder(tmp_path, "B"), device="cpu", dtype=torch.float32).model
+    assert m.head.data_ptr() != m.embedding.data_ptr()
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
+    folder = tiny_configs.make_folder(tmp_path, "B")
+    w = load_file(str(folder / SINGLE_FILE))
+    del w["model.layers.1.mlp.up_proj.weight"]
+    del w["lm_head.weight"]
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    w["model.layers.2.self_attn.q_proj.weight"] = torch.zeros(96, 95, dtype=torch.bfloat16)
+    w["model.norm.weight"] = torch.zeros(97, dtype=torch.bfloat16)
+    save_file(w, str(folder / SINGLE_FILE))
+    with pytest.raises(WeightError) as e:
+        siar.load_model(folder, device="cpu", dtype=torch.float32)
+    err = e.value
+    assert err.missing == ["lm_head.weight", "model.layers.1.mlp.up_proj.weight"]
+    assert err.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert sorted(n for n, _, _ in err.wrong_shape) == ["model.layers.2.self_attn.q_proj.weight", "model.norm.weight"]
+    text = str(err)
+    for piece in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes (2)", "expected (96, 96)",
+                  "file has (96, 95)"):
+        assert piece in text
+
+
+def test_tied_model_may_carry_a_stored_head(tmp_path):
+    folder = tiny_configs.make_folder(tmp_path, "A")
+    w = load_file(str(folder / SINGLE_FILE))
+    w["lm_head.weight"] = w["model.embed_tokens.weight"].clone()
+    save_file(w, str(folder / SINGLE_FILE))
+    siar.load_model(folder, device="cpu", dtype=torch.float32)
+
+
+def test_sharded_checkpoint_with_index(tmp_path):
+    folder = tiny_configs.make_folder(tmp_path, "A")
+    w = load_file(str(folder / SINGLE_FILE))
+    names = sorted(w)
+    half = len(names) // 2
+    shards = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+    for fname, ns in shards.items():
+        save_file({n: w[n] for n in ns}, str(folder / fname))
+    (folder / INDEX_FILE).write_text(json.dumps({"weight_map": {n: f for f, ns in shards.items() for n in ns}}))
+    (folder / SINGLE_FILE).unlink()
+    m = siar.load_model(folder, device="cpu", dtype=torch.float32).model
+    assert torch.equal(m.embedding, w["model.embed_tokens.weight"].float())
+    (folder / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(FileNotFoundError, match="shard"):
+        siar.load_model(folder, device="cpu", dtype=torch.float32)
+
+
+def test_folder_without_weights(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps(tiny_configs.TINY_A))
+    with pytest.raises(FileNotFoundError, match="neither"):
+        siar.load_model(tmp_path, device="cpu", dtype=torch.float32)
