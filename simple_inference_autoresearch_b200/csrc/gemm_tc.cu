@@ -1,0 +1,450 @@
+// bfloat16 matrix products C[M,N] = A[M,K] * W[N,K]^T on the 5th-generation tensor
+// cores of sm_100a: operands staged in shared memory by TMA (128-byte swizzle),
+// tcgen05.mma issued by one thread with the float32 accumulator in tensor memory,
+// tcgen05.ld for the epilogue.  These are the products the reference sends to
+// cuBLAS or to its Triton GEMMs (ops/attention.py:139-178,348; ops/mlp.py:179-214;
+// ops/embedding.py:123-141).
+//
+// One kernel serves both orientations, because A and W are both K-major:
+//   D[P x Q] = X[P,K] * Y[Q,K]^T,  X rows on the 128-wide MMA M axis, Y rows on N.
+//   * many rows (prefill): X = A, Y = W, C[p][q] = D[p][q].
+//   * few rows (decode, M <= 128): X = W, Y = A ("swap-AB": the weight fills the
+//     128-row axis and the batch sits on the narrow N axis), C[q][p] = D[p][q].
+// Few output tiles are cut along K (split-K): each part writes a float32 partial,
+// and the last part to finish adds all partials of the tile in part order, so the
+// sum does not depend on which part finished last.
+//
+// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory
+// and issues the MMAs, warps 2..5 run the epilogue (warp w reads TMEM lanes
+// 32*(w%4) .. 32*(w%4)+31).  Every wait on an mbarrier is bounded; when a wait
+// expires the block raises a status flag, drains, frees its tensor memory and
+// returns (the result of that launch is then invalid and the host raises).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace siar {
+
+constexpr int kBM = 128;     // MMA M
+constexpr int kBK = 64;      // one 128-byte swizzle row of bf16
+constexpr int kUmmaK = 16;
+constexpr long long kWaitCycles = 2000000000ll;   // about one second of SM clock
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when about a second has passed without the phase completing.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity))
+    if (clock64() - t0 > kWaitCycles) return false;
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused with swizzle), 16 B
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+#define SIAR_TMEM_LD_16(taddr, r)                                                                                  \
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];" \
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),   \
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) \
+               : "r"(taddr))
+
+template <typename TOut> __device__ __forceinline__ void store_out(TOut* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+struct GemmParams {
+  void* C;            // output, TOut
+  float* partial;     // split-K planes [splits][rows_c * ldc] (nullptr when splits == 1)
+  int* counters;      // one per output tile, zero between launches
+  int* status;
+  int P, Q, K;        // D is P x Q
+  int ldc;            // leading dimension of C
+  int transpose_out;  // 0: C[p][q], 1: C[q][p]
+  int kb_per_split;   // k-blocks of 64 per split
+  long long plane;    // elements of one split-K plane
+};
+
+// ------------------------------------------------------------------ kernel
+template <int BN, int STAGES, typename TOut>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY, const GemmParams prm) {
+  constexpr uint32_t kXBytes = kBM * kBK * 2;
+  constexpr uint32_t kYBytes = BN * kBK * 2;
+  constexpr uint32_t kStageBytes = kXBytes + kYBytes;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int is_last;
+
+  const uint32_t dyn = smem_u32(smem_dyn);
+  unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p0 = blockIdx.x * kBM, q0 = blockIdx.y * BN;
+  const int num_kb_total = (prm.K + kBK - 1) / kBK;
+  const int kb_begin = blockIdx.z * prm.kb_per_split;
+  const int kb_end = min(num_kb_total, kb_begin + prm.kb_per_split);
+  const int num_kb = kb_end - kb_begin;
+  const int splits = gridDim.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full_bar, 1);
+    abort_flag = 0;
+    is_last = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  // A block that starts after another one has reported an expired wait does no work:
+  // a broken launch then ends after one wave instead of one second per block.
+  const bool dead = (*(volatile int*)prm.status & kStatusWaitExpired) != 0;
+
+  if (dead) {
+    // fall through to the teardown
+  } else if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmY) : "memory");
+      int issued = 0;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1) || *(volatile int*)&abort_flag) {
+          abort_flag = 1;
+          atomicOr(prm.status, kStatusWaitExpired);
+          break;
+        }
+        unsigned char* xs = tiles + (size_t)s * kStageBytes;
+        mbar_expect_tx(&full_bar[s], kStageBytes);
+        tma_load_2d(xs, &tmX, &full_bar[s], (kb_begin + i) * kBK, p0);
+        tma_load_2d(xs + kXBytes, &tmY, &full_bar[s], (kb_begin + i) * kBK, q0);
+        issued = i + 1;
+      }
+      if (*(volatile int*)&abort_flag) {
+        // let the copies that are still in flight land before the block leaves
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(BN < 16 ? 16 : BN);
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], ph) || *(volatile int*)&abort_flag) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t xs = smem_u32(tiles + (size_t)s * kStageBytes);
+        const uint64_t da = smem_desc_sw128(xs), db = smem_desc_sw128(xs + kXBytes);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          // advancing 16 elements along K inside the swizzled row = 32 bytes = 2 descriptor units
+          umma_f16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+      }
+      umma_commit(&tmem_full_bar);    // accumulator complete (or abandoned)
+    }
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> global
+    const int quad = warp & 3;
+    const int p = p0 + quad * 32 + lane;
+    bool ok = true;
+    if (num_kb > 0) {
+      ok = mbar_wait(&tmem_full_bar, 0);
+      if (!ok) { abort_flag = 1; atomicOr(prm.status, kStatusWaitExpired); }
+    }
+    tc_fence_after();
+    ok = ok && !*(volatile int*)&abort_flag;
+    float* plane = prm.partial ? prm.partial + (long long)blockIdx.z * prm.plane : nullptr;
+    TOut* C = (TOut*)prm.C;
+    constexpr int kChunks = (BN + 15) / 16;
+#pragma unroll 1
+    for (int ch = 0; ch < kChunks; ++ch) {
+      uint32_t r[16];
+      if (num_kb > 0 && ok) {
+        SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0u;
+      }
+      if (p < prm.P) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int q = q0 + ch * 16 + j;
+          if (q < prm.Q) {
+            const long long idx = prm.transpose_out ? (long long)q * prm.ldc + p : (long long)p * prm.ldc + q;
+            const float v = __uint_as_float(r[j]);
+            if (plane) plane[idx] = v; else store_out<TOut>(C + idx, v);
+          }
+        }
+      }
+    }
+    if (plane) {
+      // split-K: the part that arrives last adds the partials of this tile in part order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const int old = atomicAdd(prm.counters + tile, 1);
+        is_last = (old == splits - 1);
+        if (old == splits - 1) prm.counters[tile] = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (is_last) {
+        __threadfence();
+        const int et = threadIdx.x - 64;   // 0..127
+        if (prm.transpose_out) {
+          // rows of C are q; p is contiguous
+          for (int j = 0; j < BN; ++j) {
+            const int q = q0 + j, pp = p0 + et;
+            if (q < prm.Q && pp < prm.P) {
+              const long long idx = (long long)q * prm.ldc + pp;
+              float acc = 0.f;
+              for (int z = 0; z < splits; ++z) acc += __ldcg(prm.partial + (long long)z * prm.plane + idx);
+              store_out<TOut>(C + idx, acc);
+            }
+          }
+        } else {
+          for (int e = et; e < kBM * BN; e += 128) {
+            const int pp = p0 + e / BN, q = q0 + e % BN;
+            if (q < prm.Q && pp < prm.P) {
+              const long long idx = (long long)pp * prm.ldc + q;
+              float acc = 0.f;
+              for (int z = 0; z < splits; ++z) acc += __ldcg(prm.partial + (long long)z * prm.plane + idx);
+              store_out<TOut>(C + idx, acc);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, K, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && K == o.K && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.K << 20) ^ (size_t)k.box_rows;
+  }
+};
+
+// A [rows, K] bf16 matrix, K contiguous, seen in boxes of box_rows x 64 with the
+// 128-byte swizzle; reads past rows or K give zeros.
+static bool tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, K, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estride[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+template <int BN, int STAGES, typename TOut>
+static int launch(const CUtensorMap& tmX, const CUtensorMap& tmY, const GemmParams& prm, int splits, cudaStream_t s) {
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+  auto kern = gemm_tc_kernel<BN, STAGES, TOut>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((prm.P + kBM - 1) / kBM, (prm.Q + BN - 1) / BN, splits);
+  kern<<<grid, 192, smem, s>>>(tmX, tmY, prm);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace siar
+
+using namespace siar;
+
+// Float32 elements of split-K scratch and int32 tile counters siar_gemm_tc_bf16 may need for these sizes.
+extern "C" int siar_gemm_tc_max_tiles() { return 4096; }
+
+// Returns 0 on launch, a cudaError_t on failure, and -1 when the shape is one this
+// unit does not take (the caller then uses the CUDA-core kernel).
+//   A [M,K], W [N,K] bf16 row-major; C [M,N] bf16 (out_f32 == 0) or float32.
+//   workspace: float32 scratch of workspace_floats elements for split-K partials (a product is
+//   only split when splits * M * N fits); counters: siar_gemm_tc_max_tiles() int32 zeros (left zero
+//   on return).
+extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
+                                 float* workspace, long long workspace_floats, int* counters, int* status,
+                                 int sm_count, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || K < 8) return -1;                       // TMA needs 16-byte row strides
+  if (((uintptr_t)A | (uintptr_t)W) & 15) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool swap = M <= 128;
+  const void* X = swap ? W : A;
+  const void* Y = swap ? A : W;
+  const int P = swap ? N : M, Q = swap ? M : N;
+  int BN;
+  if (swap) BN = Q <= 16 ? 16 : Q <= 32 ? 32 : Q <= 64 ? 64 : 128;
+  else BN = Q >= 256 ? 256 : 128;
+  CUtensorMap tmX, tmY;
+  if (!tensor_map(X, P, K, kBM, &tmX) || !tensor_map(Y, Q, K, BN, &tmY)) return -1;
+
+  const int tiles = ((P + kBM - 1) / kBM) * ((Q + BN - 1) / BN);
+  const int num_kb = (K + kBK - 1) / kBK;
+  int splits = 1;
+  if (swap && workspace && counters && tiles < sm_count && tiles <= siar_gemm_tc_max_tiles()) {
+    splits = (sm_count + tiles - 1) / tiles;
+    if (splits > 8) splits = 8;
+    if (splits > num_kb / 4) splits = num_kb / 4;
+    while (splits > 1 && (long long)splits * M * N > workspace_floats) --splits;
+    if (splits < 1) splits = 1;
+  }
+  int kbps = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kbps - 1) / kbps;
+
+  GemmParams prm;
+  prm.C = C;
+  prm.partial = splits > 1 ? workspace : nullptr;
+  prm.counters = counters;
+  prm.status = status;
+  prm.P = P; prm.Q = Q; prm.K = K;
+  prm.ldc = N;
+  prm.transpose_out = swap ? 1 : 0;
+  prm.kb_per_split = kbps;
+  prm.plane = (long long)M * N;
+
+#define SIAR_GO(BN_, ST_)                                                                      \
+  return out_f32 ? launch<BN_, ST_, float>(tmX, tmY, prm, splits, s)                           \
+                 : launch<BN_, ST_, __nv_bfloat16>(tmX, tmY, prm, splits, s)
+  switch (BN) {
+    case 16: SIAR_GO(16, 5);
+    case 32: SIAR_GO(32, 5);
+    case 64: SIAR_GO(64, 4);
+    case 128: SIAR_GO(128, 3);
+    default: SIAR_GO(256, 4);
+  }
+#undef SIAR_GO
+}

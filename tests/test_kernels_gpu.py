@@ -311,3 +311,51 @@ def test_sample_same_request_same_draw_in_any_batch():
     alone = sample_case(logits[2:3], [0.8], [0], [1.0], [42], [3])[0]
     batch = sample_case(logits, [0.8] * 5, [0] * 5, [1.0] * 5, [1, 2, 42, 4, 5], [0, 0, 3, 0, 0])
     assert batch[2] == alone
+
+
+# ----------------------------------------------------------------------------- tensor-core products
+@pytest.mark.parametrize("m,n,k", [
+    (1, 128, 64), (1, 4096, 4096), (8, 6144, 4096), (8, 512, 14336), (16, 130, 264), (17, 256, 128),
+    (33, 1000, 72), (64, 4096, 1024), (65, 384, 512), (128, 256, 256), (129, 256, 256), (200, 331, 96),
+    (300, 520, 4096), (1024, 768, 512), (5, 40, 8), (2048, 256, 128),
+])
+def test_tensor_core_linear(m, n, k):
+    from simple_inference_autoresearch_b200.kernels import gemm_tc
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.1)
+    ref = x.double() @ w.double().T
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+        assert gemm_tc.try_linear(x.to(DEV), w.to(DEV), out), "shape refused"
+        ops.check_status(DEV)
+        got = out.cpu().double()
+        assert not torch.isnan(got).any()
+        bound = 1e-5 * k ** 0.5 + (0 if out_dtype == torch.float32 else 8e-3 * ref.abs().max().item())
+        assert (got - ref).abs().max().item() <= bound + 1e-4, (m, n, k, out_dtype)
+    # the CUDA-core kernel gives the same numbers beyond rounding
+    gemm_tc.enabled = False
+    try:
+        simt = ops.linear(x.to(DEV), w.to(DEV), torch.float32).cpu()
+    finally:
+        gemm_tc.enabled = True
+    tc = ops.linear(x.to(DEV), w.to(DEV), torch.float32).cpu()
+    torch.testing.assert_close(tc, simt, rtol=1e-4, atol=1e-4)
+
+
+def test_tensor_core_linear_refuses_unaligned_k():
+    from simple_inference_autoresearch_b200.kernels import gemm_tc
+    x, w = rnd(4, 20, dtype=torch.bfloat16).to(DEV), rnd(8, 20, dtype=torch.bfloat16).to(DEV)
+    out = torch.empty(4, 8, dtype=torch.float32, device=DEV)
+    assert gemm_tc.try_linear(x, w, out) is False
+    torch.testing.assert_close(ops.linear(x, w, torch.float32).cpu(), emu.linear(x.cpu(), w.cpu(), torch.float32),
+                               rtol=1e-4, atol=1e-4)
+
+
+def test_tensor_core_rows_do_not_depend_on_batch_within_an_orientation():
+    from simple_inference_autoresearch_b200.kernels import gemm_tc
+    w = rnd(512, 1024, dtype=torch.bfloat16, seed=2, scale=0.1).to(DEV)
+    x = rnd(64, 1024, dtype=torch.bfloat16, seed=1).to(DEV)
+    whole = ops.linear(x, w, torch.float32)
+    for rows in (1, 8, 17):
+        part = ops.linear(x[:rows].contiguous(), w, torch.float32)
+        assert torch.equal(part, whole[:rows])
