@@ -1,0 +1,483 @@
+// bfloat16 causal grouped-query attention over the paged cache on the tensor cores
+// (warp-level m16n8k16 MMA, float32 accumulation and float32 softmax state).  Same
+// rules as the CUDA-core kernels in attention.cu, which stay the 32-bit path and the
+// path for head sizes other than 64 and 128 (the formulas and their places in the
+// reference are cited there).  As in the reference's flash kernel, P is rounded to
+// bfloat16 before the P.V product (kernels/attention_kernel.py:221).
+//
+// The G query heads that share a kv head are packed on the MMA's row axis, so keys
+// and values are read once per kv head, not once per query head:
+//   * prefill: rows of one (sequence, kv head) are (query position, head in group)
+//     pairs; a block takes 64 consecutive rows (16 per warp) and walks the keys in
+//     tiles of 64 = one cache page, double-buffered with cp.async.
+//   * decode: one new token, so the G heads are the only rows (padded to 16); a
+//     block takes a chunk of 128 keys (32 per warp), joins its warps' partial
+//     softmax states in shared memory and writes one partial per chunk to scratch;
+//     the combine kernel of attention.cu's scheme joins the chunks in order.
+// Key tiles start at multiples of the tile size, so a row's reduction order depends
+// on its position only.
+#include "attention_mma.cuh"
+
+#include <math.h>
+
+namespace siar {
+
+constexpr int kPad = 8;             // bf16 elements of padding per shared-memory row (16 bytes)
+constexpr int kMmaDecodeChunk = 128;
+constexpr int kMmaPrefillRows = 64;
+constexpr int kMmaKeyTile = 64;
+
+// ------------------------------------------------------------------ decode
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ k_pool,
+                       const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_table,
+                       const int* __restrict__ slot_ids, const int* __restrict__ q_start,
+                       const int* __restrict__ base_len, float* __restrict__ part_ml, float* __restrict__ part_acc,
+                       int Hq, int Hkv, int page_tokens, int max_pages, int max_chunks, float scale) {
+  constexpr int RS = D + kPad;                 // row stride in elements
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [4][32][RS]
+  __nv_bfloat16* v_s = k_s + 4 * 32 * RS;                           // [4][32][RS]
+
+  const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int kv_len = base_len[b] + 1;
+  const int c0 = c * kMmaDecodeChunk;
+  if (c0 >= kv_len) return;
+  const int slot = slot_ids[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int w0 = c0 + warp * 32;                  // first key of this warp
+  const int valid = min(32, kv_len - w0);         // keys of this warp that exist (may be <= 0)
+
+  __nv_bfloat16* kw = k_s + warp * 32 * RS;
+  __nv_bfloat16* vw = v_s + warp * 32 * RS;
+  if (valid > 0) {
+    const int page = block_table[(size_t)slot * max_pages + w0 / page_tokens];
+    const size_t row0 = ((size_t)page * Hkv + kvh) * page_tokens + (w0 % page_tokens);
+    const __nv_bfloat16* kg = k_pool + row0 * D;
+    const __nv_bfloat16* vg = v_pool + row0 * D;
+    constexpr int CPR = D / 8;                    // 16-byte chunks per row
+#pragma unroll
+    for (int it = 0; it < 32 * CPR / 32; ++it) {
+      const int id = it * 32 + lane;
+      const int r = id / CPR, ch = id % CPR;
+      const int ok = r < valid ? 16 : 0;
+      const size_t goff = (size_t)(ok ? r : 0) * D + ch * 8;
+      cp_async_16(smem_u32_generic(kw + r * RS + ch * 8), kg + goff, ok);
+      cp_async_16(smem_u32_generic(vw + r * RS + ch * 8), vg + goff, ok);
+    }
+  }
+  cp_async_commit();
+
+  // query fragments straight from global memory: rows g and g + 8 of the (padded) group
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qrow = qkv + (size_t)q_start[b] * (Hq + 2 * Hkv) * D + (size_t)kvh * G * D;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int col = kk * 16 + q * 2;
+      qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
+      qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
+      qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
+      qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+  }
+  cp_async_wait<0>();
+  __syncwarp();
+
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  if (valid > 0) {
+    // S = Q K^T : 4 key tiles of 8
+    float s[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    const uint32_t kbase = smem_u32_generic(kw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; kk += 2) {
+        uint32_t bfr[4];
+        // matrices: dims 16kk + 8m .. +7 (m = 0..3) of keys 8j .. 8j+7
+        ldmatrix_x4(bfr, kbase + (uint32_t)(((8 * j + (lane & 7)) * RS + 16 * kk + 8 * (lane >> 3)) * 2));
+        mma_bf16_16816(s[j], qa[kk], bfr[0], bfr[1]);
+        mma_bf16_16816(s[j], qa[kk + 1], bfr[2], bfr[3]);
+      }
+    }
+    // mask, row maxima, exponentials
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = 8 * j + 2 * q + (e & 1);
+        const float v = key < valid ? s[j][e] * scale : -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    mx[0] = quad_max(mx[0]);
+    mx[1] = quad_max(mx[1]);
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - mx[e >> 1]);
+        s[j][e] = p;
+        sum[e >> 1] += p;
+      }
+    }
+    m_row[0] = mx[0]; m_row[1] = mx[1];
+    l_row[0] = quad_sum(sum[0]); l_row[1] = quad_sum(sum[1]);
+    // O = P V : 2 key steps of 16, D/8 dim tiles
+    const uint32_t vbase = smem_u32_generic(vw);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      uint32_t pa[4] = {pack_bf16(s[2 * t][0], s[2 * t][1]), pack_bf16(s[2 * t][2], s[2 * t][3]),
+                        pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]), pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3])};
+#pragma unroll
+      for (int j = 0; j < D / 8; j += 2) {
+        uint32_t bfr[4];
+        // matrices: (keys 16t + 8(m%2) .. +7, dims 8j + 8(m/2) .. +7), transposed on load
+        const int mi = lane >> 3;
+        ldmatrix_x4_trans(bfr, vbase + (uint32_t)(((16 * t + 8 * (mi & 1) + (lane & 7)) * RS + 8 * j + 8 * (mi >> 1)) * 2));
+        mma_bf16_16816(o[j], pa, bfr[0], bfr[1]);
+        mma_bf16_16816(o[j + 1], pa, bfr[2], bfr[3]);
+      }
+    }
+  }
+
+  // join the four warps: reuse the tile memory as float buffers
+  __syncthreads();
+  float* mo = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
+  float* mm = mo + 4 * 16 * D;                                // [4][16]
+  float* ml = mm + 4 * 16;                                    // [4][16]
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    const int d = 8 * j + 2 * q;
+    if (g < G) { mo[(warp * 16 + g) * D + d] = o[j][0]; mo[(warp * 16 + g) * D + d + 1] = o[j][1]; }
+    if (g + 8 < G) { mo[(warp * 16 + g + 8) * D + d] = o[j][2]; mo[(warp * 16 + g + 8) * D + d + 1] = o[j][3]; }
+  }
+  if (q == 0) {
+    mm[warp * 16 + g] = m_row[0]; ml[warp * 16 + g] = l_row[0];
+    mm[warp * 16 + g + 8] = m_row[1]; ml[warp * 16 + g + 8] = l_row[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int h = idx / D, d = idx % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mm[w * 16 + h]);
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mm[w * 16 + h];
+      if (mw != -INFINITY) {
+        const float f = expf(mw - mx);
+        acc += mo[(w * 16 + h) * D + d] * f;
+        lsum += ml[w * 16 + h] * f;
+      }
+    }
+    const size_t pidx = ((size_t)b * Hq + kvh * G + h) * max_chunks + c;
+    part_acc[pidx * D + d] = acc;
+    if (d == 0) { part_ml[pidx * 2] = mx; part_ml[pidx * 2 + 1] = lsum; }
+  }
+}
+
+// grid (Hq, B): joins the chunks' partials in chunk order.
+__global__ void attn_decode_mma_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
+                                               const int* __restrict__ q_start, const int* __restrict__ base_len,
+                                               __nv_bfloat16* __restrict__ out, int Hq, int D, int max_chunks) {
+  const int hq = blockIdx.x, b = blockIdx.y;
+  const int kv_len = base_len[b] + 1;
+  const int n_chunks = (kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+  const size_t p0 = ((size_t)b * Hq + hq) * max_chunks;
+  float mx = -INFINITY;
+  for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, part_ml[(p0 + c) * 2]);
+  float lsum = 0.f;
+  for (int c = 0; c < n_chunks; ++c) lsum += part_ml[(p0 + c) * 2 + 1] * expf(part_ml[(p0 + c) * 2] - mx);
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  __nv_bfloat16* o = out + (size_t)q_start[b] * Hq * D + (size_t)hq * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f;
+    for (int c = 0; c < n_chunks; ++c) a += part_acc[(p0 + c) * D + d] * expf(part_ml[(p0 + c) * 2] - mx);
+    o[d] = __float2bfloat16_rn(a * inv);
+  }
+}
+
+// ------------------------------------------------------------------ prefill
+// grid (row tiles, Hkv, B), 128 threads.  Shared memory (bf16):
+//   q_s[64][D+8], k_s[2][64][D+8], v_s[2][64][D+8].
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_table,
+                        const int* __restrict__ slot_ids, const int* __restrict__ q_start,
+                        const int* __restrict__ base_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
+                        int page_tokens, int max_pages, float scale) {
+  constexpr int RS = D + kPad;
+  constexpr int CPR = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* k_s = q_s + kMmaPrefillRows * RS;
+  __nv_bfloat16* v_s = k_s + 2 * kMmaKeyTile * RS;
+
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int G = Hq / Hkv;
+  const int t0 = q_start[b];
+  const int q_len = q_start[b + 1] - t0;
+  const int rows_total = q_len * G;
+  const int row0 = blockIdx.x * kMmaPrefillRows;
+  if (row0 >= rows_total) return;
+  const int rows_here = min(kMmaPrefillRows, rows_total - row0);
+  const int base = base_len[b];
+  const int slot = slot_ids[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int qkv_stride = (Hq + 2 * Hkv) * D;
+  const int block_kv_end = base + (row0 + rows_here - 1) / G + 1;
+  const int n_tiles = (block_kv_end + kMmaKeyTile - 1) / kMmaKeyTile;
+
+  // ---- stage the query rows
+  for (int id = threadIdx.x; id < kMmaPrefillRows * CPR; id += blockDim.x) {
+    const int r = id / CPR, ch = id % CPR;
+    const int ok = r < rows_here ? 16 : 0;
+    const int rr = ok ? row0 + r : row0;
+    const __nv_bfloat16* src = qkv + (size_t)(t0 + rr / G) * qkv_stride + (size_t)(kvh * G + rr % G) * D + ch * 8;
+    cp_async_16(smem_u32_generic(q_s + r * RS + ch * 8), src, ok);
+  }
+  auto load_tile = [&](int tile, int stage) {
+    const int j0 = tile * kMmaKeyTile;
+    const int valid = min(kMmaKeyTile, block_kv_end - j0);
+    const int page = block_table[(size_t)slot * max_pages + j0 / page_tokens];
+    const size_t grow = ((size_t)page * Hkv + kvh) * page_tokens + (j0 % page_tokens);
+    const __nv_bfloat16* kg = k_pool + grow * D;
+    const __nv_bfloat16* vg = v_pool + grow * D;
+    __nv_bfloat16* ks = k_s + stage * kMmaKeyTile * RS;
+    __nv_bfloat16* vs = v_s + stage * kMmaKeyTile * RS;
+    for (int id = threadIdx.x; id < kMmaKeyTile * CPR; id += blockDim.x) {
+      const int r = id / CPR, ch = id % CPR;
+      const int ok = r < valid ? 16 : 0;
+      const size_t goff = (size_t)(ok ? r : 0) * D + ch * 8;
+      cp_async_16(smem_u32_generic(ks + r * RS + ch * 8), kg + goff, ok);
+      cp_async_16(smem_u32_generic(vs + r * RS + ch * 8), vg + goff, ok);
+    }
+  };
+  load_tile(0, 0);
+  cp_async_commit();
+
+  // rows of this thread: warp*16 + g and + 8
+  int kv_end[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    kv_end[h] = r < rows_here ? base + (row0 + r) / G + 1 : 0;
+  }
+  // the furthest key any row of this warp sees (warp-uniform)
+  const int warp_last_row = min(rows_here - 1, warp * 16 + 15);
+  const int warp_kv_end = warp * 16 < rows_here ? base + (row0 + warp_last_row) / G + 1 : 0;
+
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  uint32_t qa[D / 16][4];
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int stage = tile & 1;
+    if (tile + 1 < n_tiles) load_tile(tile + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (tile == 0) {
+      const uint32_t qbase = smem_u32_generic(q_s + warp * 16 * RS);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qa[kk], qbase + (uint32_t)((((lane & 7) + 8 * ((lane >> 3) & 1)) * RS + 16 * kk + 8 * (lane >> 4)) * 2));
+    }
+    const int j0 = tile * kMmaKeyTile;
+    if (j0 < warp_kv_end) {
+      float s[kMmaKeyTile / 8][4];
+#pragma unroll
+      for (int j = 0; j < kMmaKeyTile / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      const uint32_t kbase = smem_u32_generic(k_s + stage * kMmaKeyTile * RS);
+#pragma unroll
+      for (int j = 0; j < kMmaKeyTile / 8; ++j) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; kk += 2) {
+          uint32_t bfr[4];
+          ldmatrix_x4(bfr, kbase + (uint32_t)(((8 * j + (lane & 7)) * RS + 16 * kk + 8 * (lane >> 3)) * 2));
+          mma_bf16_16816(s[j], qa[kk], bfr[0], bfr[1]);
+          mma_bf16_16816(s[j], qa[kk + 1], bfr[2], bfr[3]);
+        }
+      }
+      float mx[2] = {m_row[0], m_row[1]};
+#pragma unroll
+      for (int j = 0; j < kMmaKeyTile / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = j0 + 8 * j + 2 * q + (e & 1);
+          const float v = key < kv_end[e >> 1] ? s[j][e] * scale : -INFINITY;
+          s[j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      mx[0] = quad_max(mx[0]);
+      mx[1] = quad_max(mx[1]);
+      float alpha[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) alpha[h] = mx[h] == -INFINITY ? 1.f : expf(m_row[h] - mx[h]);
+#pragma unroll
+      for (int j = 0; j < kMmaKeyTile / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - mx[e >> 1]);
+          s[j][e] = p;
+          sum[e >> 1] += p;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        l_row[h] = l_row[h] * alpha[h] + quad_sum(sum[h]);
+        m_row[h] = mx[h];
+      }
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+        o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+      }
+      const uint32_t vbase = smem_u32_generic(v_s + stage * kMmaKeyTile * RS);
+#pragma unroll
+      for (int t = 0; t < kMmaKeyTile / 16; ++t) {
+        uint32_t pa[4] = {pack_bf16(s[2 * t][0], s[2 * t][1]), pack_bf16(s[2 * t][2], s[2 * t][3]),
+                          pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]), pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3])};
+#pragma unroll
+        for (int j = 0; j < D / 8; j += 2) {
+          uint32_t bfr[4];
+          const int mi = lane >> 3;
+          ldmatrix_x4_trans(bfr, vbase + (uint32_t)(((16 * t + 8 * (mi & 1) + (lane & 7)) * RS + 8 * j + 8 * (mi >> 1)) * 2));
+          mma_bf16_16816(o[j], pa, bfr[0], bfr[1]);
+          mma_bf16_16816(o[j + 1], pa, bfr[2], bfr[3]);
+        }
+      }
+    }
+    __syncthreads();   // everyone is done with this stage before it is refilled
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    if (r >= rows_here) continue;
+    const int rr = row0 + r;
+    const float inv = l_row[h] > 0.f ? 1.f / l_row[h] : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(t0 + rr / G) * Hq * D + (size_t)(kvh * G + rr % G) * D;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      const int d = 8 * j + 2 * q;
+      *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+    }
+  }
+}
+
+template <int D>
+static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
+                         const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
+                         int B, int Hq, int Hkv, int page_tokens, int max_pages, int max_kv_len, float scale,
+                         cudaStream_t s) {
+  const int max_chunks = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+  float* part_ml = scratch;
+  float* part_acc = scratch + (size_t)B * Hq * max_chunks * 2;
+  size_t smem = (size_t)2 * 4 * 32 * (D + kPad) * 2;
+  const size_t merge = sizeof(float) * (4 * 16 * D + 2 * 4 * 16);
+  if (merge > smem) smem = merge;
+  auto kern = attn_decode_mma_kernel<D>;
+  static bool attr = false;
+  if (!attr && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  dim3 grid(max_chunks, Hkv, B);
+  kern<<<grid, 128, smem, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                               block_table, slot_ids, q_start, base_len, part_ml, part_acc, Hq, Hkv, page_tokens,
+                               max_pages, max_chunks, scale);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  attn_decode_mma_combine_kernel<<<dim3(Hq, B), 128, 0, s>>>(part_ml, part_acc, q_start, base_len,
+                                                             (__nv_bfloat16*)out, Hq, D, max_chunks);
+  return (int)cudaGetLastError();
+}
+
+template <int D>
+static int launch_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
+                          const int* slot_ids, const int* q_start, const int* base_len, void* out, int B, int Hq,
+                          int Hkv, int page_tokens, int max_pages, int max_q_len, float scale, cudaStream_t s) {
+  const int G = Hq / Hkv;
+  const size_t smem = (size_t)(kMmaPrefillRows + 4 * kMmaKeyTile) * (D + kPad) * 2;
+  auto kern = attn_prefill_mma_kernel<D>;
+  static bool attr = false;
+  if (!attr && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  dim3 grid((max_q_len * G + kMmaPrefillRows - 1) / kMmaPrefillRows, Hkv, B);
+  kern<<<grid, 128, smem, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                               block_table, slot_ids, q_start, base_len, (__nv_bfloat16*)out, Hq, Hkv, page_tokens,
+                               max_pages, scale);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace siar
+
+using namespace siar;
+
+extern "C" int siar_attn_mma_decode_chunk() { return kMmaDecodeChunk; }
+
+// 1 when the tensor-core kernels take these sizes (bf16 only): head_dim 64 or 128, at most
+// 16 query heads per kv head, pages that hold whole key tiles.
+extern "C" int siar_attn_mma_supported(int Hq, int Hkv, int D, int page_tokens) {
+  if (Hkv <= 0 || Hq % Hkv != 0) return 0;
+  return (D == 64 || D == 128) && (Hq / Hkv) <= 16 && page_tokens % kMmaKeyTile == 0;
+}
+
+extern "C" long long siar_attn_mma_decode_scratch_floats(int B, int Hq, int D, int max_kv_len) {
+  const long long chunks = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+  return (long long)B * Hq * chunks * (D + 2);
+}
+
+extern "C" int siar_attn_mma_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
+                                    const int* slot_ids, const int* q_start, const int* base_len, void* out,
+                                    float* scratch, int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
+                                    int max_kv_len, float scale, void* stream) {
+  if (B == 0) return 0;
+  if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 64)
+    return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, B, Hq,
+                             Hkv, page_tokens, max_pages, max_kv_len, scale, s);
+  return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, B, Hq, Hkv,
+                            page_tokens, max_pages, max_kv_len, scale, s);
+}
+
+extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
+                                     const int* slot_ids, const int* q_start, const int* base_len, void* out, int B,
+                                     int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_q_len,
+                                     float scale, void* stream) {
+  if (B == 0 || max_q_len == 0) return 0;
+  if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535)
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 64)
+    return launch_prefill<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv,
+                              page_tokens, max_pages, max_q_len, scale, s);
+  return launch_prefill<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv,
+                             page_tokens, max_pages, max_q_len, scale, s);
+}

@@ -131,8 +131,8 @@ class DecoderModel:
             units.append("gemm_tc")
         for layer in self.layers:
             units += list(layer.extension_units())
-        if self.dtype != torch.bfloat16:
-            units = [u for u in units if u != "gemm_tc"]
+        if self.dtype != torch.bfloat16:   # the tensor-core units are bfloat16 only
+            units = [u for u in units if u not in ("gemm_tc", "attention_mma")]
         return sorted(set(units))
 
     def weight_bytes(self) -> int:

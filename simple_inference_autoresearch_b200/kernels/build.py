@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 ]
 
 #: every unit of the library, in the order ``build_all`` compiles them
-ALL_UNITS = ("elementwise", "gemm_simt", "attention", "sampling", "gemm_tc")
+ALL_UNITS = ("elementwise", "gemm_simt", "attention", "attention_mma", "sampling", "gemm_tc")
 
 
 class ExtensionError(RuntimeError):

@@ -47,6 +47,14 @@ _signatures = {
         "siar_attn_decode_chunk": [],
         "siar_attn_max_head_dim": [],
     },
+    "attention_mma": {
+        "siar_attn_mma_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "siar_attn_mma_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
+        "siar_attn_mma_decode_chunk": [],
+    },
     "sampling": {
         "siar_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p],
@@ -220,30 +228,51 @@ def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         raise ValueError(f"num heads {n_heads} is not a multiple of kv heads {n_kv_heads}")
 
 
-def decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int) -> int:
-    chunk = attention_limits()["decode_chunk"]
+#: set to False to force the CUDA-core attention kernels on the bfloat16 path (tests compare both)
+use_mma_attention = True
+
+
+def mma_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
+    if dtype != torch.bfloat16 or not use_mma_attention:
+        return False
+    return bool(_fn("attention_mma", "siar_attn_mma_supported")(n_heads, n_kv_heads, head_dim, page_tokens))
+
+
+def decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int, chunk: int) -> int:
     chunks = (max_kv_len + chunk - 1) // chunk
     return n_seqs * n_heads * chunks * (head_dim + 2)
 
 
 def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
     """Causal attention of the new tokens' (already rotated) queries over the
-    cache entry ``kv``; returns [N, n_heads * head_dim] in qkv's dtype."""
+    cache entry ``kv``; returns [N, n_heads * head_dim] in qkv's dtype.  bfloat16
+    with head_dim 64 or 128 runs on the tensor cores, everything else on the CUDA cores."""
     _need_cuda(qkv, kv.k)
     check_attention_sizes(n_heads, n_kv_heads, head_dim)
     n = qkv.shape[0]
     out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     common = (_ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len))
+    sizes = (meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1])
+    mma = mma_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens)
     if meta.is_decode:
-        scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len),
+        if mma:
+            chunk = _fn("attention_mma", "siar_attn_mma_decode_chunk")()
+        else:
+            chunk = attention_limits()["decode_chunk"]
+        scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len, chunk),
                               dtype=torch.float32, device=qkv.device)
-        _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
-                _ptr(out), _ptr(scratch), meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens,
-                kv.block_table.shape[1], meta.max_kv_len, float(scale), _stream(), kernels=2)
+        if mma:
+            _launch("attention_mma", "siar_attn_mma_decode", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
+                    _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)
+        else:
+            _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
+                    _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)
+    elif mma:
+        _launch("attention_mma", "siar_attn_mma_prefill", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
+                *sizes, meta.max_q_len, float(scale), _stream())
     else:
         _launch("attention", "siar_attn_prefill", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
-                _ptr(out), meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1],
-                meta.max_q_len, float(scale), _stream())
+                _ptr(out), *sizes, meta.max_q_len, float(scale), _stream())
     return out
 
 

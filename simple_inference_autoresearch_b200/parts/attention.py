@@ -55,7 +55,7 @@ class GroupedQueryAttention(Mixer):
         return KVNeed(self.n_kv_heads, self.head_dim)
 
     def extension_units(self):
-        return ("elementwise", "attention", "gemm_simt", "gemm_tc")
+        return ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
 
     def forward(self, ctx, x: torch.Tensor, cache_entry, writes_cache: bool = True) -> torch.Tensor:
         qkv = ops.linear(x, self.w_qkv, ctx.dtype)

@@ -359,3 +359,44 @@ def test_tensor_core_rows_do_not_depend_on_batch_within_an_orientation():
     for rows in (1, 8, 17):
         part = ops.linear(x[:rows].contiguous(), w, torch.float32)
         assert torch.equal(part, whole[:rows])
+
+
+# ----------------------------------------------------------------------------- tensor-core attention
+@pytest.mark.parametrize("hq,hkv,d", [(6, 2, 128), (16, 1, 64), (4, 4, 128), (32, 8, 128), (8, 4, 64)])
+def test_mma_attention_decode_groups_and_lengths(hq, hkv, d):
+    assert ops.mma_attention_takes(torch.bfloat16, hq, hkv, d, 64)
+    run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 31, 127, 128, 129, 1000], q_lens=[1] * 6)
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(6, 2, 128), (16, 1, 64), (4, 4, 128), (32, 8, 128), (8, 4, 64)])
+def test_mma_attention_prefill_groups_and_lengths(hq, hkv, d):
+    run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0, 300, 63], q_lens=[1, 200, 150, 66])
+
+
+def test_mma_and_cuda_core_attention_agree():
+    for lens_before, q_lens in (([500, 64], [1, 1]), ([100, 0], [90, 130])):
+        a = run_attention_case(torch.bfloat16, 8, 2, 128, lens_before, q_lens)[DEV][0]
+        ops.use_mma_attention = False
+        try:
+            b = run_attention_case(torch.bfloat16, 8, 2, 128, lens_before, q_lens)[DEV][0]
+        finally:
+            ops.use_mma_attention = True
+        torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
+
+
+def test_mma_attention_is_refused_where_it_does_not_apply():
+    assert not ops.mma_attention_takes(torch.float32, 8, 2, 128, 64)
+    assert not ops.mma_attention_takes(torch.bfloat16, 8, 2, 48, 64)
+    assert not ops.mma_attention_takes(torch.bfloat16, 32, 1, 128, 64)     # 32 heads on one kv head
+    assert not ops.mma_attention_takes(torch.bfloat16, 8, 2, 128, 32)      # pages smaller than a key tile
+
+
+def test_mma_attention_far_key_and_rows_do_not_depend_on_batch():
+    hq, hkv, d = 8, 2, 128
+    outs = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[700], q_lens=[1], boost=(0, 200, 8.0))
+    v_row = rnd(700, (hq + 2 * hkv) * d, dtype=torch.bfloat16, seed=10)[200, (hq + hkv) * d:(hq + hkv + 1) * d].float()
+    torch.testing.assert_close(outs[DEV][0][0, :d], v_row, rtol=5e-2, atol=5e-2)
+    # the same sequence alone and beside others: identical rows
+    alone = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0], q_lens=[150])[DEV][0]
+    both = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0], q_lens=[150, 77])[DEV][0]
+    assert torch.equal(alone, both[:150])
