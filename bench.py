@@ -98,6 +98,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--cuda-profiler-range", action="store_true",
+                    help="bracket the timed decode replays with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -184,11 +186,15 @@ def main() -> int:
         before = ops.launch_count
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        if args.cuda_profiler_range and e2e:
+            torch.cuda.profiler.start()
         e0.record()
         for _ in range(steps):
             graph.replay()
         e1.record()
         torch.cuda.synchronize()
+        if args.cuda_profiler_range and e2e:
+            torch.cuda.profiler.stop()
         dev_ms = e0.elapsed_time(e1) / steps
         launches = ops.launch_count - before
         kv_mid = PROMPT_TOKENS + warmup + steps / 2

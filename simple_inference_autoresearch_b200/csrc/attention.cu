@@ -51,6 +51,8 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pool, con
                     const int* __restrict__ block_table, const int* __restrict__ slot_ids,
                     const int* __restrict__ q_start, const int* __restrict__ base_len, T* __restrict__ out,
                     int Hq, int Hkv, int D, int page_tokens, int max_pages, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = Hq / Hkv;
@@ -161,6 +163,8 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
                            const int* __restrict__ q_start, const int* __restrict__ base_len,
                            float* __restrict__ part_ml, float* __restrict__ part_acc, int Hq, int Hkv, int D,
                            int page_tokens, int max_pages, int max_chunks, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
@@ -271,6 +275,8 @@ template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
                                            const int* __restrict__ q_start, const int* __restrict__ base_len,
                                            T* __restrict__ out, int Hq, int D, int max_chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int hq = blockIdx.x, b = blockIdx.y;
   const int kv_len = base_len[b] + 1;
   const int n_chunks = (kv_len + kDecodeChunk - 1) / kDecodeChunk;
@@ -309,7 +315,7 @@ static int launch_prefill(const void* qkv, const void* k_pool, const void* v_poo
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((max_q_len * G + kPrefillRows - 1) / kPrefillRows, Hkv, B);
-  kern<<<grid, kPrefillWarps * 32, smem, s>>>((const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
+  launch_kernel(kern, grid, kPrefillWarps * 32, smem, s, (const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
                                               slot_ids, q_start, base_len, (T*)out, Hq, Hkv, D, page_tokens,
                                               max_pages, scale);
   return (int)cudaGetLastError();
@@ -318,6 +324,8 @@ static int launch_prefill(const void* qkv, const void* k_pool, const void* v_poo
 }  // namespace siar
 
 using namespace siar;
+
+SIAR_DEFINE_PDL_SWITCH()
 
 extern "C" int siar_attn_decode_chunk() { return kDecodeChunk; }
 
@@ -373,13 +381,13 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(max_chunks, Hkv, B);
-  kern<<<grid, kDecodeWarps * 32, smem, s>>>((const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
+  launch_kernel(kern, grid, kDecodeWarps * 32, smem, s, (const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
                                              slot_ids, q_start, base_len, part_ml, part_acc, Hq, Hkv, D,
                                              page_tokens, max_pages, max_chunks, scale);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   dim3 grid2(Hq, B);
-  attn_decode_combine_kernel<T><<<grid2, 128, 0, s>>>(part_ml, part_acc, q_start, base_len, (T*)out, Hq, D,
+  launch_kernel(attn_decode_combine_kernel<T>, grid2, 128, 0, s, part_ml, part_acc, q_start, base_len, (T*)out, Hq, D,
                                                       max_chunks);
   return (int)cudaGetLastError();
 }

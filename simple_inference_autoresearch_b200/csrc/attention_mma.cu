@@ -13,7 +13,8 @@
 //   * decode: one new token, so the G heads are the only rows (padded to 16); a
 //     block takes a chunk of 128 keys (32 per warp), joins its warps' partial
 //     softmax states in shared memory and writes one partial per chunk to scratch;
-//     the combine kernel of attention.cu's scheme joins the chunks in order.
+//     the block of a (sequence, kv head) that finishes last joins the chunks in chunk
+//     order.  A sequence of at most one chunk is finished by its only block.
 // Key tiles start at multiples of the tile size, so a row's reduction order depends
 // on its position only.
 #include "attention_mma.cuh"
@@ -34,8 +35,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_table,
                        const int* __restrict__ slot_ids, const int* __restrict__ q_start,
                        const int* __restrict__ base_len, float* __restrict__ part_ml, float* __restrict__ part_acc,
-                       int Hq, int Hkv, int page_tokens, int max_pages, int max_chunks, float scale) {
+                       int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int page_tokens,
+                       int max_pages, int max_chunks, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int RS = D + kPad;                 // row stride in elements
+  __shared__ int is_last;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [4][32][RS]
   __nv_bfloat16* v_s = k_s + 4 * 32 * RS;                           // [4][32][RS]
@@ -169,6 +174,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     mm[warp * 16 + g + 8] = m_row[1]; ml[warp * 16 + g + 8] = l_row[1];
   }
   __syncthreads();
+  const int n_chunks = (kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+  __nv_bfloat16* orow = out + (size_t)q_start[b] * Hq * D + (size_t)kvh * G * D;
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int h = idx / D, d = idx % D;
     float mx = -INFINITY;
@@ -184,30 +191,40 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
         lsum += ml[w * 16 + h] * f;
       }
     }
-    const size_t pidx = ((size_t)b * Hq + kvh * G + h) * max_chunks + c;
-    part_acc[pidx * D + d] = acc;
-    if (d == 0) { part_ml[pidx * 2] = mx; part_ml[pidx * 2 + 1] = lsum; }
+    if (n_chunks == 1) {                       // the only chunk: finish here, no scratch
+      orow[h * D + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    } else {
+      const size_t pidx = ((size_t)b * Hq + kvh * G + h) * max_chunks + c;
+      part_acc[pidx * D + d] = acc;
+      if (d == 0) { part_ml[pidx * 2] = mx; part_ml[pidx * 2 + 1] = lsum; }
+    }
   }
-}
+  if (n_chunks == 1) return;
 
-// grid (Hq, B): joins the chunks' partials in chunk order.
-__global__ void attn_decode_mma_combine_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
-                                               const int* __restrict__ q_start, const int* __restrict__ base_len,
-                                               __nv_bfloat16* __restrict__ out, int Hq, int D, int max_chunks) {
-  const int hq = blockIdx.x, b = blockIdx.y;
-  const int kv_len = base_len[b] + 1;
-  const int n_chunks = (kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
-  const size_t p0 = ((size_t)b * Hq + hq) * max_chunks;
-  float mx = -INFINITY;
-  for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, part_ml[(p0 + c) * 2]);
-  float lsum = 0.f;
-  for (int c = 0; c < n_chunks; ++c) lsum += part_ml[(p0 + c) * 2 + 1] * expf(part_ml[(p0 + c) * 2] - mx);
-  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-  __nv_bfloat16* o = out + (size_t)q_start[b] * Hq * D + (size_t)hq * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float a = 0.f;
-    for (int c = 0; c < n_chunks; ++c) a += part_acc[(p0 + c) * D + d] * expf(part_ml[(p0 + c) * 2] - mx);
-    o[d] = __float2bfloat16_rn(a * inv);
+  // The block of this (sequence, kv head) that finishes last joins the chunks' partials
+  // in chunk order (so the result does not depend on which block that was).
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(counters + b * Hkv + kvh, 1);
+    is_last = (old == n_chunks - 1);
+    if (old == n_chunks - 1) counters[b * Hkv + kvh] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int h = idx / D, d = idx % D;
+    const size_t p0 = ((size_t)b * Hq + kvh * G + h) * max_chunks;
+    float mx = -INFINITY;
+    for (int cc = 0; cc < n_chunks; ++cc) mx = fmaxf(mx, __ldcg(part_ml + (p0 + cc) * 2));
+    float lsum = 0.f, acc = 0.f;
+    for (int cc = 0; cc < n_chunks; ++cc) {
+      const float f = expf(__ldcg(part_ml + (p0 + cc) * 2) - mx);
+      lsum += __ldcg(part_ml + (p0 + cc) * 2 + 1) * f;
+      acc += __ldcg(part_acc + (p0 + cc) * D + d) * f;
+    }
+    orow[h * D + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
   }
 }
 
@@ -221,6 +238,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
                         const int* __restrict__ slot_ids, const int* __restrict__ q_start,
                         const int* __restrict__ base_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
                         int page_tokens, int max_pages, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int RS = D + kPad;
   constexpr int CPR = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -388,8 +407,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
 template <int D>
 static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                          const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
-                         int B, int Hq, int Hkv, int page_tokens, int max_pages, int max_kv_len, float scale,
-                         cudaStream_t s) {
+                         int* counters, int B, int Hq, int Hkv, int page_tokens, int max_pages, int max_kv_len,
+                         float scale, cudaStream_t s) {
   const int max_chunks = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
   float* part_ml = scratch;
   float* part_acc = scratch + (size_t)B * Hq * max_chunks * 2;
@@ -404,14 +423,9 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
     attr = true;
   }
   dim3 grid(max_chunks, Hkv, B);
-  kern<<<grid, 128, smem, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-                               block_table, slot_ids, q_start, base_len, part_ml, part_acc, Hq, Hkv, page_tokens,
-                               max_pages, max_chunks, scale);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  attn_decode_mma_combine_kernel<<<dim3(Hq, B), 128, 0, s>>>(part_ml, part_acc, q_start, base_len,
-                                                             (__nv_bfloat16*)out, Hq, D, max_chunks);
-  return (int)cudaGetLastError();
+  return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
+                            (const __nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, part_ml, part_acc,
+                            counters, (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, max_chunks, scale);
 }
 
 template <int D>
@@ -428,15 +442,16 @@ static int launch_prefill(const void* qkv, const void* k_pool, const void* v_poo
     attr = true;
   }
   dim3 grid((max_q_len * G + kMmaPrefillRows - 1) / kMmaPrefillRows, Hkv, B);
-  kern<<<grid, 128, smem, s>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-                               block_table, slot_ids, q_start, base_len, (__nv_bfloat16*)out, Hq, Hkv, page_tokens,
-                               max_pages, scale);
-  return (int)cudaGetLastError();
+  return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
+                            (const __nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len,
+                            (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, scale);
 }
 
 }  // namespace siar
 
 using namespace siar;
+
+SIAR_DEFINE_PDL_SWITCH()
 
 extern "C" int siar_attn_mma_decode_chunk() { return kMmaDecodeChunk; }
 
@@ -452,19 +467,20 @@ extern "C" long long siar_attn_mma_decode_scratch_floats(int B, int Hq, int D, i
   return (long long)B * Hq * chunks * (D + 2);
 }
 
+// counters: B * Hkv int32 zeros (left zero on return); scratch: siar_attn_mma_decode_scratch_floats floats.
 extern "C" int siar_attn_mma_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                                     const int* slot_ids, const int* q_start, const int* base_len, void* out,
-                                    float* scratch, int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
-                                    int max_kv_len, float scale, void* stream) {
+                                    float* scratch, int* counters, int B, int Hq, int Hkv, int D, int page_tokens,
+                                    int max_pages, int max_kv_len, float scale, void* stream) {
   if (B == 0) return 0;
   if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64)
-    return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, B, Hq,
-                             Hkv, page_tokens, max_pages, max_kv_len, scale, s);
-  return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, B, Hq, Hkv,
-                            page_tokens, max_pages, max_kv_len, scale, s);
+    return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters,
+                             B, Hq, Hkv, page_tokens, max_pages, max_kv_len, scale, s);
+  return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters, B,
+                            Hq, Hkv, page_tokens, max_pages, max_kv_len, scale, s);
 }
 
 extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,

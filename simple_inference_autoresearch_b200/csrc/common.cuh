@@ -73,4 +73,42 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the library is launched with the "programmatic stream serialization"
+// attribute: its blocks may become resident while the kernel before it on the stream is
+// still running, so that launch latency and the prologue (barrier set-up, tensor-memory
+// allocation, loads of weights, which no earlier kernel writes) overlap the predecessor's
+// tail.  A kernel calls pdl_launch_dependents() first (the next kernel may start its own
+// prologue) and pdl_wait() before it reads or writes anything an earlier kernel touches;
+// pdl_wait() returns once all earlier kernels have completed and their writes are visible.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool& pdl_enabled() {
+  static bool on = true;
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace siar
+
+// One switch per shared object: siar_set_pdl(0) launches every kernel of the unit
+// without the attribute (plain stream order).
+#define SIAR_DEFINE_PDL_SWITCH() \
+  extern "C" void siar_set_pdl(int on) { siar::pdl_enabled() = on != 0; }

@@ -20,6 +20,8 @@ namespace siar {
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                     float* __restrict__ out, int H, int V, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = tokens[t];
   if (id < 0 || id >= V) {
@@ -34,6 +36,8 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __r
 // ------------------------------------------------------------------ row gather
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,
                                    float* __restrict__ dst, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* s = src + (size_t)rows[r] * H;
   for (int j = threadIdx.x; j < H; j += blockDim.x) dst[(size_t)r * H + j] = s[j];
@@ -46,6 +50,8 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __r
 template <typename TOut, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                    const TW* __restrict__ weight, TOut* __restrict__ out, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
   float ss = 0.f;
@@ -69,6 +75,73 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
   }
 }
 
+// Vector form for H % 4 == 0 and H <= 4 * 4 * blockDim: the row stays in registers
+// (one read of residual and delta, one write of each output).  The sum of squares is
+// formed per thread over its own elements in index order, then by block_sum.
+template <typename TW> __device__ __forceinline__ float4 load_w4(const TW* w, int c);
+template <> __device__ __forceinline__ float4 load_w4<float>(const float* w, int c) {
+  return reinterpret_cast<const float4*>(w)[c];
+}
+template <> __device__ __forceinline__ float4 load_w4<__nv_bfloat16>(const __nv_bfloat16* w, int c) {
+  const uint2 u = reinterpret_cast<const uint2*>(w)[c];
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* o, int c, float4 v) { reinterpret_cast<float4*>(o)[c] = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* o, int c, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  reinterpret_cast<uint2*>(o)[c] = u;
+}
+
+template <typename TOut, typename TW>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+                                       const TW* __restrict__ weight, TOut* __restrict__ out, int H, float eps) {
+  pdl_launch_dependents();
+  __shared__ float scratch[32];
+  constexpr int VPT = 4;
+  const int chunks = H >> 2;
+  const size_t base = (size_t)blockIdx.x * chunks;
+  float4 w[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {           // weights are written by no kernel: load them before the wait
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) w[i] = load_w4<TW>(weight, c);
+  }
+  pdl_wait();
+  float4 r[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks) {
+      float4 v = reinterpret_cast<const float4*>(residual)[base + c];
+      if (delta != nullptr) {
+        const float4 d = reinterpret_cast<const float4*>(delta)[base + c];
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        reinterpret_cast<float4*>(residual)[base + c] = v;
+      }
+      r[i] = v;
+      ss += v.x * v.x;
+      ss += v.y * v.y;
+      ss += v.z * v.z;
+      ss += v.w * v.w;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < chunks)
+      store4(out + (size_t)blockIdx.x * H, c,
+             make_float4(r[i].x * inv * w[i].x, r[i].y * inv * w[i].y, r[i].z * inv * w[i].z, r[i].w * inv * w[i].w));
+  }
+}
+
 // ------------------------------------------------------------------ rotary + cache write
 // grid (N, Hq + 2*Hkv); one block per (token, head of the fused qkv row).
 // q heads are rotated in place, k heads are rotated into the cache, v heads are
@@ -80,6 +153,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      const int* __restrict__ q_start, const int* __restrict__ base_len,
                                      int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
                                      int n_pages, int write_kv, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;
   const int b = find_sequence(q_start, B, t);
@@ -127,6 +202,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
 // ------------------------------------------------------------------ SwiGLU
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
   if (j >= I) return;
@@ -140,6 +217,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // base_len[b] += q_start[b+1] - q_start[b]; used by the captured decode step so
 // that a replay sees the lengths the previous replay left.
 __global__ void advance_lengths_kernel(int* __restrict__ base_len, const int* __restrict__ q_start, int B) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < B) base_len[b] += q_start[b + 1] - q_start[b];
 }
@@ -148,6 +227,8 @@ __global__ void advance_lengths_kernel(int* __restrict__ base_len, const int* __
 
 using namespace siar;
 
+SIAR_DEFINE_PDL_SWITCH()
+
 #define LAUNCH_END() return (int)cudaGetLastError()
 
 extern "C" int siar_embed_gather(int is_bf16, const int* tokens, const void* table, float* out, int N, int H,
@@ -155,15 +236,15 @@ extern "C" int siar_embed_gather(int is_bf16, const int* tokens, const void* tab
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (is_bf16)
-    embed_gather_kernel<__nv_bfloat16><<<N, 256, 0, s>>>(tokens, (const __nv_bfloat16*)table, out, H, V, status);
+    launch_kernel(embed_gather_kernel<__nv_bfloat16>, N, 256, 0, s, tokens, (const __nv_bfloat16*)table, out, H, V, status);
   else
-    embed_gather_kernel<float><<<N, 256, 0, s>>>(tokens, (const float*)table, out, H, V, status);
+    launch_kernel(embed_gather_kernel<float>, N, 256, 0, s, tokens, (const float*)table, out, H, V, status);
   LAUNCH_END();
 }
 
 extern "C" int siar_gather_rows(const float* src, const int* rows, float* dst, int R, int H, void* stream) {
   if (R == 0) return 0;
-  gather_rows_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(src, rows, dst, H);
+  launch_kernel(gather_rows_kernel, R, 256, 0, (cudaStream_t)stream, src, rows, dst, H);
   LAUNCH_END();
 }
 
@@ -171,19 +252,38 @@ extern "C" int siar_add_rmsnorm(int out_bf16, int weight_bf16, float* residual, 
                                 const void* weight, void* out, int N, int H, float eps, void* stream) {
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)out) % 16 == 0) &&
+                       ((uintptr_t)weight % 16 == 0);
+  if (H % 4 == 0 && H <= 16384 && aligned) {
+    int threads = ((H / 4 + 3) / 4 + 31) / 32 * 32;
+    if (threads < 64) threads = 64;
+    if (out_bf16 && weight_bf16)
+      launch_kernel(add_rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, N, threads, 0, s, residual, delta,
+                    (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, H, eps);
+    else if (out_bf16)
+      launch_kernel(add_rmsnorm_vec_kernel<__nv_bfloat16, float>, N, threads, 0, s, residual, delta,
+                    (const float*)weight, (__nv_bfloat16*)out, H, eps);
+    else if (weight_bf16)
+      launch_kernel(add_rmsnorm_vec_kernel<float, __nv_bfloat16>, N, threads, 0, s, residual, delta,
+                    (const __nv_bfloat16*)weight, (float*)out, H, eps);
+    else
+      launch_kernel(add_rmsnorm_vec_kernel<float, float>, N, threads, 0, s, residual, delta, (const float*)weight,
+                    (float*)out, H, eps);
+    LAUNCH_END();
+  }
   const int threads = H >= 2048 ? 512 : 256;
   if (out_bf16 && weight_bf16)
-    add_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16><<<N, threads, 0, s>>>(
-        residual, delta, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, H, eps);
+    launch_kernel(add_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>, N, threads, 0, s, residual, delta,
+                  (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, H, eps);
   else if (out_bf16)
-    add_rmsnorm_kernel<__nv_bfloat16, float><<<N, threads, 0, s>>>(residual, delta, (const float*)weight,
-                                                                  (__nv_bfloat16*)out, H, eps);
+    launch_kernel(add_rmsnorm_kernel<__nv_bfloat16, float>, N, threads, 0, s, residual, delta, (const float*)weight,
+                  (__nv_bfloat16*)out, H, eps);
   else if (weight_bf16)
-    add_rmsnorm_kernel<float, __nv_bfloat16><<<N, threads, 0, s>>>(residual, delta, (const __nv_bfloat16*)weight,
-                                                                  (float*)out, H, eps);
+    launch_kernel(add_rmsnorm_kernel<float, __nv_bfloat16>, N, threads, 0, s, residual, delta,
+                  (const __nv_bfloat16*)weight, (float*)out, H, eps);
   else
-    add_rmsnorm_kernel<float, float><<<N, threads, 0, s>>>(residual, delta, (const float*)weight, (float*)out, H,
-                                                          eps);
+    launch_kernel(add_rmsnorm_kernel<float, float>, N, threads, 0, s, residual, delta, (const float*)weight,
+                  (float*)out, H, eps);
   LAUNCH_END();
 }
 
@@ -196,11 +296,11 @@ extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq,
   dim3 grid(N, Hq + 2 * Hkv);
   const int threads = D >= 128 ? 64 : 32;
   if (is_bf16)
-    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(
+    launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, grid, threads, 0, s, 
         (__nv_bfloat16*)qkv, inv_freq, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids,
         q_start, base_len, B, Hq, Hkv, D, page_tokens, max_pages, n_pages, write_kv, status);
   else
-    rope_kv_write_kernel<float><<<grid, threads, 0, s>>>((float*)qkv, inv_freq, (float*)k_pool, (float*)v_pool,
+    launch_kernel(rope_kv_write_kernel<float>, grid, threads, 0, s, (float*)qkv, inv_freq, (float*)k_pool, (float*)v_pool,
                                                         block_table, slot_ids, q_start, base_len, B, Hq, Hkv, D,
                                                         page_tokens, max_pages, n_pages, write_kv, status);
   LAUNCH_END();
@@ -211,14 +311,14 @@ extern "C" int siar_swiglu(int is_bf16, const void* gu, void* out, int N, int I,
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(N, (I + 255) / 256);
   if (is_bf16)
-    swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+    launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
   else
-    swiglu_kernel<float><<<grid, 256, 0, s>>>((const float*)gu, (float*)out, I);
+    launch_kernel(swiglu_kernel<float>, grid, 256, 0, s, (const float*)gu, (float*)out, I);
   LAUNCH_END();
 }
 
 extern "C" int siar_advance_lengths(int* base_len, const int* q_start, int B, void* stream) {
   if (B == 0) return 0;
-  advance_lengths_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(base_len, q_start, B);
+  launch_kernel(advance_lengths_kernel, (B + 127) / 128, 128, 0, (cudaStream_t)stream, base_len, q_start, B);
   LAUNCH_END();
 }

@@ -22,6 +22,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256) gemm_nt_tiled_kernel(const TIn* __restrict__ A, const TIn* __restrict__ W,
                                                            TOut* __restrict__ C, int M, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -84,6 +86,8 @@ template <typename TOut, int MB>
 __global__ void __launch_bounds__(256) gemm_nt_skinny_kernel(const __nv_bfloat16* __restrict__ A,
                                                             const __nv_bfloat16* __restrict__ W,
                                                             TOut* __restrict__ C, int M, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 8 + warp;
   if (n >= N) return;
@@ -117,6 +121,8 @@ __global__ void __launch_bounds__(256) gemm_nt_skinny_kernel(const __nv_bfloat16
 
 using namespace siar;
 
+SIAR_DEFINE_PDL_SWITCH()
+
 // in_bf16: dtype of A and W; out_f32: dtype of C.  allow_skinny picks the
 // streaming kernel where it applies (bf16, M <= 16, K % 8 == 0, 16-byte aligned).
 extern "C" int siar_gemm_nt_simt(int in_bf16, int out_f32, const void* A, const void* W, void* C, int M, int N,
@@ -128,12 +134,12 @@ extern "C" int siar_gemm_nt_simt(int in_bf16, int out_f32, const void* A, const 
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     if (M <= 4) {
       dim3 grid((N + 7) / 8, 1);
-      if (out_f32) gemm_nt_skinny_kernel<float, 4><<<grid, 256, 0, s>>>(a, w, (float*)C, M, N, K);
-      else gemm_nt_skinny_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(a, w, (__nv_bfloat16*)C, M, N, K);
+      if (out_f32) launch_kernel(gemm_nt_skinny_kernel<float, 4>, grid, 256, 0, s, a, w, (float*)C, M, N, K);
+      else launch_kernel(gemm_nt_skinny_kernel<__nv_bfloat16, 4>, grid, 256, 0, s, a, w, (__nv_bfloat16*)C, M, N, K);
     } else {
       dim3 grid((N + 7) / 8, (M + 7) / 8);
-      if (out_f32) gemm_nt_skinny_kernel<float, 8><<<grid, 256, 0, s>>>(a, w, (float*)C, M, N, K);
-      else gemm_nt_skinny_kernel<__nv_bfloat16, 8><<<grid, 256, 0, s>>>(a, w, (__nv_bfloat16*)C, M, N, K);
+      if (out_f32) launch_kernel(gemm_nt_skinny_kernel<float, 8>, grid, 256, 0, s, a, w, (float*)C, M, N, K);
+      else launch_kernel(gemm_nt_skinny_kernel<__nv_bfloat16, 8>, grid, 256, 0, s, a, w, (__nv_bfloat16*)C, M, N, K);
     }
     return (int)cudaGetLastError();
   }
@@ -141,13 +147,13 @@ extern "C" int siar_gemm_nt_simt(int in_bf16, int out_f32, const void* A, const 
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
   if (in_bf16) {
     if (out_f32)
-      gemm_nt_tiled_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)A,
+      launch_kernel(gemm_nt_tiled_kernel<__nv_bfloat16, float>, grid, 256, 0, s, (const __nv_bfloat16*)A,
                                                                      (const __nv_bfloat16*)W, (float*)C, M, N, K);
     else
-      gemm_nt_tiled_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(
+      launch_kernel(gemm_nt_tiled_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, s, 
           (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K);
   } else {
-    gemm_nt_tiled_kernel<float, float><<<grid, 256, 0, s>>>((const float*)A, (const float*)W, (float*)C, M, N, K);
+    launch_kernel(gemm_nt_tiled_kernel<float, float>, grid, 256, 0, s, (const float*)A, (const float*)W, (float*)C, M, N, K);
   }
   return (int)cudaGetLastError();
 }

@@ -128,6 +128,7 @@ struct GemmParams {
   int transpose_out;  // 0: C[p][q], 1: C[q][p]
   int kb_per_split;   // k-blocks of 64 per split
   long long plane;    // elements of one split-K plane
+  int x_is_weight;    // X is written by no kernel (swap-AB): its tiles may load before pdl_wait()
 };
 
 // ------------------------------------------------------------------ kernel
@@ -150,6 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const uint32_t dyn = smem_u32(smem_dyn);
   unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p0 = blockIdx.x * kBM, q0 = blockIdx.y * BN;
   const int num_kb_total = (prm.K + kBK - 1) / kBK;
@@ -185,7 +187,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmY) : "memory");
       int issued = 0;
-      for (int i = 0; i < num_kb; ++i) {
+      // Weights do not depend on earlier kernels: when X is the weight, the first STAGES
+      // tiles of it are requested before this grid waits for its predecessors.
+      const int pre = prm.x_is_weight ? min(STAGES, num_kb) : 0;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], kStageBytes);
+        tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
+      issued = pre;
+      for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1) || *(volatile int*)&abort_flag) {
@@ -233,6 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     // ---------------- epilogue: TMEM -> registers -> global
     const int quad = warp & 3;
     const int p = p0 + quad * 32 + lane;
+    pdl_wait();   // C and the split-K scratch may still be in use by an earlier kernel
     bool ok = true;
     if (num_kb > 0) {
       ok = mbar_wait(&tmem_full_bar, 0);
@@ -243,6 +257,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     float* plane = prm.partial ? prm.partial + (long long)blockIdx.z * prm.plane : nullptr;
     TOut* C = (TOut*)prm.C;
     constexpr int kChunks = (BN + 15) / 16;
+    if (!prm.transpose_out && plane == nullptr) {
+      // Rows of C are rows of the tile: stage the tile in the (now idle) pipeline memory,
+      // one padded float row per thread, then write it out in whole row segments.
+      constexpr int LD = BN + 1;
+      float* stage = reinterpret_cast<float*>(tiles);
+      const int tr = quad * 32 + lane;
+#pragma unroll 1
+      for (int ch = 0; ch < kChunks; ++ch) {
+        uint32_t r[16];
+        if (num_kb > 0 && ok) {
+          SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int et = threadIdx.x - 64;          // 0..127
+      const int ew = et >> 5;                   // warp of the epilogue group
+      const int cols = min(BN, prm.Q - q0);
+      constexpr int VEC = 4;                    // elements per lane and pass
+      const bool vec_ok = (prm.ldc % VEC == 0) && (cols % VEC == 0) &&
+                          ((reinterpret_cast<uintptr_t>(C) % 16) == 0);
+      for (int rr = ew; rr < kBM; rr += 4) {
+        const int pp = p0 + rr;
+        if (pp >= prm.P) break;
+        const float* src = stage + rr * LD;
+        TOut* dst = C + (long long)pp * prm.ldc + q0;
+        if (vec_ok) {
+          for (int c4 = lane * VEC; c4 < cols; c4 += 32 * VEC) {
+            const float v0 = src[c4], v1 = src[c4 + 1], v2 = src[c4 + 2], v3 = src[c4 + 3];
+            if constexpr (sizeof(TOut) == 4) {
+              *reinterpret_cast<float4*>(dst + c4) = make_float4(v0, v1, v2, v3);
+            } else {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
+              uint2 pk;
+              pk.x = *reinterpret_cast<uint32_t*>(&lo);
+              pk.y = *reinterpret_cast<uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(dst + c4) = pk;
+            }
+          }
+        } else {
+          for (int c1 = lane; c1 < cols; c1 += 32) store_out<TOut>(dst + c1, src[c1]);
+        }
+      }
+    } else
 #pragma unroll 1
     for (int ch = 0; ch < kChunks; ++ch) {
       uint32_t r[16];
@@ -378,13 +441,14 @@ static int launch(const CUtensorMap& tmX, const CUtensorMap& tmY, const GemmPara
     attr_set = true;
   }
   dim3 grid((prm.P + kBM - 1) / kBM, (prm.Q + BN - 1) / BN, splits);
-  kern<<<grid, 192, smem, s>>>(tmX, tmY, prm);
-  return (int)cudaGetLastError();
+  return (int)launch_kernel(kern, grid, dim3(192), smem, s, tmX, tmY, prm);
 }
 
 }  // namespace siar
 
 using namespace siar;
+
+SIAR_DEFINE_PDL_SWITCH()
 
 // Float32 elements of split-K scratch and int32 tile counters siar_gemm_tc_bf16 may need for these sizes.
 extern "C" int siar_gemm_tc_max_tiles() { return 4096; }
@@ -435,6 +499,7 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   prm.transpose_out = swap ? 1 : 0;
   prm.kb_per_split = kbps;
   prm.plane = (long long)M * N;
+  prm.x_is_weight = swap ? 1 : 0;
 
 #define SIAR_GO(BN_, ST_)                                                                      \
   return out_f32 ? launch<BN_, ST_, float>(tmX, tmY, prm, splits, s)                           \

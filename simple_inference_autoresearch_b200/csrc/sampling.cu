@@ -109,6 +109,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const long long* __restrict__ seeds, int* __restrict__ draw_index, int advance_index,
               int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ Shared sh;
   const int r = blockIdx.x;
   const float* x = logits + (size_t)r * V;
@@ -263,11 +265,13 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 
 using namespace siar;
 
+SIAR_DEFINE_PDL_SWITCH()
+
 extern "C" int siar_sample(const float* logits, int R, int V, const float* temperature, const int* top_k,
                            const float* top_p, const long long* seeds, int* draw_index, int advance_index,
                            int* out, void* stream) {
   if (R == 0) return 0;
-  sample_kernel<<<R, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, V, temperature, top_k, top_p, seeds,
+  launch_kernel(sample_kernel, R, kSampleThreads, 0, (cudaStream_t)stream, logits, V, temperature, top_k, top_p, seeds,
                                                                draw_index, advance_index, out);
   return (int)cudaGetLastError();
 }

@@ -51,7 +51,8 @@ _signatures = {
         "siar_attn_mma_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
         "siar_attn_mma_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                 c_void_p],
         "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
         "siar_attn_mma_decode_chunk": [],
     },
@@ -228,6 +229,34 @@ def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         raise ValueError(f"num heads {n_heads} is not a multiple of kv heads {n_kv_heads}")
 
 
+_counters = {}
+
+
+def _decode_counters(device, need: int) -> torch.Tensor:
+    """Zeroed int32 counters the split decode attention uses to find the block that
+    finishes last; the kernel leaves them zero.  Allocated once per device."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _counters.get(key)
+    if t is None or t.numel() < need:
+        t = torch.zeros(max(need, 1 << 16), dtype=torch.int32, device=dev)
+        _counters[key] = t
+    return t
+
+
+def set_programmatic_launch(on: bool) -> None:
+    """Turns programmatic dependent launch on or off for every loaded and future unit
+    (off = plain stream order between kernels; results are the same either way)."""
+    global _pdl
+    _pdl = bool(on)
+    for unit in build.available_units():
+        lib = build.load_unit(unit)
+        if hasattr(lib, "siar_set_pdl"):
+            lib.siar_set_pdl(int(_pdl))
+
+
+_pdl = True
+
 #: set to False to force the CUDA-core attention kernels on the bfloat16 path (tests compare both)
 use_mma_attention = True
 
@@ -263,7 +292,8 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
                               dtype=torch.float32, device=qkv.device)
         if mma:
             _launch("attention_mma", "siar_attn_mma_decode", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
-                    _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)
+                    _ptr(scratch), _ptr(_decode_counters(qkv.device, meta.n_seqs * n_kv_heads)), *sizes,
+                    meta.max_kv_len, float(scale), _stream())
         else:
             _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
                     _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)

@@ -220,3 +220,25 @@ def test_generation_stops_at_stop_tokens_and_samples_reproducibly(folders):
     eng1 = siar.build_engine(loaded, max_batch=1, max_seq_len=128, use_cuda_graph=False)
     alone = eng1.generate([reqs[0]], p, max_new_tokens=12, ignore_eos=True)
     assert alone[0] == a[0]
+
+
+def test_programmatic_launch_on_and_off_give_the_same_tokens_and_logits(folders):
+    """Kernels launched with and without programmatic dependent launch: identical results
+    (a kernel that read its input before its predecessor had finished would show here)."""
+    from simple_inference_autoresearch_b200.kernels import ops
+    name = "C"
+    vocab = tiny_configs.CONFIGS[name]["vocab_size"]
+    reqs = prompts(vocab, [40, 9, 77], seed=8)
+    results = []
+    for on in (True, False, True):
+        ops.set_programmatic_launch(on)
+        try:
+            eng = engine_for(folders, name, torch.bfloat16, max_batch=3)
+            toks = eng.generate(reqs, SamplingParams(temperature=0.0), max_new_tokens=20, ignore_eos=True)
+            s = eng.open()
+            logits = eng.step([StepEntry(s, reqs[2], range(len(reqs[2])))]).cpu()
+            results.append((toks, logits))
+        finally:
+            ops.set_programmatic_launch(True)
+    assert results[0][0] == results[1][0] == results[2][0]
+    assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][1], results[2][1])
