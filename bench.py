@@ -98,6 +98,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--no-pdl", action="store_true", help="launch kernels in plain stream order (no programmatic dependent launch)")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the timed decode replays with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -121,6 +122,8 @@ def main() -> int:
     from simple_inference_autoresearch_b200.engine import generation
     from simple_inference_autoresearch_b200.kernels import ops
 
+    if args.no_pdl:
+        ops.set_programmatic_launch(False)
     full = LlamaConfig.from_json(preset_path("llama-3.1-8b"))
     cfg = dataclasses.replace(full, num_hidden_layers=args.layers) if args.layers else full
     pk, pk_src = peaks()

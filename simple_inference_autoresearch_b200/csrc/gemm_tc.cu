@@ -10,9 +10,10 @@
 //   * many rows (prefill): X = A, Y = W, C[p][q] = D[p][q].
 //   * few rows (decode, M <= 128): X = W, Y = A ("swap-AB": the weight fills the
 //     128-row axis and the batch sits on the narrow N axis), C[q][p] = D[p][q].
-// Few output tiles are cut along K (split-K): each part writes a float32 partial,
-// and the last part to finish adds all partials of the tile in part order, so the
-// sum does not depend on which part finished last.
+// Few output tiles are cut along K (split-K): the parts of a tile run as one thread-block
+// cluster, keep their float32 partial tiles in shared memory, and after a cluster barrier
+// every block adds, for its share of the outputs, all partials in rank order through
+// distributed shared memory.  No scratch in global memory, and one order of summation.
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory
 // and issues the MMAs, warps 2..5 run the epilogue (warp w reads TMEM lanes
@@ -120,16 +121,28 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 
 struct GemmParams {
   void* C;            // output, TOut
-  float* partial;     // split-K planes [splits][rows_c * ldc] (nullptr when splits == 1)
-  int* counters;      // one per output tile, zero between launches
   int* status;
   int P, Q, K;        // D is P x Q
   int ldc;            // leading dimension of C
   int transpose_out;  // 0: C[p][q], 1: C[q][p]
   int kb_per_split;   // k-blocks of 64 per split
-  long long plane;    // elements of one split-K plane
   int x_is_weight;    // X is written by no kernel (swap-AB): its tiles may load before pdl_wait()
+#ifdef SIAR_TIMING
+  unsigned long long* stamps;   // [blocks][8] globaltimer marks, for profiling builds only
+#endif
 };
+
+#ifdef SIAR_TIMING
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define SIAR_STAMP(i) \
+  if (prm.stamps) prm.stamps[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (i)] = gtime()
+#else
+#define SIAR_STAMP(i)
+#endif
 
 // ------------------------------------------------------------------ kernel
 template <int BN, int STAGES, typename TOut>
@@ -146,12 +159,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   __shared__ __align__(8) uint64_t tmem_full_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ int is_last;
 
   const uint32_t dyn = smem_u32(smem_dyn);
   unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
 
   pdl_launch_dependents();
+  if (threadIdx.x == 0) { SIAR_STAMP(0); }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p0 = blockIdx.x * kBM, q0 = blockIdx.y * BN;
   const int num_kb_total = (prm.K + kBK - 1) / kBK;
@@ -167,7 +180,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
     mbar_init(&tmem_full_bar, 1);
     abort_flag = 0;
-    is_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(&tmem_base_slot, kTmemCols);
@@ -178,9 +190,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   // A block that starts after another one has reported an expired wait does no work:
   // a broken launch then ends after one wave instead of one second per block.
   const bool dead = (*(volatile int*)prm.status & kStatusWaitExpired) != 0;
+  constexpr int kChunks = (BN + 15) / 16;
+  constexpr int LD = BN + 1;                       // padded row of the accumulator stage
+  float* stage = reinterpret_cast<float*>(tiles);
+  TOut* C = (TOut*)prm.C;
 
+  {
   if (dead) {
-    // fall through to the teardown
+    // fall through to the write-out barriers and the teardown
   } else if (warp == 0) {
     // ---------------- TMA producer
     if (lane == 0) {
@@ -194,7 +211,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         mbar_expect_tx(&full_bar[i], kStageBytes);
         tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
       }
+      SIAR_STAMP(1);
       pdl_wait();
+      SIAR_STAMP(2);
       for (int i = 0; i < pre; ++i)
         tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
       issued = pre;
@@ -226,6 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait(&full_bar[s], ph) || *(volatile int*)&abort_flag) { ok = false; break; }
+        if (i == 0) { SIAR_STAMP(3); }
         tc_fence_after();
         const uint32_t xs = smem_u32(tiles + (size_t)s * kStageBytes);
         const uint64_t da = smem_desc_sw128(xs), db = smem_desc_sw128(xs + kXBytes);
@@ -243,42 +263,84 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       umma_commit(&tmem_full_bar);    // accumulator complete (or abandoned)
     }
   } else {
-    // ---------------- epilogue: TMEM -> registers -> global
+    // ---------------- epilogue: TMEM -> registers -> shared-memory stage
     const int quad = warp & 3;
-    const int p = p0 + quad * 32 + lane;
-    pdl_wait();   // C and the split-K scratch may still be in use by an earlier kernel
+    pdl_wait();   // C may still be read by an earlier kernel
     bool ok = true;
     if (num_kb > 0) {
       ok = mbar_wait(&tmem_full_bar, 0);
       if (!ok) { abort_flag = 1; atomicOr(prm.status, kStatusWaitExpired); }
     }
     tc_fence_after();
+    if (threadIdx.x == 64) { SIAR_STAMP(4); }
     ok = ok && !*(volatile int*)&abort_flag;
-    float* plane = prm.partial ? prm.partial + (long long)blockIdx.z * prm.plane : nullptr;
-    TOut* C = (TOut*)prm.C;
-    constexpr int kChunks = (BN + 15) / 16;
-    if (!prm.transpose_out && plane == nullptr) {
-      // Rows of C are rows of the tile: stage the tile in the (now idle) pipeline memory,
-      // one padded float row per thread, then write it out in whole row segments.
-      constexpr int LD = BN + 1;
-      float* stage = reinterpret_cast<float*>(tiles);
-      const int tr = quad * 32 + lane;
+    // The accumulator tile goes to the (now idle) pipeline memory, one padded float row per
+    // tile row, so that it can be written out in whole row segments or, with split-K, be read
+    // by the other blocks of the cluster.
+    const int tr = quad * 32 + lane;
 #pragma unroll 1
-      for (int ch = 0; ch < kChunks; ++ch) {
-        uint32_t r[16];
-        if (num_kb > 0 && ok) {
-          SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        } else {
+    for (int ch = 0; ch < kChunks; ++ch) {
+      uint32_t r[16];
+      if (num_kb > 0 && ok) {
+        SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) r[j] = 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) r[j] = 0u;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const int et = threadIdx.x - 64;          // 0..127
-      const int ew = et >> 5;                   // warp of the epilogue group
+#pragma unroll
+      for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+  }
+  }  // roles
+
+  // ---------------- write-out
+  if (splits > 1) {
+    // split-K: the blocks of a cluster hold the partial tiles of the same outputs.  After a
+    // cluster barrier every block adds, for its share of the outputs, the partials of all
+    // blocks in rank order (read through distributed shared memory), so the sum has one order.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (threadIdx.x == 64) { SIAR_STAMP(5); }
+    if (warp >= 2 && !dead) {
+      const int et = threadIdx.x - 64;            // 0..127: tile row p (transposed output: contiguous)
+      const int pp = p0 + et;
+      const uint32_t my = smem_u32(stage + et * LD);
+      // outputs jq = rank, rank + splits, ...; the loads of one output are independent
+      uint32_t peer[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z)
+        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[z]) : "r"(my), "r"(z < splits ? z : 0));
+      for (int jq = (int)blockIdx.z; jq < BN; jq += splits) {
+        const int q = q0 + jq;
+        if (q >= prm.Q) break;
+        float v[8];
+#pragma unroll
+        for (int z = 0; z < 8; ++z)
+          if (z < splits) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[z]) : "r"(peer[z] + (uint32_t)jq * 4u));
+        float acc = 0.f;
+#pragma unroll
+        for (int z = 0; z < 8; ++z)
+          if (z < splits) acc += v[z];
+        if (pp < prm.P) store_out<TOut>(C + (long long)q * prm.ldc + pp, acc);
+      }
+    }
+    // nobody leaves while its tile may still be read
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  } else if (warp >= 2 && !dead) {
+    const int et = threadIdx.x - 64;          // 0..127
+    const int ew = et >> 5;
+    if (prm.transpose_out) {
+      // C[q][p]: for a fixed q the 128 tile rows are contiguous
+      const int pp = p0 + et;
+      if (pp < prm.P) {
+        const int cols = min(BN, prm.Q - q0);
+        for (int jq = 0; jq < cols; ++jq)
+          store_out<TOut>(C + (long long)(q0 + jq) * prm.ldc + pp, stage[et * LD + jq]);
+      }
+    } else {
       const int cols = min(BN, prm.Q - q0);
       constexpr int VEC = 4;                    // elements per lane and pass
       const bool vec_ok = (prm.ldc % VEC == 0) && (cols % VEC == 0) &&
@@ -305,70 +367,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           for (int c1 = lane; c1 < cols; c1 += 32) store_out<TOut>(dst + c1, src[c1]);
         }
       }
-    } else
-#pragma unroll 1
-    for (int ch = 0; ch < kChunks; ++ch) {
-      uint32_t r[16];
-      if (num_kb > 0 && ok) {
-        SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = 0u;
-      }
-      if (p < prm.P) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int q = q0 + ch * 16 + j;
-          if (q < prm.Q) {
-            const long long idx = prm.transpose_out ? (long long)q * prm.ldc + p : (long long)p * prm.ldc + q;
-            const float v = __uint_as_float(r[j]);
-            if (plane) plane[idx] = v; else store_out<TOut>(C + idx, v);
-          }
-        }
-      }
-    }
-    if (plane) {
-      // split-K: the part that arrives last adds the partials of this tile in part order
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-        const int old = atomicAdd(prm.counters + tile, 1);
-        is_last = (old == splits - 1);
-        if (old == splits - 1) prm.counters[tile] = 0;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (is_last) {
-        __threadfence();
-        const int et = threadIdx.x - 64;   // 0..127
-        if (prm.transpose_out) {
-          // rows of C are q; p is contiguous
-          for (int j = 0; j < BN; ++j) {
-            const int q = q0 + j, pp = p0 + et;
-            if (q < prm.Q && pp < prm.P) {
-              const long long idx = (long long)q * prm.ldc + pp;
-              float acc = 0.f;
-              for (int z = 0; z < splits; ++z) acc += __ldcg(prm.partial + (long long)z * prm.plane + idx);
-              store_out<TOut>(C + idx, acc);
-            }
-          }
-        } else {
-          for (int e = et; e < kBM * BN; e += 128) {
-            const int pp = p0 + e / BN, q = q0 + e % BN;
-            if (q < prm.Q && pp < prm.P) {
-              const long long idx = (long long)pp * prm.ldc + q;
-              float acc = 0.f;
-              for (int z = 0; z < splits; ++z) acc += __ldcg(prm.partial + (long long)z * prm.plane + idx);
-              store_out<TOut>(C + idx, acc);
-            }
-          }
-        }
-      }
     }
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) { SIAR_STAMP(6); }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -441,7 +444,22 @@ static int launch(const CUtensorMap& tmX, const CUtensorMap& tmY, const GemmPara
     attr_set = true;
   }
   dim3 grid((prm.P + kBM - 1) / kBM, (prm.Q + BN - 1) / BN, splits);
-  return (int)launch_kernel(kern, grid, dim3(192), smem, s, tmX, tmY, prm);
+  // The `splits` blocks of an output tile form one thread-block cluster (along z).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, kern, tmX, tmY, prm);
 }
 
 }  // namespace siar
@@ -450,18 +468,18 @@ using namespace siar;
 
 SIAR_DEFINE_PDL_SWITCH()
 
-// Float32 elements of split-K scratch and int32 tile counters siar_gemm_tc_bf16 may need for these sizes.
-extern "C" int siar_gemm_tc_max_tiles() { return 4096; }
+
+#ifdef SIAR_TIMING
+static unsigned long long* g_stamps = nullptr;
+extern "C" void siar_gemm_tc_set_stamps(unsigned long long* p) { g_stamps = p; }
+#endif
 
 // Returns 0 on launch, a cudaError_t on failure, and -1 when the shape is one this
 // unit does not take (the caller then uses the CUDA-core kernel).
 //   A [M,K], W [N,K] bf16 row-major; C [M,N] bf16 (out_f32 == 0) or float32.
-//   workspace: float32 scratch of workspace_floats elements for split-K partials (a product is
-//   only split when splits * M * N fits); counters: siar_gemm_tc_max_tiles() int32 zeros (left zero
-//   on return).
+//   max_splits caps the split along K (1 = never split; at most 8, the portable cluster size).
 extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
-                                 float* workspace, long long workspace_floats, int* counters, int* status,
-                                 int sm_count, void* stream) {
+                                 int max_splits, int* status, int sm_count, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || K < 8) return -1;                       // TMA needs 16-byte row strides
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -1;
@@ -479,11 +497,11 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   const int tiles = ((P + kBM - 1) / kBM) * ((Q + BN - 1) / BN);
   const int num_kb = (K + kBK - 1) / kBK;
   int splits = 1;
-  if (swap && workspace && counters && tiles < sm_count && tiles <= siar_gemm_tc_max_tiles()) {
+  if (swap && tiles < sm_count) {
     splits = (sm_count + tiles - 1) / tiles;
     if (splits > 8) splits = 8;
+    if (splits > max_splits) splits = max_splits;
     if (splits > num_kb / 4) splits = num_kb / 4;
-    while (splits > 1 && (long long)splits * M * N > workspace_floats) --splits;
     if (splits < 1) splits = 1;
   }
   int kbps = (num_kb + splits - 1) / splits;
@@ -491,15 +509,15 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
 
   GemmParams prm;
   prm.C = C;
-  prm.partial = splits > 1 ? workspace : nullptr;
-  prm.counters = counters;
   prm.status = status;
   prm.P = P; prm.Q = Q; prm.K = K;
   prm.ldc = N;
   prm.transpose_out = swap ? 1 : 0;
   prm.kb_per_split = kbps;
-  prm.plane = (long long)M * N;
   prm.x_is_weight = swap ? 1 : 0;
+#ifdef SIAR_TIMING
+  prm.stamps = g_stamps;
+#endif
 
 #define SIAR_GO(BN_, ST_)                                                                      \
   return out_f32 ? launch<BN_, ST_, float>(tmX, tmY, prm, splits, s)                           \

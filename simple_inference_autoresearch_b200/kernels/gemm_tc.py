@@ -2,9 +2,7 @@
 
 ``try_linear`` runs the product when the shape is one the unit takes (K a multiple
 of 8, 16-byte aligned operands) and returns False otherwise, so that the caller
-uses the CUDA-core kernel.  The unit keeps, per device, a float32 scratch for
-split-K partials and a few zeroed tile counters; both are allocated once, outside
-any graph capture (the engine runs a step eagerly before it captures one).
+uses the CUDA-core kernel.
 """
 
 from __future__ import annotations
@@ -15,8 +13,9 @@ import torch
 
 from . import build
 
-_WORKSPACE_FLOATS = 8 * 128 * 16384      # 64 MiB: eight partial planes of a 128-row, 16384-wide product
 _state = {}
+#: cap of the split along K for products with few output tiles (1 disables it)
+max_splits = 8
 _fn = None
 enabled = True
 
@@ -27,11 +26,10 @@ def _bind():
         lib = build.load_unit("gemm_tc")
         f = lib.siar_gemm_tc_bf16
         c = ctypes
-        f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_void_p,
-                      c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p]
+        f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                      c.c_void_p, c.c_int, c.c_void_p]
         f.restype = c.c_int
-        lib.siar_gemm_tc_max_tiles.restype = c.c_int
-        _fn = (f, lib.siar_gemm_tc_max_tiles())
+        _fn = f
     return _fn
 
 
@@ -39,12 +37,7 @@ def _device_state(device: torch.device):
     key = device.index if device.index is not None else torch.cuda.current_device()
     st = _state.get(key)
     if st is None:
-        _, max_tiles = _bind()
-        st = {
-            "workspace": torch.empty(_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
-            "counters": torch.zeros(max_tiles, dtype=torch.int32, device=device),
-            "sms": torch.cuda.get_device_properties(device).multi_processor_count,
-        }
+        st = {"sms": torch.cuda.get_device_properties(device).multi_processor_count}
         _state[key] = st
     return st
 
@@ -55,12 +48,11 @@ def try_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
         return False
     from . import ops
 
-    fn, _ = _bind()
+    fn = _bind()
     m, k = x.shape
     n = w.shape[0]
     st = _device_state(x.device)
-    err = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
-             st["workspace"].data_ptr(), _WORKSPACE_FLOATS, st["counters"].data_ptr(),
+    err = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32), max_splits,
              ops.status_word(x.device).data_ptr(), st["sms"], torch.cuda.current_stream().cuda_stream)
     if err == -1:
         return False
