@@ -143,9 +143,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
 }
 
 // ------------------------------------------------------------------ rotary + cache write
-// grid (N, Hq + 2*Hkv); one block per (token, head of the fused qkv row).
-// q heads are rotated in place, k heads are rotated into the cache, v heads are
-// copied into the cache.  inv_freq == nullptr means "no rotation".
+// One block per token.  The token's sin/cos (one pair per rotary frequency, shared by all
+// heads) are formed once in shared memory; then q heads are rotated in place, k heads are
+// rotated into the cache and v heads are copied into the cache.  inv_freq == nullptr means
+// "no rotation".
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ inv_freq,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -154,48 +155,50 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
                                      int n_pages, int write_kv, int* __restrict__ status) {
   pdl_launch_dependents();
+  extern __shared__ float cs[];   // cos[half], sin[half]
+  const int half = D >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) cs[i] = inv_freq != nullptr ? inv_freq[i] : 0.f;
   pdl_wait();
   const int t = blockIdx.x;
-  const int head = blockIdx.y;
   const int b = find_sequence(q_start, B, t);
   const int pos = base_len[b] + (t - q_start[b]);
-  const int half = D >> 1;
-  T* row = qkv + (size_t)t * (Hq + 2 * Hkv) * D + (size_t)head * D;
-
-  T* dst = nullptr;
-  if (head >= Hq) {
-    if (!write_kv) return;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn = 0.f, c = 1.f;
+    if (inv_freq != nullptr) sincosf((float)pos * cs[i], &sn, &c);
+    cs[i] = c;
+    cs[half + i] = sn;
+  }
+  T* row = qkv + (size_t)t * (Hq + 2 * Hkv) * D;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (write_kv) {
     const int slot = slot_ids[b];
     const int page = block_table[(size_t)slot * max_pages + pos / page_tokens];
     if (page < 0 || page >= n_pages) {
       if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
-      return;
+    } else {
+      const size_t off = ((size_t)page * Hkv * page_tokens + (pos % page_tokens)) * D;   // kv head 0
+      kdst = k_pool + off;
+      vdst = v_pool + off;
     }
-    const int kvh = (head - Hq) % Hkv;
-    T* pool = (head < Hq + Hkv) ? k_pool : v_pool;
-    dst = pool + (((size_t)page * Hkv + kvh) * page_tokens + (pos % page_tokens)) * D;
   }
-
-  if (head < Hq + Hkv) {  // q or k: rotate
+  __syncthreads();
+  const size_t head_stride = (size_t)page_tokens * D;   // between kv heads inside a page
+  const int n_rot = Hq + (kdst != nullptr ? Hkv : 0);
+  // heads are dealt to the blocks of a token (gridDim.y of them: more than one when few tokens run)
+  for (int head = blockIdx.y; head < n_rot; head += gridDim.y) {
+    T* dst = head < Hq ? row + head * D : kdst + (size_t)(head - Hq) * head_stride;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      float a = to_f32(row[i]), c = to_f32(row[i + half]);
-      float oa = a, oc = c;
-      if (inv_freq != nullptr) {
-        float sn, cs;
-        sincosf((float)pos * inv_freq[i], &sn, &cs);
-        oa = a * cs - c * sn;
-        oc = c * cs + a * sn;
-      }
-      if (dst != nullptr) {
-        dst[i] = from_f32<T>(oa);
-        dst[i + half] = from_f32<T>(oc);
-      } else {
-        row[i] = from_f32<T>(oa);
-        row[i + half] = from_f32<T>(oc);
-      }
+      const float a = to_f32(row[head * D + i]), c = to_f32(row[head * D + i + half]);
+      const float cosv = cs[i], sinv = cs[half + i];
+      dst[i] = from_f32<T>(a * cosv - c * sinv);
+      dst[i + half] = from_f32<T>(c * cosv + a * sinv);
     }
-  } else {  // v: copy
-    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = row[i];
+  }
+  if (vdst != nullptr) {
+    const T* vrow = row + (size_t)(Hq + Hkv) * D;
+    for (int head = blockIdx.y; head < Hkv; head += gridDim.y)
+      for (int i = threadIdx.x; i < D; i += blockDim.x) vdst[(size_t)head * head_stride + i] = vrow[head * D + i];
   }
 }
 
@@ -211,6 +214,27 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   const float u = to_f32(gu[row * 2 * I + I + j]);
   const float s = g / (1.f + expf(-g));
   out[row * I + j] = from_f32<T>(s * u);
+}
+
+// bf16, I % 8 == 0, 16-byte aligned rows: eight outputs per thread with 16-byte accesses.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (j >= I) return;
+  const uint4 gv = *reinterpret_cast<const uint4*>(gu + row * 2 * I + j);
+  const uint4 uv = *reinterpret_cast<const uint4*>(gu + row * 2 * I + I + j);
+  const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  uint4 ov;
+  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+    op[e] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+  }
+  *reinterpret_cast<uint4*>(out + row * I + j) = ov;
 }
 
 // ------------------------------------------------------------------ bookkeeping
@@ -293,22 +317,30 @@ extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq,
                                   int max_pages, int n_pages, int write_kv, int* status, void* stream) {
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(N, Hq + 2 * Hkv);
-  const int threads = D >= 128 ? 64 : 32;
+  if (D % 2 != 0) return (int)cudaErrorInvalidValue;
+  // many tokens: one block per token walks all heads; few tokens: several blocks share a token
+  const int ysplit = N >= 256 ? 1 : (Hq + Hkv < 16 ? Hq + Hkv : 16);
+  const int threads = D / 2 > 64 ? 128 : D / 2 > 32 ? 64 : 32;   // one pass over the D/2 pairs of a head
+  const size_t smem = sizeof(float) * D;
   if (is_bf16)
-    launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, grid, threads, 0, s, 
-        (__nv_bfloat16*)qkv, inv_freq, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids,
-        q_start, base_len, B, Hq, Hkv, D, page_tokens, max_pages, n_pages, write_kv, status);
+    launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(N, ysplit), dim3(threads), smem, s, (__nv_bfloat16*)qkv, inv_freq,
+                  (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv,
+                  D, page_tokens, max_pages, n_pages, write_kv, status);
   else
-    launch_kernel(rope_kv_write_kernel<float>, grid, threads, 0, s, (float*)qkv, inv_freq, (float*)k_pool, (float*)v_pool,
-                                                        block_table, slot_ids, q_start, base_len, B, Hq, Hkv, D,
-                                                        page_tokens, max_pages, n_pages, write_kv, status);
+    launch_kernel(rope_kv_write_kernel<float>, dim3(N, ysplit), dim3(threads), smem, s, (float*)qkv, inv_freq, (float*)k_pool,
+                  (float*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv, D, page_tokens, max_pages,
+                  n_pages, write_kv, status);
   LAUNCH_END();
 }
 
 extern "C" int siar_swiglu(int is_bf16, const void* gu, void* out, int N, int I, void* stream) {
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  if (is_bf16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) % 16) == 0) {
+    dim3 grid8(N, (I / 8 + 255) / 256);
+    launch_kernel(swiglu_bf16x8_kernel, grid8, dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+    LAUNCH_END();
+  }
   dim3 grid(N, (I + 255) / 256);
   if (is_bf16)
     launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);

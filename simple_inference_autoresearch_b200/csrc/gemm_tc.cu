@@ -11,9 +11,9 @@
 //   * few rows (decode, M <= 128): X = W, Y = A ("swap-AB": the weight fills the
 //     128-row axis and the batch sits on the narrow N axis), C[q][p] = D[p][q].
 // Few output tiles are cut along K (split-K): the parts of a tile run as one thread-block
-// cluster, keep their float32 partial tiles in shared memory, and after a cluster barrier
-// every block adds, for its share of the outputs, all partials in rank order through
-// distributed shared memory.  No scratch in global memory, and one order of summation.
+// cluster; every block owns a share of the tile's outputs, receives the other blocks'
+// float32 partials for them through distributed shared memory, and adds them in rank
+// order.  No scratch in global memory, and one order of summation.
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory
 // and issues the MMAs, warps 2..5 run the epilogue (warp w reads TMEM lanes
@@ -194,6 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   constexpr int LD = BN + 1;                       // padded row of the accumulator stage
   float* stage = reinterpret_cast<float*>(tiles);
   TOut* C = (TOut*)prm.C;
+  bool acc_ok = false;      // epilogue threads: the accumulator in tensor memory is complete
 
   {
   if (dead) {
@@ -274,61 +275,83 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     tc_fence_after();
     if (threadIdx.x == 64) { SIAR_STAMP(4); }
     ok = ok && !*(volatile int*)&abort_flag;
-    // The accumulator tile goes to the (now idle) pipeline memory, one padded float row per
-    // tile row, so that it can be written out in whole row segments or, with split-K, be read
-    // by the other blocks of the cluster.
-    const int tr = quad * 32 + lane;
+    // Without split-K the accumulator tile goes to the (now idle) pipeline memory, one padded
+    // float row per tile row, so that it can be written out in whole row segments.
+    if (splits == 1) {
+      const int tr = quad * 32 + lane;
 #pragma unroll 1
-    for (int ch = 0; ch < kChunks; ++ch) {
-      uint32_t r[16];
-      if (num_kb > 0 && ok) {
-        SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      } else {
+      for (int ch = 0; ch < kChunks; ++ch) {
+        uint32_t r[16];
+        if (num_kb > 0 && ok) {
+          SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = 0u;
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
       }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    acc_ok = ok;
   }
   }  // roles
 
   // ---------------- write-out
   if (splits > 1) {
-    // split-K: the blocks of a cluster hold the partial tiles of the same outputs.  After a
-    // cluster barrier every block adds, for its share of the outputs, the partials of all
-    // blocks in rank order (read through distributed shared memory), so the sum has one order.
+    // split-K: the blocks of a cluster hold partial tiles of the same outputs.  Output jq of
+    // the tile belongs to the block of rank jq % splits.  Barrier 1: every block's main loop is
+    // done, so its pipeline memory is free.  Then each block sends its partials to their owners
+    // (remote shared-memory stores into slot [sender rank]).  Barrier 2: all partials have
+    // arrived; each owner adds them in rank order, so the sum has one order, and stores.
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (threadIdx.x == 64) { SIAR_STAMP(5); }
+    const int rank = (int)blockIdx.z;
+    const int NL = (BN + splits - 1) / splits;          // outputs per owner
+    const int et = threadIdx.x - 64;                    // epilogue thread = tile row p
+    const uint32_t recv = smem_u32(tiles);              // float recv[splits][NL][128]
+    if (warp >= 2) {
+      const int quad = warp & 3;
+      const int tr = quad * 32 + lane;                  // the tile row this thread reads from TMEM
+#pragma unroll 1
+      for (int ch = 0; ch < kChunks; ++ch) {
+        uint32_t r[16];
+        if (num_kb > 0 && acc_ok) {
+          SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int jq = ch * 16 + j;
+          if (jq < BN) {
+            const int owner = jq % splits, jl = jq / splits;
+            const uint32_t local = recv + (uint32_t)(((rank * NL + jl) * 128 + tr) * 4);
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(r[j]) : "memory");
+          }
+        }
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (warp >= 2 && !dead) {
-      const int et = threadIdx.x - 64;            // 0..127: tile row p (transposed output: contiguous)
       const int pp = p0 + et;
-      const uint32_t my = smem_u32(stage + et * LD);
-      // outputs jq = rank, rank + splits, ...; the loads of one output are independent
-      uint32_t peer[8];
-#pragma unroll
-      for (int z = 0; z < 8; ++z)
-        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[z]) : "r"(my), "r"(z < splits ? z : 0));
-      for (int jq = (int)blockIdx.z; jq < BN; jq += splits) {
+      const float* mine = reinterpret_cast<const float*>(tiles);
+      for (int jl = 0; jl < NL; ++jl) {
+        const int jq = jl * splits + rank;
         const int q = q0 + jq;
-        if (q >= prm.Q) break;
-        float v[8];
-#pragma unroll
-        for (int z = 0; z < 8; ++z)
-          if (z < splits) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[z]) : "r"(peer[z] + (uint32_t)jq * 4u));
+        if (jq >= BN || q >= prm.Q) break;
         float acc = 0.f;
-#pragma unroll
-        for (int z = 0; z < 8; ++z)
-          if (z < splits) acc += v[z];
+        for (int z = 0; z < splits; ++z) acc += mine[(z * NL + jl) * 128 + et];
         if (pp < prm.P) store_out<TOut>(C + (long long)q * prm.ldc + pp, acc);
       }
     }
-    // nobody leaves while its tile may still be read
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   } else if (warp >= 2 && !dead) {
     const int et = threadIdx.x - 64;          // 0..127
     const int ew = et >> 5;
