@@ -24,11 +24,32 @@
 namespace siar {
 
 constexpr int kPad = 8;             // bf16 elements of padding per shared-memory row (16 bytes)
-constexpr int kMmaDecodeChunk = 128;
+constexpr int kMmaDecodeChunk = 128;   // granularity of a decode block's key range
+constexpr int kDecodeWarpKeys = 16;    // keys per warp and pipeline step in the decode kernel
 constexpr int kMmaPrefillRows = 64;
 constexpr int kMmaKeyTile = 64;
 
+#ifdef SIAR_TIMING
+__device__ unsigned long long* g_attn_stamps = nullptr;   // profiling builds only: [blocks][8] globaltimer marks
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define SIAR_STAMP(i)                                                                                    \
+  if (g_attn_stamps && threadIdx.x == 0)                                                                 \
+  g_attn_stamps[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (i)] = gtime()
+#else
+#define SIAR_STAMP(i)
+#endif
+
 // ------------------------------------------------------------------ decode
+// grid (chunks, Hkv, B), 128 threads.  A block owns `chunk_keys` consecutive keys of one
+// (sequence, kv head); warp w walks keys [c0 + 64 it + 16 w, +16) for it = 0, 1, ... with a
+// running (max, sum, output) per query head, its two shared-memory stages filled by cp.async
+// one step ahead (small stages, so that three blocks fit on an SM).  chunk_keys is a multiple of 128 chosen by the host so that the grid fills
+// the GPU: one chunk per sequence when the batch alone gives enough blocks, 128-key chunks
+// for a single sequence.
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ k_pool,
@@ -36,44 +57,51 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        const int* __restrict__ slot_ids, const int* __restrict__ q_start,
                        const int* __restrict__ base_len, float* __restrict__ part_ml, float* __restrict__ part_acc,
                        int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int page_tokens,
-                       int max_pages, int max_chunks, float scale) {
+                       int max_pages, int max_chunks, int chunk_keys, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int RS = D + kPad;                 // row stride in elements
+  constexpr int CPR = D / 8;                   // 16-byte pieces per row
+  constexpr int WK = kDecodeWarpKeys;          // keys per warp and step
+  constexpr int kStageElems = 2 * 4 * WK * RS; // K and V tiles of the four warps
   __shared__ int is_last;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [4][32][RS]
-  __nv_bfloat16* v_s = k_s + 4 * 32 * RS;                           // [4][32][RS]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2 stages][K|V][4][WK][RS]
 
   const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
   const int kv_len = base_len[b] + 1;
-  const int c0 = c * kMmaDecodeChunk;
+  const int c0 = c * chunk_keys;
   if (c0 >= kv_len) return;
+  SIAR_STAMP(0);
+  const int c_end = min(kv_len, c0 + chunk_keys);
+  const int n_it = (c_end - c0 + 4 * WK - 1) / (4 * WK);
   const int slot = slot_ids[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int w0 = c0 + warp * 32;                  // first key of this warp
-  const int valid = min(32, kv_len - w0);         // keys of this warp that exist (may be <= 0)
+  const int* table = block_table + (size_t)slot * max_pages;
 
-  __nv_bfloat16* kw = k_s + warp * 32 * RS;
-  __nv_bfloat16* vw = v_s + warp * 32 * RS;
-  if (valid > 0) {
-    const int page = block_table[(size_t)slot * max_pages + w0 / page_tokens];
+  auto load_tile = [&](int it, int stage) {
+    const int w0 = c0 + it * 4 * WK + warp * WK;
+    const int valid = min(WK, c_end - w0);
+    if (valid <= 0) return;
+    const int page = table[w0 / page_tokens];
     const size_t row0 = ((size_t)page * Hkv + kvh) * page_tokens + (w0 % page_tokens);
     const __nv_bfloat16* kg = k_pool + row0 * D;
     const __nv_bfloat16* vg = v_pool + row0 * D;
-    constexpr int CPR = D / 8;                    // 16-byte chunks per row
+    __nv_bfloat16* kw = tiles + stage * kStageElems + warp * WK * RS;
+    __nv_bfloat16* vw = kw + 4 * WK * RS;
 #pragma unroll
-    for (int it = 0; it < 32 * CPR / 32; ++it) {
-      const int id = it * 32 + lane;
+    for (int i = 0; i < WK * CPR / 32; ++i) {
+      const int id = i * 32 + lane;
       const int r = id / CPR, ch = id % CPR;
       const int ok = r < valid ? 16 : 0;
       const size_t goff = (size_t)(ok ? r : 0) * D + ch * 8;
       cp_async_16(smem_u32_generic(kw + r * RS + ch * 8), kg + goff, ok);
       cp_async_16(smem_u32_generic(vw + r * RS + ch * 8), vg + goff, ok);
     }
-  }
+  };
+  load_tile(0, 0);
   cp_async_commit();
 
   // query fragments straight from global memory: rows g and g + 8 of the (padded) group
@@ -89,22 +117,30 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
     }
   }
-  cp_async_wait<0>();
-  __syncwarp();
+  SIAR_STAMP(1);
 
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
   float o[D / 8][4];
 #pragma unroll
   for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  if (valid > 0) {
-    // S = Q K^T : 4 key tiles of 8
-    float s[4][4];
+  for (int it = 0; it < n_it; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_it) load_tile(it + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    if (it == 0) { SIAR_STAMP(2); }
+    const int valid = min(WK, c_end - (c0 + it * 4 * WK + warp * WK));
+    if (valid <= 0) continue;
+    const uint32_t kbase = smem_u32_generic(tiles + stage * kStageElems + warp * WK * RS);
+    const uint32_t vbase = kbase + 4 * WK * RS * 2;
+    // S = Q K^T : WK/8 key tiles of 8
+    float s[WK / 8][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const uint32_t kbase = smem_u32_generic(kw);
+    for (int j = 0; j < WK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; kk += 2) {
         uint32_t bfr[4];
@@ -114,10 +150,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
         mma_bf16_16816(s[j], qa[kk + 1], bfr[2], bfr[3]);
       }
     }
-    // mask, row maxima, exponentials
-    float mx[2] = {-INFINITY, -INFINITY};
+    // mask, running maxima, exponentials
+    float mx[2] = {m_row[0], m_row[1]};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = 8 * j + 2 * q + (e & 1);
@@ -128,9 +164,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     }
     mx[0] = quad_max(mx[0]);
     mx[1] = quad_max(mx[1]);
-    float sum[2] = {0.f, 0.f};
+    float alpha[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int h = 0; h < 2; ++h) alpha[h] = mx[h] == -INFINITY ? 1.f : expf(m_row[h] - mx[h]);
+#pragma unroll
+    for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - mx[e >> 1]);
@@ -138,12 +176,21 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
         sum[e >> 1] += p;
       }
     }
-    m_row[0] = mx[0]; m_row[1] = mx[1];
-    l_row[0] = quad_sum(sum[0]); l_row[1] = quad_sum(sum[1]);
-    // O = P V : 2 key steps of 16, D/8 dim tiles
-    const uint32_t vbase = smem_u32_generic(vw);
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
+    for (int h = 0; h < 2; ++h) {
+      l_row[h] = l_row[h] * alpha[h] + quad_sum(sum[h]);
+      m_row[h] = mx[h];
+    }
+    if (it > 0) {
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+        o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+      }
+    }
+    // O += P V : WK/16 key steps of 16, D/8 dim tiles
+#pragma unroll
+    for (int t = 0; t < WK / 16; ++t) {
       uint32_t pa[4] = {pack_bf16(s[2 * t][0], s[2 * t][1]), pack_bf16(s[2 * t][2], s[2 * t][3]),
                         pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]), pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3])};
 #pragma unroll
@@ -157,8 +204,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       }
     }
   }
+  cp_async_wait<0>();
 
   // join the four warps: reuse the tile memory as float buffers
+  SIAR_STAMP(3);
   __syncthreads();
   float* mo = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
   float* mm = mo + 4 * 16 * D;                                // [4][16]
@@ -174,7 +223,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     mm[warp * 16 + g + 8] = m_row[1]; ml[warp * 16 + g + 8] = l_row[1];
   }
   __syncthreads();
-  const int n_chunks = (kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+  const int n_chunks = (kv_len + chunk_keys - 1) / chunk_keys;
   __nv_bfloat16* orow = out + (size_t)q_start[b] * Hq * D + (size_t)kvh * G * D;
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int h = idx / D, d = idx % D;
@@ -199,6 +248,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       if (d == 0) { part_ml[pidx * 2] = mx; part_ml[pidx * 2 + 1] = lsum; }
     }
   }
+  SIAR_STAMP(4);
   if (n_chunks == 1) return;
 
   // The block of this (sequence, kv head) that finishes last joins the chunks' partials
@@ -211,21 +261,50 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     if (old == n_chunks - 1) counters[b * Hkv + kvh] = 0;
   }
   __syncthreads();
+  SIAR_STAMP(5);
   if (!is_last) return;
   __threadfence();
+  // weights of the chunks: wgt[h][c] = exp(m_c - max) / sum, formed once per head
+  float* cm = reinterpret_cast<float*>(smem_raw);            // [G][n_chunks] maxima, then weights
+  float* cl = cm + G * n_chunks;                              // [G][n_chunks] sums
+  const size_t pbase = ((size_t)b * Hq + kvh * G) * max_chunks;
+  for (int idx = threadIdx.x; idx < G * n_chunks; idx += blockDim.x) {
+    const int h = idx / n_chunks, cc = idx % n_chunks;
+    cm[idx] = __ldcg(part_ml + (pbase + (size_t)h * max_chunks + cc) * 2);
+    cl[idx] = __ldcg(part_ml + (pbase + (size_t)h * max_chunks + cc) * 2 + 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int h = threadIdx.x;
+    float mx = -INFINITY;
+    for (int cc = 0; cc < n_chunks; ++cc) mx = fmaxf(mx, cm[h * n_chunks + cc]);
+    float lsum = 0.f;
+    for (int cc = 0; cc < n_chunks; ++cc) {
+      const float f = expf(cm[h * n_chunks + cc] - mx);
+      lsum += cl[h * n_chunks + cc] * f;
+      cm[h * n_chunks + cc] = f;
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    for (int cc = 0; cc < n_chunks; ++cc) cm[h * n_chunks + cc] *= inv;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int h = idx / D, d = idx % D;
-    const size_t p0 = ((size_t)b * Hq + kvh * G + h) * max_chunks;
-    float mx = -INFINITY;
-    for (int cc = 0; cc < n_chunks; ++cc) mx = fmaxf(mx, __ldcg(part_ml + (p0 + cc) * 2));
-    float lsum = 0.f, acc = 0.f;
-    for (int cc = 0; cc < n_chunks; ++cc) {
-      const float f = expf(__ldcg(part_ml + (p0 + cc) * 2) - mx);
-      lsum += __ldcg(part_ml + (p0 + cc) * 2 + 1) * f;
-      acc += __ldcg(part_acc + (p0 + cc) * D + d) * f;
+    const float* pa = part_acc + (pbase + (size_t)h * max_chunks) * D + d;
+    float acc = 0.f;
+    int cc = 0;
+    for (; cc + 4 <= n_chunks; cc += 4) {
+      const float v0 = __ldcg(pa + (size_t)cc * D), v1 = __ldcg(pa + (size_t)(cc + 1) * D);
+      const float v2 = __ldcg(pa + (size_t)(cc + 2) * D), v3 = __ldcg(pa + (size_t)(cc + 3) * D);
+      acc += v0 * cm[h * n_chunks + cc];
+      acc += v1 * cm[h * n_chunks + cc + 1];
+      acc += v2 * cm[h * n_chunks + cc + 2];
+      acc += v3 * cm[h * n_chunks + cc + 3];
     }
-    orow[h * D + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    for (; cc < n_chunks; ++cc) acc += __ldcg(pa + (size_t)cc * D) * cm[h * n_chunks + cc];
+    orow[h * D + d] = __float2bfloat16_rn(acc);
   }
+  SIAR_STAMP(6);
 }
 
 // ------------------------------------------------------------------ prefill
@@ -404,15 +483,29 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   }
 }
 
+// Keys per decode block for a batch of B sequences with kv heads Hkv and lengths up to
+// max_kv_len: a multiple of 128, as large as still gives about eight blocks per SM, and
+// large enough that a sequence has at most 64 chunks.
+static int decode_chunk_keys(int B, int Hkv, int max_kv_len, int sm_count) {
+  const int tiles = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;       // 128-key tiles per sequence
+  long long want = ((long long)8 * sm_count + (long long)B * Hkv - 1) / ((long long)B * Hkv);   // chunks per sequence
+  if (want < 1) want = 1;
+  if (want > tiles) want = tiles;
+  int tiles_per_chunk = (int)((tiles + want - 1) / want);
+  if (tiles_per_chunk < (tiles + 63) / 64) tiles_per_chunk = (tiles + 63) / 64;
+  return tiles_per_chunk * kMmaDecodeChunk;
+}
+
 template <int D>
 static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                          const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
                          int* counters, int B, int Hq, int Hkv, int page_tokens, int max_pages, int max_kv_len,
-                         float scale, cudaStream_t s) {
-  const int max_chunks = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+                         int sm_count, float scale, cudaStream_t s) {
+  const int chunk_keys = decode_chunk_keys(B, Hkv, max_kv_len, sm_count);
+  const int max_chunks = (max_kv_len + chunk_keys - 1) / chunk_keys;
   float* part_ml = scratch;
   float* part_acc = scratch + (size_t)B * Hq * max_chunks * 2;
-  size_t smem = (size_t)2 * 4 * 32 * (D + kPad) * 2;
+  size_t smem = (size_t)2 * 2 * 4 * kDecodeWarpKeys * (D + kPad) * 2;       // two stages of K and V tiles
   const size_t merge = sizeof(float) * (4 * 16 * D + 2 * 4 * 16);
   if (merge > smem) smem = merge;
   auto kern = attn_decode_mma_kernel<D>;
@@ -425,7 +518,8 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   dim3 grid(max_chunks, Hkv, B);
   return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, part_ml, part_acc,
-                            counters, (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, max_chunks, scale);
+                            counters, (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, max_chunks, chunk_keys,
+                            scale);
 }
 
 template <int D>
@@ -453,7 +547,11 @@ using namespace siar;
 
 SIAR_DEFINE_PDL_SWITCH()
 
-extern "C" int siar_attn_mma_decode_chunk() { return kMmaDecodeChunk; }
+// Scratch floats siar_attn_mma_decode needs: the worst case is chunks of 128 keys.
+
+#ifdef SIAR_TIMING
+extern "C" void siar_attn_set_stamps(unsigned long long* p) { cudaMemcpyToSymbol(siar::g_attn_stamps, &p, sizeof(p)); }
+#endif
 
 // 1 when the tensor-core kernels take these sizes (bf16 only): head_dim 64 or 128, at most
 // 16 query heads per kv head, pages that hold whole key tiles.
@@ -462,8 +560,10 @@ extern "C" int siar_attn_mma_supported(int Hq, int Hkv, int D, int page_tokens) 
   return (D == 64 || D == 128) && (Hq / Hkv) <= 16 && page_tokens % kMmaKeyTile == 0;
 }
 
-extern "C" long long siar_attn_mma_decode_scratch_floats(int B, int Hq, int D, int max_kv_len) {
-  const long long chunks = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
+extern "C" long long siar_attn_mma_decode_scratch_floats(int B, int Hq, int Hkv, int D, int max_kv_len,
+                                                         int sm_count) {
+  const int chunk_keys = decode_chunk_keys(B, Hkv, max_kv_len, sm_count);
+  const long long chunks = (max_kv_len + chunk_keys - 1) / chunk_keys;
   return (long long)B * Hq * chunks * (D + 2);
 }
 
@@ -471,16 +571,16 @@ extern "C" long long siar_attn_mma_decode_scratch_floats(int B, int Hq, int D, i
 extern "C" int siar_attn_mma_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                                     const int* slot_ids, const int* q_start, const int* base_len, void* out,
                                     float* scratch, int* counters, int B, int Hq, int Hkv, int D, int page_tokens,
-                                    int max_pages, int max_kv_len, float scale, void* stream) {
+                                    int max_pages, int max_kv_len, int sm_count, float scale, void* stream) {
   if (B == 0) return 0;
   if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64)
     return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters,
-                             B, Hq, Hkv, page_tokens, max_pages, max_kv_len, scale, s);
+                             B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
   return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters, B,
-                            Hq, Hkv, page_tokens, max_pages, max_kv_len, scale, s);
+                            Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
 }
 
 extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,

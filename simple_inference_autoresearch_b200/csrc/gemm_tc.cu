@@ -497,6 +497,10 @@ static unsigned long long* g_stamps = nullptr;
 extern "C" void siar_gemm_tc_set_stamps(unsigned long long* p) { g_stamps = p; }
 #endif
 
+// Products with fewer output tiles than this many per SM are split along K.
+static int g_split_target = 1;
+extern "C" void siar_gemm_tc_set_split_target(int blocks_per_sm) { g_split_target = blocks_per_sm < 1 ? 1 : blocks_per_sm; }
+
 // Returns 0 on launch, a cudaError_t on failure, and -1 when the shape is one this
 // unit does not take (the caller then uses the CUDA-core kernel).
 //   A [M,K], W [N,K] bf16 row-major; C [M,N] bf16 (out_f32 == 0) or float32.
@@ -520,8 +524,8 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   const int tiles = ((P + kBM - 1) / kBM) * ((Q + BN - 1) / BN);
   const int num_kb = (K + kBK - 1) / kBK;
   int splits = 1;
-  if (swap && tiles < sm_count) {
-    splits = (sm_count + tiles - 1) / tiles;
+  if (swap && tiles < g_split_target * sm_count) {
+    splits = (g_split_target * sm_count + tiles - 1) / tiles;
     if (splits > 8) splits = 8;
     if (splits > max_splits) splits = max_splits;
     if (splits > num_kb / 4) splits = num_kb / 4;

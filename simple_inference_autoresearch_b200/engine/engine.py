@@ -127,11 +127,11 @@ class Engine:
         st = self._graph_state
         if st.capacity < b:
             self._graph_state = st = _GraphBuffers(self, b)
+        # A captured step serves lengths up to `bucket`; the attention grid and its chunking
+        # are fixed by it, so buckets are kept fine (512 keys) and a new graph is captured
+        # when the longest sequence crosses one.
         longest = max(self.cache.length(s) for s in slots) + 1
-        bucket = 1024
-        while bucket < longest:
-            bucket *= 2
-        bucket = min(bucket, self.max_seq_len)
+        bucket = min(-(-longest // 512) * 512, self.max_seq_len)
         if st.slots != slots or st.bucket != bucket:
             st.upload(requests, bucket)
         # the step's input tokens come from the host every step, as the caller gives them

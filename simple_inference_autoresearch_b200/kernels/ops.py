@@ -51,10 +51,10 @@ _signatures = {
         "siar_attn_mma_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
         "siar_attn_mma_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                 c_void_p],
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_void_p],
         "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
-        "siar_attn_mma_decode_chunk": [],
+        "siar_attn_mma_decode_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
     "sampling": {
         "siar_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -230,6 +230,15 @@ def check_attention_sizes(n_heads: int, n_kv_heads: int, head_dim: int) -> None:
 
 
 _counters = {}
+_sms = {}
+
+
+def _sm_count(device) -> int:
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _sms:
+        _sms[key] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sms[key]
 
 
 def _decode_counters(device, need: int) -> torch.Tensor:
@@ -285,16 +294,18 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
     mma = mma_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens)
     if meta.is_decode:
         if mma:
-            chunk = _fn("attention_mma", "siar_attn_mma_decode_chunk")()
-        else:
-            chunk = attention_limits()["decode_chunk"]
-        scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len, chunk),
-                              dtype=torch.float32, device=qkv.device)
-        if mma:
+            sms = _sm_count(qkv.device)
+            f = _fn("attention_mma", "siar_attn_mma_decode_scratch_floats")
+            f.restype = c_longlong
+            scratch = torch.empty(f(meta.n_seqs, n_heads, n_kv_heads, head_dim, meta.max_kv_len, sms),
+                                  dtype=torch.float32, device=qkv.device)
             _launch("attention_mma", "siar_attn_mma_decode", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
                     _ptr(scratch), _ptr(_decode_counters(qkv.device, meta.n_seqs * n_kv_heads)), *sizes,
-                    meta.max_kv_len, float(scale), _stream())
+                    meta.max_kv_len, sms, float(scale), _stream())
         else:
+            chunk = attention_limits()["decode_chunk"]
+            scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len, chunk),
+                                  dtype=torch.float32, device=qkv.device)
             _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
                     _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)
     elif mma:
