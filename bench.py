@@ -105,8 +105,9 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference's public API loads weights with huggingface_hub.snapshot_download "
-                          "(no network here), has no random-weights mode, and its kernels are Triton JIT"}))
+                          "pip cannot install the reference offline (setuptools: multiple top-level packages in a "
+                          "flat layout); its public API also downloads weights with huggingface_hub (no network) "
+                          "and it has no random-weights mode"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")

@@ -75,3 +75,25 @@ def write_model_folder(folder, config, seed: int, store_dtype: torch.dtype = tor
         json.dump(raw, f, indent=1)
     save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt", "seed": str(seed)})
     return folder
+
+
+def main(argv=None) -> int:
+    """``python -m simple_inference_autoresearch_b200.weights.random_init --config config.json --out DIR --seed 0``"""
+    import argparse
+
+    from .. import registry
+
+    ap = argparse.ArgumentParser(description="write a model folder with seeded random weights")
+    ap.add_argument("--config", required=True, help="a config.json (or a folder holding one)")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    args = ap.parse_args(argv)
+    _, config = registry.resolve_path(args.config)
+    folder = write_model_folder(args.out, config, args.seed, store_dtype=getattr(torch, args.dtype))
+    print(folder)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

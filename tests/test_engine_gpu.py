@@ -242,3 +242,14 @@ def test_programmatic_launch_on_and_off_give_the_same_tokens_and_logits(folders)
             ops.set_programmatic_launch(True)
     assert results[0][0] == results[1][0] == results[2][0]
     assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][1], results[2][1])
+
+
+def test_command_line(folders, capsys):
+    from simple_inference_autoresearch_b200 import inference
+    rc = inference.main(["--model", str(folders["A"]), "--prompt-ids", "5,17,3", "--max-new-tokens", "6",
+                         "--temperature", "0", "--dtype", "float32", "--ignore-eos"])
+    out = capsys.readouterr().out
+    assert rc == 0
+    first = [int(t) for t in out.splitlines()[0].split()]
+    assert first == plain_greedy(folders["A"], [5, 17, 3], 6)
+    assert "decode_tok_s" in out and "ttft_ms" in out and "prompt_tokens" in out
