@@ -597,3 +597,82 @@ extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const 
   return launch_prefill<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv,
                              page_tokens, max_pages, max_q_len, scale, s);
 }
+
+// ------------------------------------------------------------------ decode without allocation
+// See no_alloc.h.  One array in the shared object serves as the scratch of
+// siar_attn_mma_decode: the first SIAR_NOALLOC_MAX_PAIRS 32-bit words are the counters, the
+// rest holds the float partials.  In host code `noalloc_scratch` is only a handle for the
+// symbol, not a device address; the address comes from cudaGetSymbolAddress.
+#include "no_alloc.h"
+
+#include <stdio.h>
+
+static __device__ __align__(256) float noalloc_scratch[SIAR_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+static float* noalloc_base[64];   // device address of the array, per device, looked up once
+
+extern "C" long long siar_attn_mma_noalloc_max_floats(void) {
+  return (long long)(SIAR_NOALLOC_SCRATCH_BYTES / sizeof(float)) - SIAR_NOALLOC_MAX_PAIRS;
+}
+
+extern "C" int siar_attn_mma_decode_noalloc(const void* qkv, const void* k_pool, const void* v_pool,
+                                            const int* block_table, const int* slot_ids, const int* q_start,
+                                            const int* base_len, void* out, int B, int Hq, int Hkv, int D,
+                                            int page_tokens, int max_pages, int max_kv_len, int sm_count,
+                                            float scale, void* stream, char* message, int message_len) {
+  auto say = [&](const char* fmt, long long a, long long b) {
+    if (message != nullptr && message_len > 0) snprintf(message, (size_t)message_len, fmt, a, b);
+  };
+  if (message != nullptr && message_len > 0) message[0] = 0;
+  if (B <= 0) return 0;
+  if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || B > 65535 || max_kv_len <= 0 || sm_count <= 0) {
+    say("sizes not taken by the tensor-core decode attention (head_dim %lld, %lld query heads per kv head)",
+        (long long)D, (long long)(Hkv > 0 ? Hq / Hkv : 0));
+    return -2;
+  }
+  const long long need = siar_attn_mma_decode_scratch_floats(B, Hq, Hkv, D, max_kv_len, sm_count);
+  if (need > siar_attn_mma_noalloc_max_floats()) {
+    say("these sizes need %lld floats of scratch; the built-in array holds %lld", need,
+        siar_attn_mma_noalloc_max_floats());
+    return -3;
+  }
+  if ((long long)B * Hkv > SIAR_NOALLOC_MAX_PAIRS) {
+    say("%lld (sequence, kv head) pairs; the built-in array has counters for %lld", (long long)B * Hkv,
+        (long long)SIAR_NOALLOC_MAX_PAIRS);
+    return -3;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    say("cudaGetDevice failed or device index out of range (error %lld, device %lld)", (long long)e, (long long)dev);
+    return e != cudaSuccess ? (int)e : (int)cudaErrorInvalidDevice;
+  }
+  if (noalloc_base[dev] == nullptr) {
+    // set-up, once per device: the device address of the array on the current device
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      say("cudaGetSymbolAddress failed (error %lld) on device %lld", (long long)e, (long long)dev);
+      return e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol;
+    }
+    noalloc_base[dev] = ptr;
+  }
+  int* counters = reinterpret_cast<int*>(noalloc_base[dev]);
+  float* partials = noalloc_base[dev] + SIAR_NOALLOC_MAX_PAIRS;
+  cudaStream_t s = (cudaStream_t)stream;
+  // the counters must start at zero; an earlier call that was cut short may have left some
+  e = cudaMemsetAsync(counters, 0, sizeof(int) * (size_t)B * Hkv, s);
+  if (e != cudaSuccess) {
+    say("cudaMemsetAsync on the counters failed (error %lld) on device %lld", (long long)e, (long long)dev);
+    return (int)e;
+  }
+  int rc;
+  if (D == 64)
+    rc = launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, partials, counters, B,
+                           Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
+  else
+    rc = launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, partials, counters,
+                            B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
+  if (rc != 0) say("the kernel launch failed (error %lld) on device %lld", (long long)rc, (long long)dev);
+  return rc;
+}

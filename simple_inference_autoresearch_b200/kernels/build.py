@@ -77,7 +77,7 @@ def _build_dir() -> Path:
 def _fingerprint(unit: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for p in [CSRC / f"{unit}.cu"] + sorted(CSRC.glob("*.cuh")):
+    for p in [CSRC / f"{unit}.cu"] + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     return h.hexdigest()
