@@ -99,8 +99,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels in plain stream order (no programmatic dependent launch)")
-    ap.add_argument("--cuda-profiler-range", action="store_true",
-                    help="bracket the timed decode replays with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--cuda-profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                    help="bracket the timed decode replays (or the timed prefill steps) with cudaProfilerStart/Stop, "
+                         "for ncu --profile-from-start off")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -153,7 +154,11 @@ def main() -> int:
 
     for _ in range(2):
         prefill_once()
+    if args.cuda_profiler_range == "prefill":
+        torch.cuda.profiler.start()
     prefill_ms = statistics.median(prefill_once() for _ in range(3))
+    if args.cuda_profiler_range == "prefill":
+        torch.cuda.profiler.stop()
     h, i, v, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
     qkv_n = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
     lin_params = L * (qkv_n * h + h * cfg.num_attention_heads * cfg.head_dim + 3 * h * i)
@@ -190,14 +195,14 @@ def main() -> int:
         before = ops.launch_count
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
-        if args.cuda_profiler_range and e2e:
+        if args.cuda_profiler_range == "decode" and e2e:
             torch.cuda.profiler.start()
         e0.record()
         for _ in range(steps):
             graph.replay()
         e1.record()
         torch.cuda.synchronize()
-        if args.cuda_profiler_range and e2e:
+        if args.cuda_profiler_range == "decode" and e2e:
             torch.cuda.profiler.stop()
         dev_ms = e0.elapsed_time(e1) / steps
         launches = ops.launch_count - before
