@@ -113,6 +113,11 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) \
                : "r"(taddr))
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <typename TOut> __device__ __forceinline__ void store_out(TOut* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) {
@@ -401,6 +406,194 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   }
 }
 
+// ------------------------------------------------------------------ persistent kernel (many rows)
+// The prefill orientation (X = activations, C[p][q] = D[p][q]) as persistent blocks: one block
+// per SM walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tile rows fastest, so
+// that a wave of blocks shares weight tiles in L2).  Tensor memory holds TWO accumulators:
+// while the epilogue warps drain tile i from one, the MMA thread already fills the other with
+// tile i + 1, and the TMA thread runs ahead through the shared-memory ring.  The epilogue
+// stores straight from registers: each thread owns one tile row and writes 32 consecutive
+// outputs at a time with 16-byte stores.
+#define SIAR_TMEM_LD_32(taddr, r)                                                                                  \
+  asm volatile(                                                                                                    \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                    \
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28," \
+      "%29,%30,%31}, [%32];"                                                                                       \
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), \
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),     \
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),    \
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                  \
+      : "r"(taddr))
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int STAGES, typename TOut>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
+                          const GemmParams prm) {
+  constexpr uint32_t kXBytes = kBM * kBK * 2;
+  constexpr uint32_t kYBytes = BN * kBK * 2;
+  constexpr uint32_t kStageBytes = kXBytes + kYBytes;
+  constexpr uint32_t kTmemCols = 2 * BN;               // two accumulators
+
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  pdl_launch_dependents();
+  const uint32_t dyn = smem_u32(smem_dyn);
+  unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_p = (prm.P + kBM - 1) / kBM, tiles_q = (prm.Q + BN - 1) / BN;
+  const int n_tiles = tiles_p * tiles_q;
+  const int num_kb = (prm.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 1);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const bool dead = (*(volatile int*)prm.status & kStatusWaitExpired) != 0;
+
+  if (dead) {
+    // nothing
+  } else if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmY) : "memory");
+      pdl_wait();
+      int it = 0, issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int p0 = (t % tiles_p) * kBM, q0 = (t / tiles_p) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1) || *(volatile int*)&abort_flag) { ok = false; break; }
+          unsigned char* xs = tiles + (size_t)s * kStageBytes;
+          mbar_expect_tx(&full_bar[s], kStageBytes);
+          tma_load_2d(xs, &tmX, &full_bar[s], kb * kBK, p0);
+          tma_load_2d(xs + kXBytes, &tmY, &full_bar[s], kb * kBK, q0);
+          issued = it + 1;
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(BN);
+      int it = 0, i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++i) {
+        const int acc = i & 1;
+        // the epilogue has drained this accumulator (passes at once for the first two tiles)
+        if (!mbar_wait(&tempty_bar[acc], ((i >> 1) & 1) ^ 1) || *(volatile int*)&abort_flag) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph) || *(volatile int*)&abort_flag) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t xs = smem_u32(tiles + (size_t)s * kStageBytes);
+          const uint64_t da = smem_desc_sw128(xs), db = smem_desc_sw128(xs + kXBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_f16(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    TOut* C = (TOut*)prm.C;
+    pdl_wait();
+    const bool vec_ok = (prm.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) % 16) == 0);
+    int i = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
+      const int acc = i & 1;
+      const int p0 = (t % tiles_p) * kBM, q0 = (t / tiles_p) * BN;
+      if (!mbar_wait(&tfull_bar[acc], (i >> 1) & 1) || *(volatile int*)&abort_flag) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+        break;
+      }
+      tc_fence_after();
+      const int p = p0 + quad * 32 + lane;
+      TOut* crow = C + (long long)p * prm.ldc;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t r[32];
+        SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int q = q0 + ch * 32;
+        if (p < prm.P && q < prm.Q) {
+          if (vec_ok && q + 32 <= prm.Q) {
+            if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(crow + q + j) =
+                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                __uint_as_float(r[j + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                pk.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                pk.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                pk.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                pk.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                *reinterpret_cast<uint4*>(crow + q + j) = pk;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (q + j < prm.Q) store_out<TOut>(crow + q + j, __uint_as_float(r[j]));
+          }
+        }
+      }
+      // this accumulator may be overwritten once all four epilogue warps have read it
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -485,6 +678,22 @@ static int launch(const CUtensorMap& tmX, const CUtensorMap& tmY, const GemmPara
   return (int)cudaLaunchKernelEx(&cfg, kern, tmX, tmY, prm);
 }
 
+template <int BN, int STAGES, typename TOut>
+static int launch_persistent(const CUtensorMap& tmX, const CUtensorMap& tmY, const GemmParams& prm, int sm_count,
+                             cudaStream_t s) {
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK * 2 + BN * kBK * 2) + 1024;
+  auto kern = gemm_tc_persistent_kernel<BN, STAGES, TOut>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int n_tiles = ((prm.P + kBM - 1) / kBM) * ((prm.Q + BN - 1) / BN);
+  const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
+  return (int)launch_kernel(kern, dim3(blocks), dim3(192), smem, s, tmX, tmY, prm);
+}
+
 }  // namespace siar
 
 using namespace siar;
@@ -546,6 +755,13 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   prm.stamps = g_stamps;
 #endif
 
+  if (!swap) {
+    if (BN == 256)
+      return out_f32 ? launch_persistent<256, 4, float>(tmX, tmY, prm, sm_count, s)
+                     : launch_persistent<256, 4, __nv_bfloat16>(tmX, tmY, prm, sm_count, s);
+    return out_f32 ? launch_persistent<128, 6, float>(tmX, tmY, prm, sm_count, s)
+                   : launch_persistent<128, 6, __nv_bfloat16>(tmX, tmY, prm, sm_count, s);
+  }
 #define SIAR_GO(BN_, ST_)                                                                      \
   return out_f32 ? launch<BN_, ST_, float>(tmX, tmY, prm, splits, s)                           \
                  : launch<BN_, ST_, __nv_bfloat16>(tmX, tmY, prm, splits, s)
