@@ -157,12 +157,13 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
   pdl_launch_dependents();
   extern __shared__ float cs[];   // cos[half], sin[half]
   const int half = D >> 1;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) cs[i] = inv_freq != nullptr ? inv_freq[i] : 0.f;
+  const int flat = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+  for (int i = flat; i < half; i += nthreads) cs[i] = inv_freq != nullptr ? inv_freq[i] : 0.f;
   pdl_wait();
   const int t = blockIdx.x;
   const int b = find_sequence(q_start, B, t);
   const int pos = base_len[b] + (t - q_start[b]);
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+  for (int i = flat; i < half; i += nthreads) {
     float sn = 0.f, c = 1.f;
     if (inv_freq != nullptr) sincosf((float)pos * cs[i], &sn, &c);
     cs[i] = c;
@@ -175,7 +176,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     const int slot = slot_ids[b];
     const int page = block_table[(size_t)slot * max_pages + pos / page_tokens];
     if (page < 0 || page >= n_pages) {
-      if (threadIdx.x == 0) atomicOr(status, kStatusBadPage);
+      if (flat == 0) atomicOr(status, kStatusBadPage);
     } else {
       const size_t off = ((size_t)page * Hkv * page_tokens + (pos % page_tokens)) * D;   // kv head 0
       kdst = k_pool + off;
@@ -185,8 +186,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
   __syncthreads();
   const size_t head_stride = (size_t)page_tokens * D;   // between kv heads inside a page
   const int n_rot = Hq + (kdst != nullptr ? Hkv : 0);
-  // heads are dealt to the blocks of a token (gridDim.y of them: more than one when few tokens run)
-  for (int head = blockIdx.y; head < n_rot; head += gridDim.y) {
+  // Heads are dealt to the blocks of a token (gridDim.y of them: more than one when few tokens
+  // run) and, inside a block, to its threadIdx.y rows; threadIdx.x walks the pairs of a head.
+  const int hstep = gridDim.y * blockDim.y;
+  for (int head = blockIdx.y * blockDim.y + threadIdx.y; head < n_rot; head += hstep) {
     T* dst = head < Hq ? row + head * D : kdst + (size_t)(head - Hq) * head_stride;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
       const float a = to_f32(row[head * D + i]), c = to_f32(row[head * D + i + half]);
@@ -197,21 +200,22 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
   }
   if (vdst != nullptr) {
     const T* vrow = row + (size_t)(Hq + Hkv) * D;
-    for (int head = blockIdx.y; head < Hkv; head += gridDim.y)
+    for (int head = blockIdx.y * blockDim.y + threadIdx.y; head < Hkv; head += hstep)
       for (int i = threadIdx.x; i < D; i += blockDim.x) vdst[(size_t)head * head_stride + i] = vrow[head * D + i];
   }
 }
 
 // ------------------------------------------------------------------ SwiGLU
+// interleaved == 0: rows are [gate (I) | up (I)]; interleaved == 1: rows are (gate_0, up_0, gate_1, ...).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int interleaved) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
   if (j >= I) return;
-  const float g = to_f32(gu[row * 2 * I + j]);
-  const float u = to_f32(gu[row * 2 * I + I + j]);
+  const float g = to_f32(gu[row * 2 * I + (interleaved ? 2 * j : j)]);
+  const float u = to_f32(gu[row * 2 * I + (interleaved ? 2 * j + 1 : I + j)]);
   const float s = g / (1.f + expf(-g));
   out[row * I + j] = from_f32<T>(s * u);
 }
@@ -320,7 +324,8 @@ extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq,
   if (D % 2 != 0) return (int)cudaErrorInvalidValue;
   // many tokens: one block per token walks all heads; few tokens: several blocks share a token
   const int ysplit = N >= 256 ? 1 : (Hq + Hkv < 16 ? Hq + Hkv : 16);
-  const int threads = D / 2 > 64 ? 128 : D / 2 > 32 ? 64 : 32;   // one pass over the D/2 pairs of a head
+  const int tx = D / 2 > 64 ? 128 : D / 2 > 32 ? 64 : 32;   // one pass over the D/2 pairs of a head
+  const dim3 threads(tx, ysplit == 1 ? 256 / tx : 1);        // many tokens: several heads at a time per block
   const size_t smem = sizeof(float) * D;
   if (is_bf16)
     launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(N, ysplit), dim3(threads), smem, s, (__nv_bfloat16*)qkv, inv_freq,
@@ -333,19 +338,19 @@ extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq,
   LAUNCH_END();
 }
 
-extern "C" int siar_swiglu(int is_bf16, const void* gu, void* out, int N, int I, void* stream) {
+extern "C" int siar_swiglu(int is_bf16, const void* gu, void* out, int N, int I, int interleaved, void* stream) {
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  if (is_bf16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) % 16) == 0) {
+  if (!interleaved && is_bf16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) % 16) == 0) {
     dim3 grid8(N, (I / 8 + 255) / 256);
     launch_kernel(swiglu_bf16x8_kernel, grid8, dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
     LAUNCH_END();
   }
   dim3 grid(N, (I + 255) / 256);
   if (is_bf16)
-    launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+    launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, interleaved);
   else
-    launch_kernel(swiglu_kernel<float>, grid, 256, 0, s, (const float*)gu, (float*)out, I);
+    launch_kernel(swiglu_kernel<float>, grid, 256, 0, s, (const float*)gu, (float*)out, I, interleaved);
   LAUNCH_END();
 }
 

@@ -113,6 +113,10 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) \
                : "r"(taddr))
 
+// silu(g) * u in 32-bit, the reference's SwiGLU (kernels/swiglu_kernel.py:139-140), here applied to
+// the float32 accumulators of the gate/up product before anything is rounded.
+__device__ __forceinline__ float swiglu_f(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -132,6 +136,7 @@ struct GemmParams {
   int transpose_out;  // 0: C[p][q], 1: C[q][p]
   int kb_per_split;   // k-blocks of 64 per split
   int x_is_weight;    // X is written by no kernel (swap-AB): its tiles may load before pdl_wait()
+  int swiglu;         // weight rows interleaved (gate_j, up_j): write silu(gate) * up, half as many outputs
 #ifdef SIAR_TIMING
   unsigned long long* stamps;   // [blocks][8] globaltimer marks, for profiling builds only
 #endif
@@ -360,7 +365,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   } else if (warp >= 2 && !dead) {
     const int et = threadIdx.x - 64;          // 0..127
     const int ew = et >> 5;
-    if (prm.transpose_out) {
+    if (prm.transpose_out && prm.swiglu) {
+      // tile rows are weight rows (gate_j, up_j, gate_j+1, ...): even rows write silu(gate) * up
+      const int pp = p0 + et;
+      if ((et & 1) == 0 && pp + 1 < prm.P) {
+        const int cols = min(BN, prm.Q - q0);
+        for (int jq = 0; jq < cols; ++jq)
+          store_out<TOut>(C + (long long)(q0 + jq) * prm.ldc + (pp >> 1),
+                          swiglu_f(stage[et * LD + jq], stage[(et + 1) * LD + jq]));
+      }
+    } else if (prm.transpose_out) {
       // C[q][p]: for a fixed q the 128 tile rows are contiguous
       const int pp = p0 + et;
       if (pp < prm.P) {
@@ -535,7 +549,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     const int quad = warp & 3;
     TOut* C = (TOut*)prm.C;
     pdl_wait();
-    const bool vec_ok = (prm.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) % 16) == 0);
+    // with the SwiGLU epilogue a 32-column chunk becomes 16 outputs: rows must stay 16-byte aligned
+    const bool vec_ok = (prm.ldc % (prm.swiglu ? 16 : 8) == 0) && ((reinterpret_cast<uintptr_t>(C) % 16) == 0);
     int i = 0;
     for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
       const int acc = i & 1;
@@ -554,7 +569,32 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int q = q0 + ch * 32;
-        if (p < prm.P && q < prm.Q) {
+        if (prm.swiglu) {
+          // columns are (gate_j, up_j) pairs: 16 outputs from these 32 accumulators
+          if (p < prm.P && q < prm.Q) {
+            TOut* orow = crow + (q >> 1);
+            if (vec_ok && q + 32 <= prm.Q && sizeof(TOut) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 16) {
+                uint4 pk;
+                pk.x = pack_bf16x2(swiglu_f(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                                   swiglu_f(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+                pk.y = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                                   swiglu_f(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+                pk.z = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 8]), __uint_as_float(r[j + 9])),
+                                   swiglu_f(__uint_as_float(r[j + 10]), __uint_as_float(r[j + 11])));
+                pk.w = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 12]), __uint_as_float(r[j + 13])),
+                                   swiglu_f(__uint_as_float(r[j + 14]), __uint_as_float(r[j + 15])));
+                *reinterpret_cast<uint4*>(orow + (j >> 1)) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 2)
+                if (q + j + 1 < prm.Q)
+                  store_out<TOut>(orow + (j >> 1), swiglu_f(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+            }
+          }
+        } else if (p < prm.P && q < prm.Q) {
           if (vec_ok && q + 32 <= prm.Q) {
             if constexpr (sizeof(TOut) == 4) {
 #pragma unroll
@@ -714,9 +754,13 @@ extern "C" void siar_gemm_tc_set_split_target(int blocks_per_sm) { g_split_targe
 // unit does not take (the caller then uses the CUDA-core kernel).
 //   A [M,K], W [N,K] bf16 row-major; C [M,N] bf16 (out_f32 == 0) or float32.
 //   max_splits caps the split along K (1 = never split; at most 8, the portable cluster size).
+//   epilogue 1: W's rows are interleaved (gate_0, up_0, gate_1, up_1, ...) and C [M, N/2] bf16 receives
+//   silu(gate) * up (never split along K).
 extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
-                                 int max_splits, int* status, int sm_count, void* stream) {
+                                 int max_splits, int epilogue, int* status, int sm_count, void* stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (epilogue != 0 && (epilogue != 1 || out_f32 || (N & 1))) return -1;
+  if (epilogue == 1) max_splits = 1;
   if (K % 8 != 0 || K < 8) return -1;                       // TMA needs 16-byte row strides
   if (((uintptr_t)A | (uintptr_t)W) & 15) return -1;
   cudaStream_t s = (cudaStream_t)stream;
@@ -747,7 +791,8 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   prm.C = C;
   prm.status = status;
   prm.P = P; prm.Q = Q; prm.K = K;
-  prm.ldc = N;
+  prm.ldc = epilogue == 1 ? N / 2 : N;
+  prm.swiglu = epilogue == 1 ? 1 : 0;
   prm.transpose_out = swap ? 1 : 0;
   prm.kb_per_split = kbps;
   prm.x_is_weight = swap ? 1 : 0;

@@ -26,7 +26,7 @@ def _bind():
         lib = build.load_unit("gemm_tc")
         f = lib.siar_gemm_tc_bf16
         c = ctypes
-        f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+        f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                       c.c_void_p, c.c_int, c.c_void_p]
         f.restype = c.c_int
         _fn = f
@@ -42,8 +42,9 @@ def _device_state(device: torch.device):
     return st
 
 
-def try_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    """out[M, N] = x[M, K] @ w[N, K]^T; False when the shape is refused (nothing launched)."""
+def try_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> bool:
+    """out[M, N] = x[M, K] @ w[N, K]^T; False when the shape is refused (nothing launched).
+    ``epilogue=1``: w's rows alternate (gate, up) and out[M, N/2] = silu(gate) * up."""
     if not enabled:
         return False
     from . import ops
@@ -53,7 +54,7 @@ def try_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     n = w.shape[0]
     st = _device_state(x.device)
     err = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32), max_splits,
-             ops.status_word(x.device).data_ptr(), st["sms"], torch.cuda.current_stream().cuda_stream)
+             int(epilogue), ops.status_word(x.device).data_ptr(), st["sms"], torch.cuda.current_stream().cuda_stream)
     if err == -1:
         return False
     if err != 0:

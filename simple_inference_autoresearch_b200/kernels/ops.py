@@ -32,7 +32,7 @@ _signatures = {
         "siar_rope_kv_write": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p],
-        "siar_swiglu": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "siar_swiglu": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "siar_advance_lengths": [c_void_p, c_void_p, c_int, c_void_p],
     },
     "gemm_simt": {
@@ -317,15 +317,31 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
     return out
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(gate) * up for rows laid out as [gate (I) | up (I)]."""
+def swiglu(gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """silu(gate) * up.  Rows are laid out as [gate (I) | up (I)], or with ``interleaved`` as
+    (gate_0, up_0, gate_1, up_1, ...)."""
     _need_cuda(gate_up)
     assert gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0 and gate_up.is_contiguous()
     n, two_i = gate_up.shape
     out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _launch("elementwise", "siar_swiglu", _is_bf16(gate_up.dtype), _ptr(gate_up), _ptr(out), n, two_i // 2,
-            _stream())
+            int(interleaved), _stream())
     return out
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+    """silu(x @ Wg^T) * (x @ Wu^T) for a weight whose rows alternate (gate_0, up_0, gate_1, ...);
+    returns [M, N/2] in x's dtype.  On the bfloat16 path the activation runs in the product's
+    epilogue on the float32 accumulators; otherwise it is a product followed by ``swiglu``."""
+    _need_cuda(x, w_interleaved)
+    assert x.dim() == 2 and w_interleaved.dim() == 2 and x.shape[1] == w_interleaved.shape[1]
+    assert w_interleaved.shape[0] % 2 == 0 and x.dtype == w_interleaved.dtype
+    if x.dtype == torch.bfloat16:
+        from . import gemm_tc
+        out = torch.empty((x.shape[0], w_interleaved.shape[0] // 2), dtype=x.dtype, device=x.device)
+        if gemm_tc.try_linear(x, w_interleaved, out, epilogue=1):
+            return out
+    return swiglu(linear(x, w_interleaved, x.dtype), interleaved=True)
 
 
 def advance_lengths(base_len: torch.Tensor, q_start: torch.Tensor, n_seqs: int) -> None:

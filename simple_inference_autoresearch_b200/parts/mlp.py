@@ -1,11 +1,14 @@
 """SwiGLU feed-forward.
 
-    gu = x [W_gate; W_up]^T      (one product; rows [0, I) gate, [I, 2I) up)
+    gu = x [W_gate; W_up]^T      (one product)
     f  = silu(gate) * up,  silu(g) = g * sigmoid(g)
     m  = f W_down^T
 
-as the reference's MLP (ops/mlp.py:98-129,179-214; kernels/swiglu_kernel.py:139-140).
-The activation is computed in 32-bit from the stored ``gu`` and rounded once.
+as the reference's MLP (ops/mlp.py:98-129,179-214; kernels/swiglu_kernel.py:139-140).  The
+reference stacks the two weights as halves (rows [0, I) gate, [I, 2I) up); here their rows
+alternate (gate_0, up_0, gate_1, up_1, ...), so that a tile of the product holds gate and up
+of the same outputs and the activation can run in the product's epilogue, in 32-bit on the
+accumulators, with one rounding of ``f`` (the reference's unfused path rounds ``gu`` first).
 """
 
 from __future__ import annotations
@@ -37,14 +40,13 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]],
-                                   dim=0).contiguous()
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
         self.w_down = tensors[p + "down_proj.weight"].contiguous()
 
     def extension_units(self):
         return ("elementwise", "gemm_simt", "gemm_tc")
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        gu = ops.linear(x, self.w_gate_up, ctx.dtype)
-        f = ops.swiglu(gu)
+        f = ops.linear_swiglu(x, self.w_gate_up)
         return ops.linear(f, self.w_down, torch.float32)

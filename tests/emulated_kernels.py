@@ -108,10 +108,15 @@ def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale):
     return out.to(qkv.dtype)
 
 
-def swiglu(gate_up):
+def swiglu(gate_up, interleaved=False):
     i = gate_up.shape[1] // 2
-    g, u = gate_up[:, :i].to(torch.float32), gate_up[:, i:].to(torch.float32)
+    x = gate_up.to(torch.float32)
+    g, u = (x[:, 0::2], x[:, 1::2]) if interleaved else (x[:, :i], x[:, i:])
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
+
+
+def linear_swiglu(x, w_interleaved):
+    return swiglu(linear(x, w_interleaved, torch.float32), interleaved=True).to(x.dtype)
 
 
 def advance_lengths(base_len, q_start, n_seqs):
@@ -137,6 +142,6 @@ def install(monkeypatch) -> None:
     """Swaps the functions above in for the CUDA ones (CPU tests of engine logic)."""
     from simple_inference_autoresearch_b200.kernels import ops
 
-    for name in ("embed", "gather_rows", "add_rmsnorm", "linear", "rope_kv_write", "attention", "swiglu",
+    for name in ("embed", "gather_rows", "add_rmsnorm", "linear", "linear_swiglu", "rope_kv_write", "attention", "swiglu",
                  "advance_lengths", "sample", "check_status"):
         monkeypatch.setattr(ops, name, globals()[name])

@@ -109,12 +109,30 @@ def test_linear_fp32_rows_do_not_depend_on_batch():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu(dtype):
-    gu = rnd(5, 2 * 176, dtype=dtype, scale=2.0)
-    out = ops.swiglu(gu.to(DEV))
-    ref = emu.swiglu(gu)
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("i", [176, 331, 14336])
+def test_swiglu(dtype, interleaved, i):
+    gu = rnd(5, 2 * i, dtype=dtype, scale=2.0)
+    out = ops.swiglu(gu.to(DEV), interleaved)
+    ref = emu.swiglu(gu, interleaved)
     torch.testing.assert_close(out.cpu().float(), ref.float(), **(dict(rtol=1e-5, atol=1e-6)
                                if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,i,k", [(1, 176, 64), (8, 14336, 512), (70, 136, 80), (64, 256, 96), (130, 331, 96),
+                                   (300, 1024, 264), (2048, 512, 128), (5, 44, 20)])
+def test_linear_with_swiglu_epilogue(dtype, m, i, k):
+    """The fused product + activation (tensor cores, both orientations) and its unfused fallback."""
+    x = rnd(m, k, dtype=dtype, seed=1)
+    w = rnd(2 * i, k, dtype=dtype, seed=2, scale=0.2)
+    out = ops.linear_swiglu(x.to(DEV), w.to(DEV))
+    ops.check_status(DEV)
+    assert out.shape == (m, i) and out.dtype == dtype
+    ref = emu.swiglu(emu.linear(x, w, torch.float32), interleaved=True)
+    # float32: gate * up multiplies two sums of k terms, so rounding of the sums shows scaled by the other factor
+    torch.testing.assert_close(out.cpu().float(), ref, **(dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32
+                                                          else dict(rtol=2e-2, atol=2e-2)))
 
 
 # ----------------------------------------------------------------------------- attention over the cache

@@ -53,6 +53,10 @@ def test_held_dtypes(tmp_path, dtype):
     p = "model.layers.1.self_attn."
     want = torch.cat([w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"]]).to(dtype)
     assert torch.equal(m.layers[1].mixer.w_qkv, want)
+    # gate and up rows alternate in the merged feed-forward weight
+    q = "model.layers.1.mlp."
+    gu = m.layers[1].ffn.w_gate_up
+    assert torch.equal(gu[0::2], w[q + "gate_proj.weight"].to(dtype)) and torch.equal(gu[1::2], w[q + "up_proj.weight"].to(dtype))
 
 
 def test_tied_head_is_the_embedding(tmp_path):
