@@ -380,6 +380,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   // the furthest key any row of this warp sees (warp-uniform)
   const int warp_last_row = min(rows_here - 1, warp * 16 + 15);
   const int warp_kv_end = warp * 16 < rows_here ? base + (row0 + warp_last_row) / G + 1 : 0;
+  // the nearest limit of any row of this warp (rows past rows_here count as 0: always masked)
+  const int warp_kv_min = warp * 16 + 15 < rows_here ? base + (row0 + warp * 16) / G + 1 : 0;
+  const float sl2 = scale * 1.4426950408889634f;
 
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
   float o[D / 8][4];
@@ -415,27 +418,33 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
           mma_bf16_16816(s[j], qa[kk + 1], bfr[2], bfr[3]);
         }
       }
-      float mx[2] = {m_row[0], m_row[1]};
+      // Softmax in the base-2 domain: with c = scale * log2(e), exp(s * scale - m) = 2^(s c - m c),
+      // one FFMA and one EX2 per score; m_row holds the running maximum of s * c.  Keys past a
+      // row's own position are masked only in the tiles that reach that far (warp-uniform test).
+      if (j0 + kMmaKeyTile > warp_kv_min) {
 #pragma unroll
-      for (int j = 0; j < kMmaKeyTile / 8; ++j) {
+        for (int j = 0; j < kMmaKeyTile / 8; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = j0 + 8 * j + 2 * q + (e & 1);
-          const float v = key < kv_end[e >> 1] ? s[j][e] * scale : -INFINITY;
-          s[j][e] = v;
-          mx[e >> 1] = fmaxf(mx[e >> 1], v);
-        }
+          for (int e = 0; e < 4; ++e)
+            if (j0 + 8 * j + 2 * q + (e & 1) >= kv_end[e >> 1]) s[j][e] = -INFINITY;
       }
-      mx[0] = quad_max(mx[0]);
-      mx[1] = quad_max(mx[1]);
-      float alpha[2], sum[2] = {0.f, 0.f};
+      float raw[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int h = 0; h < 2; ++h) alpha[h] = mx[h] == -INFINITY ? 1.f : expf(m_row[h] - mx[h]);
+      for (int j = 0; j < kMmaKeyTile / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) raw[e >> 1] = fmaxf(raw[e >> 1], s[j][e]);
+      float mx[2], alpha[2], neg_m[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(m_row[h], quad_max(raw[h]) * sl2);
+        alpha[h] = mx[h] == -INFINITY ? 1.f : fast_exp2(m_row[h] - mx[h]);
+        neg_m[h] = mx[h] == -INFINITY ? 0.f : -mx[h];
+      }
 #pragma unroll
       for (int j = 0; j < kMmaKeyTile / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - mx[e >> 1]);
+          const float p = fast_exp2(fmaf(s[j][e], sl2, neg_m[e >> 1]));   // 2^(-inf) = 0 for masked keys
           s[j][e] = p;
           sum[e >> 1] += p;
         }
@@ -445,10 +454,13 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
         l_row[h] = l_row[h] * alpha[h] + quad_sum(sum[h]);
         m_row[h] = mx[h];
       }
+      // the output only needs rescaling when some row's maximum moved (rare after the first tiles)
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-      for (int j = 0; j < D / 8; ++j) {
-        o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
-        o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+        for (int j = 0; j < D / 8; ++j) {
+          o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+          o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+        }
       }
       const uint32_t vbase = smem_u32_generic(v_s + stage * kMmaKeyTile * RS);
 #pragma unroll
