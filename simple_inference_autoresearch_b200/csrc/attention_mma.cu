@@ -26,6 +26,8 @@ namespace siar {
 constexpr int kPad = 8;             // bf16 elements of padding per shared-memory row (16 bytes)
 constexpr int kMmaDecodeChunk = 128;   // granularity of a decode block's key range
 constexpr int kDecodeWarpKeys = 16;    // keys per warp and pipeline step in the decode kernel
+constexpr int kDecodeStages = 3;       // pipeline depth per warp
+constexpr int kDecodeBlocksPerSM = 2;  // what shared memory allows with that depth
 constexpr int kMmaPrefillRows = 64;
 constexpr int kMmaKeyTile = 64;
 
@@ -46,8 +48,8 @@ __device__ __forceinline__ unsigned long long gtime() {
 // ------------------------------------------------------------------ decode
 // grid (chunks, Hkv, B), 128 threads.  A block owns `chunk_keys` consecutive keys of one
 // (sequence, kv head); warp w walks keys [c0 + 64 it + 16 w, +16) for it = 0, 1, ... with a
-// running (max, sum, output) per query head, its two shared-memory stages filled by cp.async
-// one step ahead (small stages, so that three blocks fit on an SM).  chunk_keys is a multiple of 128 chosen by the host so that the grid fills
+// running (max, sum, output) per query head, its kDecodeStages shared-memory stages filled by
+// cp.async kDecodeStages - 1 steps ahead (small stages, so that two blocks fit on an SM).  chunk_keys is a multiple of 128 chosen by the host so that the grid fills
 // the GPU: one chunk per sequence when the batch alone gives enough blocks, 128-key chunks
 // for a single sequence.
 template <int D>
@@ -66,7 +68,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   constexpr int kStageElems = 2 * 4 * WK * RS; // K and V tiles of the four warps
   __shared__ int is_last;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2 stages][K|V][4][WK][RS]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [kDecodeStages][K|V][4][WK][RS]
 
   const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
@@ -101,8 +103,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       cp_async_16(smem_u32_generic(vw + r * RS + ch * 8), vg + goff, ok);
     }
   };
-  load_tile(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int pre = 0; pre < kDecodeStages - 1; ++pre) {
+    if (pre < n_it) load_tile(pre, pre);
+    cp_async_commit();
+  }
 
   // query fragments straight from global memory: rows g and g + 8 of the (padded) group
   uint32_t qa[D / 16][4];
@@ -125,10 +130,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
   for (int it = 0; it < n_it; ++it) {
-    const int stage = it & 1;
-    if (it + 1 < n_it) load_tile(it + 1, stage ^ 1);
+    const int stage = it % kDecodeStages;
+    if (it + kDecodeStages - 1 < n_it) load_tile(it + kDecodeStages - 1, (it + kDecodeStages - 1) % kDecodeStages);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<kDecodeStages - 1>();
     __syncwarp();
     if (it == 0) { SIAR_STAMP(2); }
     const int valid = min(WK, c_end - (c0 + it * 4 * WK + warp * WK));
@@ -496,15 +501,15 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
 }
 
 // Keys per decode block for a batch of B sequences with kv heads Hkv and lengths up to
-// max_kv_len: a multiple of 128 (t tiles of 128 keys).  Three blocks fit on an SM; a block
+// max_kv_len: a multiple of 128 (t tiles of 128 keys).  kDecodeBlocksPerSM blocks fit on an SM; a block
 // costs a fixed part (set-up, joining its warps, the partial, the counter) plus a part per
-// tile, and blocks run in waves of 3 * sm_count.  The t with the smallest estimate wins, with
+// tile, and blocks run in waves of kDecodeBlocksPerSM * sm_count.  The t with the smallest estimate wins, with
 // at most 64 chunks per sequence.  (Measured on B200: about 6 us fixed and 2.8 us per tile
 // with three blocks sharing an SM's bandwidth.)
 static int decode_chunk_keys(int B, int Hkv, int max_kv_len, int sm_count) {
   const int tiles = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
   const long long pairs = (long long)B * Hkv;
-  const long long slots = 3ll * sm_count;
+  const long long slots = (long long)kDecodeBlocksPerSM * sm_count;
   int best_t = tiles;
   double best = 1e30;
   for (int t = (tiles + 63) / 64; t <= tiles; ++t) {
@@ -526,7 +531,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   const int max_chunks = (max_kv_len + chunk_keys - 1) / chunk_keys;
   float* part_ml = scratch;
   float* part_acc = scratch + (size_t)B * Hq * max_chunks * 2;
-  size_t smem = (size_t)2 * 2 * 4 * kDecodeWarpKeys * (D + kPad) * 2;       // two stages of K and V tiles
+  size_t smem = (size_t)kDecodeStages * 2 * 4 * kDecodeWarpKeys * (D + kPad) * 2;       // stages of K and V tiles
   const size_t merge = sizeof(float) * (4 * 16 * D + 2 * 4 * 16);
   if (merge > smem) smem = merge;
   auto kern = attn_decode_mma_kernel<D>;
