@@ -143,11 +143,14 @@ class Engine:
         if g is None:
             g = self._graphs[key] = _DecodeGraph(self, st, b, bucket)
         g.replay()
+        # one synchronisation for both read-backs: the sampled tokens and the kernels' status word
         st.host_tokens[:b].copy_(st.tokens[:b], non_blocking=True)
+        st.host_status.copy_(ops.status_word(self.device), non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.cache.commit(slots, [1] * b)
         out = st.host_tokens[:b].tolist()
-        ops.check_status(self.device)
+        if int(st.host_status[0]):
+            ops.check_status(self.device)      # raises with the kernels' message and clears the word
         return out
 
     # ------------------------------------------------------------------ generation
@@ -209,6 +212,7 @@ class _GraphBuffers:
         self.seeds = z(capacity, torch.int64)
         self.host_tokens = torch.zeros(capacity, dtype=torch.int32).pin_memory()
         self.host_in = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.host_status = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.engine = engine
         self.slots: Optional[List[int]] = None
         self.bucket = 0

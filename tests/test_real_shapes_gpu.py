@@ -1,0 +1,39 @@
+"""The three shipped presets' layer shapes (Llama-3.2-1B: head_dim 64, tied embeddings;
+Llama-3.2-3B: three query heads per kv head; Llama-3.1-8B) with two layers and random weights:
+the bfloat16 path (tensor-core products and attention at their real tile sizes) against the
+library's own float32 path, which the other tests tie to the plain implementation.  Unequal
+prompts in one step, then single tokens."""
+
+import dataclasses
+
+import pytest
+import torch
+
+import simple_inference_autoresearch_b200 as siar
+from simple_inference_autoresearch_b200 import StepEntry
+from simple_inference_autoresearch_b200.config import LlamaConfig, preset_path
+from tests.test_engine_gpu import REL_TOL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("preset", ["llama-3.2-1b", "llama-3.2-3b", "llama-3.1-8b"])
+def test_bfloat16_path_at_real_layer_shapes(preset):
+    cfg = dataclasses.replace(LlamaConfig.from_json(preset_path(preset)), num_hidden_layers=2)
+    g = torch.Generator().manual_seed(0)
+    reqs = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 77, 513)]
+    outs = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        loaded = siar.init_random(siar.build_model(cfg, dtype, "cuda"), seed=1)
+        eng = siar.Engine(loaded.model, max_batch=3, max_seq_len=1024, use_cuda_graph=False)
+        slots = [eng.open() for _ in reqs]
+        o = [eng.step([StepEntry(s, r[:-3], [0, len(r) - 4]) for s, r in zip(slots, reqs)])]
+        for k in range(3):
+            o.append(eng.step([StepEntry(s, [r[len(r) - 3 + k]], [0]) for s, r in zip(slots, reqs)]))
+        outs[dtype] = torch.cat(o).float().cpu()
+        del eng, loaded
+        torch.cuda.empty_cache()
+    ref, got = outs[torch.float32], outs[torch.bfloat16]
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs().max().item()
+    assert err <= REL_TOL[torch.bfloat16] * ref.abs().max().item(), err
