@@ -31,6 +31,10 @@ NVCC_FLAGS = [
     "-shared", "-Xcompiler", "-fPIC",
 ]
 
+#: extra nvcc flags for profiling builds, e.g. SIAR_NVCC_FLAGS="-DSIAR_TIMING" compiles the
+#: globaltimer stamps into the product and attention kernels (separate build folder per flag set)
+EXTRA_FLAGS = os.environ.get("SIAR_NVCC_FLAGS", "").split()
+
 #: every unit of the library, in the order ``build_all`` compiles them
 ALL_UNITS = ("elementwise", "gemm_simt", "attention", "attention_mma", "sampling", "gemm_tc")
 
@@ -61,7 +65,7 @@ def _nvcc() -> str:
 
 def _build_dir() -> Path:
     """In-tree ``csrc/_build`` when it can be written, else a per-user temp folder."""
-    d = CSRC / "_build"
+    d = CSRC / ("_build" if not EXTRA_FLAGS else "_build_" + hashlib.sha256(" ".join(EXTRA_FLAGS).encode()).hexdigest()[:8])
     try:
         d.mkdir(exist_ok=True)
         probe = d / f".w{os.getpid()}"
@@ -76,7 +80,7 @@ def _build_dir() -> Path:
 
 def _fingerprint(unit: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + EXTRA_FLAGS).encode())
     for p in [CSRC / f"{unit}.cu"] + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
         h.update(p.name.encode())
         h.update(p.read_bytes())
@@ -88,7 +92,7 @@ def _compile(unit: str, out: Path) -> None:
     if not src.exists():
         raise ExtensionError(f"no such CUDA unit: {src}")
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp), str(src)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *EXTRA_FLAGS, "-I", str(CSRC), "-o", str(tmp), str(src)]
     _say(f"compiling {src.name} for sm_100a ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
