@@ -61,7 +61,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int page_tokens,
                        int max_pages, int max_chunks, int chunk_keys, float scale) {
   pdl_launch_dependents();
+  SIAR_TRACE(20, 0);
   pdl_wait();
+  SIAR_TRACE(20, 2);
   constexpr int RS = D + kPad;                 // row stride in elements
   constexpr int CPR = D / 8;                   // 16-byte pieces per row
   constexpr int WK = kDecodeWarpKeys;          // keys per warp and step
@@ -83,11 +85,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   const int g = lane >> 2, q = lane & 3;
   const int* table = block_table + (size_t)slot * max_pages;
 
-  auto load_tile = [&](int it, int stage) {
+  // The page of a tile is read from the block table one step before the tile is requested, so
+  // that the (dependent) table read never sits in front of the loads it feeds.
+  auto page_of = [&](int it) {
+    const int w0 = c0 + it * 4 * WK + warp * WK;
+    return w0 < c_end ? __ldg(table + w0 / page_tokens) : 0;
+  };
+  auto load_tile = [&](int it, int stage, int page) {
     const int w0 = c0 + it * 4 * WK + warp * WK;
     const int valid = min(WK, c_end - w0);
     if (valid <= 0) return;
-    const int page = table[w0 / page_tokens];
     const size_t row0 = ((size_t)page * Hkv + kvh) * page_tokens + (w0 % page_tokens);
     const __nv_bfloat16* kg = k_pool + row0 * D;
     const __nv_bfloat16* vg = v_pool + row0 * D;
@@ -103,11 +110,15 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       cp_async_16(smem_u32_generic(vw + r * RS + ch * 8), vg + goff, ok);
     }
   };
+  int pages[kDecodeStages];
+#pragma unroll
+  for (int pre = 0; pre < kDecodeStages; ++pre) pages[pre] = page_of(pre);
 #pragma unroll
   for (int pre = 0; pre < kDecodeStages - 1; ++pre) {
-    if (pre < n_it) load_tile(pre, pre);
+    if (pre < n_it) load_tile(pre, pre, pages[pre]);
     cp_async_commit();
   }
+  int page_ahead = pages[kDecodeStages - 1];      // page of tile it + kDecodeStages - 1 at step it
 
   // query fragments straight from global memory: rows g and g + 8 of the (padded) group
   uint32_t qa[D / 16][4];
@@ -131,8 +142,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
 
   for (int it = 0; it < n_it; ++it) {
     const int stage = it % kDecodeStages;
-    if (it + kDecodeStages - 1 < n_it) load_tile(it + kDecodeStages - 1, (it + kDecodeStages - 1) % kDecodeStages);
+    if (it + kDecodeStages - 1 < n_it)
+      load_tile(it + kDecodeStages - 1, (it + kDecodeStages - 1) % kDecodeStages, page_ahead);
     cp_async_commit();
+    page_ahead = page_of(it + kDecodeStages);       // used at the next step
     cp_async_wait<kDecodeStages - 1>();
     __syncwarp();
     if (it == 0) { SIAR_STAMP(2); }
@@ -254,7 +267,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     }
   }
   SIAR_STAMP(4);
-  if (n_chunks == 1) return;
+  if (n_chunks == 1) { SIAR_TRACE(20, 1); return; }
 
   // The block of this (sequence, kv head) that finishes last joins the chunks' partials
   // in chunk order (so the result does not depend on which block that was).
@@ -267,7 +280,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   }
   __syncthreads();
   SIAR_STAMP(5);
-  if (!is_last) return;
+  if (!is_last) { SIAR_TRACE(20, 1); return; }
   __threadfence();
   // weights of the chunks: wgt[h][c] = exp(m_c - max) / sum, formed once per head
   float* cm = reinterpret_cast<float*>(smem_raw);            // [G][n_chunks] maxima, then weights
@@ -310,6 +323,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     orow[h * D + d] = __float2bfloat16_rn(acc);
   }
   SIAR_STAMP(6);
+  SIAR_TRACE(20, 1);
 }
 
 // ------------------------------------------------------------------ prefill
@@ -323,7 +337,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
                         const int* __restrict__ base_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
                         int page_tokens, int max_pages, float scale) {
   pdl_launch_dependents();
+  SIAR_TRACE(21, 0);
   pdl_wait();
+  SIAR_TRACE(21, 2);
   constexpr int RS = D + kPad;
   constexpr int CPR = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -355,10 +371,11 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     const __nv_bfloat16* src = qkv + (size_t)(t0 + rr / G) * qkv_stride + (size_t)(kvh * G + rr % G) * D + ch * 8;
     cp_async_16(smem_u32_generic(q_s + r * RS + ch * 8), src, ok);
   }
-  auto load_tile = [&](int tile, int stage) {
+  const int* table = block_table + (size_t)slot * max_pages;
+  auto page_of = [&](int tile) { return tile < n_tiles ? __ldg(table + tile * kMmaKeyTile / page_tokens) : 0; };
+  auto load_tile = [&](int tile, int stage, int page) {
     const int j0 = tile * kMmaKeyTile;
     const int valid = min(kMmaKeyTile, block_kv_end - j0);
-    const int page = block_table[(size_t)slot * max_pages + j0 / page_tokens];
     const size_t grow = ((size_t)page * Hkv + kvh) * page_tokens + (j0 % page_tokens);
     const __nv_bfloat16* kg = k_pool + grow * D;
     const __nv_bfloat16* vg = v_pool + grow * D;
@@ -372,7 +389,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
       cp_async_16(smem_u32_generic(vs + r * RS + ch * 8), vg + goff, ok);
     }
   };
-  load_tile(0, 0);
+  int page_next = page_of(1);           // read one tile ahead of its use
+  load_tile(0, 0, page_of(0));
   cp_async_commit();
 
   // rows of this thread: warp*16 + g and + 8
@@ -397,8 +415,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
 
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int stage = tile & 1;
-    if (tile + 1 < n_tiles) load_tile(tile + 1, stage ^ 1);
+    if (tile + 1 < n_tiles) load_tile(tile + 1, stage ^ 1, page_next);
     cp_async_commit();
+    page_next = page_of(tile + 2);
     cp_async_wait<1>();
     __syncthreads();
     if (tile == 0) {

@@ -85,6 +85,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---------------------------------------------------------------- timeline marks (profiling builds)
+// With -DSIAR_TIMING thread 0 of every block appends (tag * 16 + phase + (blocks << 16), block, globaltimer)
+// records to a buffer shared by all units: phase 0 = block started, 2 = its dependency wait
+// returned, 1 = block done.  Without the flag the macro is empty.
+#ifdef SIAR_TIMING
+__device__ unsigned long long* g_trace_buf = nullptr;
+__device__ unsigned int* g_trace_cursor = nullptr;
+__device__ unsigned int g_trace_capacity = 0;
+__device__ __forceinline__ void trace_mark(unsigned int tag, unsigned int phase) {
+  if (g_trace_buf == nullptr || threadIdx.x != 0 || threadIdx.y != 0) return;
+  const unsigned int rec = atomicAdd(g_trace_cursor, 1u);
+  if (rec >= g_trace_capacity) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  g_trace_buf[rec * 3ull] = (unsigned long long)(tag * 16u + phase) |
+                            ((unsigned long long)(gridDim.x * gridDim.y * gridDim.z) << 16);
+  g_trace_buf[rec * 3ull + 1] = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  g_trace_buf[rec * 3ull + 2] = t;
+}
+#define SIAR_TRACE(tag, phase) siar::trace_mark(tag, phase)
+#else
+#define SIAR_TRACE(tag, phase)
+#endif
+
 inline bool& pdl_enabled() {
   static bool on = true;
   return on;
@@ -110,5 +134,15 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 
 // One switch per shared object: siar_set_pdl(0) launches every kernel of the unit
 // without the attribute (plain stream order).
+#ifdef SIAR_TIMING
+#define SIAR_DEFINE_PDL_SWITCH()                                                                      \
+  extern "C" void siar_set_pdl(int on) { siar::pdl_enabled() = on != 0; }                             \
+  extern "C" void siar_set_trace(unsigned long long* buf, unsigned int* cursor, unsigned int capacity) { \
+    cudaMemcpyToSymbol(siar::g_trace_buf, &buf, sizeof(buf));                                         \
+    cudaMemcpyToSymbol(siar::g_trace_cursor, &cursor, sizeof(cursor));                                \
+    cudaMemcpyToSymbol(siar::g_trace_capacity, &capacity, sizeof(capacity));                          \
+  }
+#else
 #define SIAR_DEFINE_PDL_SWITCH() \
   extern "C" void siar_set_pdl(int on) { siar::pdl_enabled() = on != 0; }
+#endif

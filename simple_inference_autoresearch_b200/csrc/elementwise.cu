@@ -21,7 +21,9 @@ template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                     float* __restrict__ out, int H, int V, int* __restrict__ status) {
   pdl_launch_dependents();
+  SIAR_TRACE(1, 0);
   pdl_wait();
+  SIAR_TRACE(1, 2);
   const int t = blockIdx.x;
   int id = tokens[t];
   if (id < 0 || id >= V) {
@@ -37,7 +39,9 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __r
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,
                                    float* __restrict__ dst, int H) {
   pdl_launch_dependents();
+  SIAR_TRACE(5, 0);
   pdl_wait();
+  SIAR_TRACE(5, 2);
   const int r = blockIdx.x;
   const float* s = src + (size_t)rows[r] * H;
   for (int j = threadIdx.x; j < H; j += blockDim.x) dst[(size_t)r * H + j] = s[j];
@@ -101,6 +105,7 @@ template <typename TOut, typename TW>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                        const TW* __restrict__ weight, TOut* __restrict__ out, int H, float eps) {
   pdl_launch_dependents();
+  SIAR_TRACE(2, 0);
   __shared__ float scratch[32];
   constexpr int VPT = 4;
   const int chunks = H >> 2;
@@ -112,6 +117,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
     if (c < chunks) w[i] = load_w4<TW>(weight, c);
   }
   pdl_wait();
+  SIAR_TRACE(2, 2);
   float4 r[VPT];
   float ss = 0.f;
 #pragma unroll
@@ -140,6 +146,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
       store4(out + (size_t)blockIdx.x * H, c,
              make_float4(r[i].x * inv * w[i].x, r[i].y * inv * w[i].y, r[i].z * inv * w[i].z, r[i].w * inv * w[i].w));
   }
+  SIAR_TRACE(2, 1);
 }
 
 // ------------------------------------------------------------------ rotary + cache write
@@ -155,11 +162,13 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
                                      int n_pages, int write_kv, int* __restrict__ status) {
   pdl_launch_dependents();
+  SIAR_TRACE(3, 0);
   extern __shared__ float cs[];   // cos[half], sin[half]
   const int half = D >> 1;
   const int flat = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
   for (int i = flat; i < half; i += nthreads) cs[i] = inv_freq != nullptr ? inv_freq[i] : 0.f;
   pdl_wait();
+  SIAR_TRACE(3, 2);
   const int t = blockIdx.x;
   const int b = find_sequence(q_start, B, t);
   const int pos = base_len[b] + (t - q_start[b]);
@@ -223,7 +232,9 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // bf16, I % 8 == 0, 16-byte aligned rows: eight outputs per thread with 16-byte accesses.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I) {
   pdl_launch_dependents();
+  SIAR_TRACE(4, 0);
   pdl_wait();
+  SIAR_TRACE(4, 2);
   const size_t row = blockIdx.x;
   const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (j >= I) return;
@@ -246,7 +257,9 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_
 // that a replay sees the lengths the previous replay left.
 __global__ void advance_lengths_kernel(int* __restrict__ base_len, const int* __restrict__ q_start, int B) {
   pdl_launch_dependents();
+  SIAR_TRACE(6, 0);
   pdl_wait();
+  SIAR_TRACE(6, 2);
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < B) base_len[b] += q_start[b + 1] - q_start[b];
 }

@@ -174,6 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
 
   pdl_launch_dependents();
+  SIAR_TRACE(10, 0);
   if (threadIdx.x == 0) { SIAR_STAMP(0); }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p0 = blockIdx.x * kBM, q0 = blockIdx.y * BN;
@@ -224,6 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
       SIAR_STAMP(1);
       pdl_wait();
+      SIAR_TRACE(10, 2);
       SIAR_STAMP(2);
       for (int i = 0; i < pre; ++i)
         tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
@@ -413,6 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
+  SIAR_TRACE(10, 1);
   if (threadIdx.x == 0) { SIAR_STAMP(6); }
   if (warp == 1) {
     tc_fence_after();

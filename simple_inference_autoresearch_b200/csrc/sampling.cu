@@ -110,7 +110,9 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
               const long long* __restrict__ seeds, int* __restrict__ draw_index, int advance_index,
               int* __restrict__ out) {
   pdl_launch_dependents();
+  SIAR_TRACE(30, 0);
   pdl_wait();
+  SIAR_TRACE(30, 2);
   __shared__ Shared sh;
   const int r = blockIdx.x;
   const float* x = logits + (size_t)r * V;
