@@ -59,7 +59,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        const int* __restrict__ slot_ids, const int* __restrict__ q_start,
                        const int* __restrict__ base_len, float* __restrict__ part_ml, float* __restrict__ part_acc,
                        int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int page_tokens,
-                       int max_pages, int max_chunks, int chunk_keys, float scale) {
+                       int max_pages, int max_chunks, int chunk_keys, float scale, const float* __restrict__ inv_freq,
+                       int fuse_rope, int write_kv) {
+  // fuse_rope: the fused qkv rows are as the product left them; this kernel rotates q (in
+  // registers) and the new token's k by the token's position, writes that k and v to the cache
+  // (write_kv) and uses them from shared memory, so no separate rotate-and-write kernel runs.
+  __shared__ float cs_s[D];                     // cos[D/2], sin[D/2] of the new token's position
   pdl_launch_dependents();
   SIAR_TRACE(20, 0);
   pdl_wait();
@@ -119,6 +124,17 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     cp_async_commit();
   }
   int page_ahead = pages[kDecodeStages - 1];      // page of tile it + kDecodeStages - 1 at step it
+  const int pos = kv_len - 1;                      // position of the new token
+  if (fuse_rope) {
+    for (int i = threadIdx.x; i < D / 2; i += blockDim.x) {
+      float sn = 0.f, cs = 1.f;
+      if (inv_freq != nullptr) sincosf((float)pos * __ldg(inv_freq + i), &sn, &cs);
+      cs_s[i] = cs;
+      cs_s[D / 2 + i] = sn;
+    }
+    __syncthreads();
+  }
+  const size_t tok_row = (size_t)q_start[b] * (Hq + 2 * Hkv) * D;
 
   // query fragments straight from global memory: rows g and g + 8 of the (padded) group
   uint32_t qa[D / 16][4];
@@ -131,6 +147,21 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
       qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
       qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+    if (fuse_rope) {
+      // columns c < D/2 pair with c + D/2: fragment kk pairs with fragment kk + D/32, same register
+#pragma unroll
+      for (int kk = 0; kk < D / 32; ++kk) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int col = kk * 16 + q * 2 + (r >= 2 ? 8 : 0);
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk][r]));
+          const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk + D / 32][r]));
+          const float c0v = cs_s[col], c1v = cs_s[col + 1], s0v = cs_s[D / 2 + col], s1v = cs_s[D / 2 + col + 1];
+          qa[kk][r] = pack_bf16(a.x * c0v - c2.x * s0v, a.y * c1v - c2.y * s1v);
+          qa[kk + D / 32][r] = pack_bf16(c2.x * c0v + a.x * s0v, c2.y * c1v + a.y * s1v);
+        }
+      }
     }
   }
   SIAR_STAMP(1);
@@ -149,8 +180,34 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     cp_async_wait<kDecodeStages - 1>();
     __syncwarp();
     if (it == 0) { SIAR_STAMP(2); }
-    const int valid = min(WK, c_end - (c0 + it * 4 * WK + warp * WK));
+    const int w0 = c0 + it * 4 * WK + warp * WK;
+    const int valid = min(WK, c_end - w0);
     if (valid <= 0) continue;
+    if (fuse_rope && write_kv && pos >= w0 && pos < w0 + WK) {
+      // this warp's tile holds the new token: its k (rotated) and v come from the fused qkv row,
+      // go to the cache for later steps and replace the row that cp.async just fetched
+      const __nv_bfloat16* krow = qkv + tok_row + (size_t)(Hq + kvh) * D;
+      const __nv_bfloat16* vrow = qkv + tok_row + (size_t)(Hq + Hkv + kvh) * D;
+      __nv_bfloat16* ks = tiles + stage * kStageElems + warp * WK * RS + (pos - w0) * RS;
+      __nv_bfloat16* vs = ks + 4 * WK * RS;
+      const int page = __ldg(table + pos / page_tokens);
+      const size_t grow = (((size_t)page * Hkv + kvh) * page_tokens + (pos % page_tokens)) * D;
+      __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(k_pool) + grow;
+      __nv_bfloat16* vdst = const_cast<__nv_bfloat16*>(v_pool) + grow;
+      for (int i = lane; i < D / 2; i += 32) {
+        const float a = __bfloat162float(krow[i]), c2 = __bfloat162float(krow[i + D / 2]);
+        const __nv_bfloat16 oa = __float2bfloat16_rn(a * cs_s[i] - c2 * cs_s[D / 2 + i]);
+        const __nv_bfloat16 oc = __float2bfloat16_rn(c2 * cs_s[i] + a * cs_s[D / 2 + i]);
+        ks[i] = oa; ks[i + D / 2] = oc;
+        kdst[i] = oa; kdst[i + D / 2] = oc;
+      }
+      for (int d = lane; d < D; d += 32) {
+        const __nv_bfloat16 v = vrow[d];
+        vs[d] = v;
+        vdst[d] = v;
+      }
+      __syncwarp();
+    }
     const uint32_t kbase = smem_u32_generic(tiles + stage * kStageElems + warp * WK * RS);
     const uint32_t vbase = kbase + 4 * WK * RS * 2;
     // S = Q K^T : WK/8 key tiles of 8
@@ -545,7 +602,8 @@ template <int D>
 static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                          const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
                          int* counters, int B, int Hq, int Hkv, int page_tokens, int max_pages, int max_kv_len,
-                         int sm_count, float scale, cudaStream_t s) {
+                         int sm_count, float scale, cudaStream_t s, const float* inv_freq = nullptr,
+                         int fuse_rope = 0, int write_kv = 1) {
   const int chunk_keys = decode_chunk_keys(B, Hkv, max_kv_len, sm_count);
   const int max_chunks = (max_kv_len + chunk_keys - 1) / chunk_keys;
   float* part_ml = scratch;
@@ -564,7 +622,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, part_ml, part_acc,
                             counters, (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, max_chunks, chunk_keys,
-                            scale);
+                            scale, inv_freq, fuse_rope, write_kv);
 }
 
 template <int D>
@@ -626,6 +684,26 @@ extern "C" int siar_attn_mma_decode(const void* qkv, const void* k_pool, const v
                              B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
   return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters, B,
                             Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
+}
+
+// The same with the rotary encoding and the cache write of the new token fused in: qkv holds the
+// product's output (q and k not rotated), inv_freq the rotary frequencies (nullptr: no rotation),
+// write_kv == 0 leaves the cache alone (a layer that reads another layer's cache).
+extern "C" int siar_attn_mma_decode_rope(const void* qkv, void* k_pool, void* v_pool, const int* block_table,
+                                         const int* slot_ids, const int* q_start, const int* base_len, void* out,
+                                         float* scratch, int* counters, const float* inv_freq, int write_kv, int B,
+                                         int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_kv_len,
+                                         int sm_count, float scale, void* stream) {
+  if (B == 0) return 0;
+  if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 64)
+    return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters,
+                             B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, inv_freq, 1,
+                             write_kv);
+  return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters, B,
+                            Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, inv_freq, 1, write_kv);
 }
 
 extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,

@@ -53,6 +53,9 @@ _signatures = {
         "siar_attn_mma_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_void_p],
+        "siar_attn_mma_decode_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_float, c_void_p],
         "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
         "siar_attn_mma_decode_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
@@ -279,6 +282,45 @@ def mma_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_
 def decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int, chunk: int) -> int:
     chunks = (max_kv_len + chunk - 1) // chunk
     return n_seqs * n_heads * chunks * (head_dim + 2)
+
+
+def decode_fuses_rope(meta, dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
+    """True when ``rope_and_attention`` runs one kernel for this step (one token per sequence
+    on the tensor-core path); otherwise it is ``rope_kv_write`` followed by ``attention``."""
+    return bool(meta.is_decode) and fuse_decode_rope and mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim,
+                                                                              page_tokens)
+
+
+#: set to False to keep the rotary/cache-write kernel separate from decode attention
+fuse_decode_rope = True
+
+
+def rope_and_attention(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, meta, n_heads: int, n_kv_heads: int,
+                       head_dim: int, scale: float, write_kv: bool = True) -> torch.Tensor:
+    """Rotates q and k by the tokens' positions, writes k and v to the cache entry and attends:
+    what a rotary attention mixer does between its two products.  For steps of one token per
+    sequence on the tensor-core path this is ONE kernel (q is rotated in registers, the new k and
+    v go to the cache and are used from shared memory); otherwise two."""
+    if not decode_fuses_rope(meta, qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
+        rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
+        return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale)
+    _need_cuda(qkv, kv.k, inv_freq)
+    check_attention_sizes(n_heads, n_kv_heads, head_dim)
+    assert qkv.is_contiguous() and qkv.shape == (meta.n_seqs, (n_heads + 2 * n_kv_heads) * head_dim)
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2
+    out = torch.empty((meta.n_seqs, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    sms = _sm_count(qkv.device)
+    f = _fn("attention_mma", "siar_attn_mma_decode_scratch_floats")
+    f.restype = c_longlong
+    scratch = torch.empty(f(meta.n_seqs, n_heads, n_kv_heads, head_dim, meta.max_kv_len, sms), dtype=torch.float32,
+                          device=qkv.device)
+    _launch("attention_mma", "siar_attn_mma_decode_rope", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
+            _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len), _ptr(out), _ptr(scratch),
+            _ptr(_decode_counters(qkv.device, meta.n_seqs * n_kv_heads)), _ptr(inv_freq), int(write_kv), meta.n_seqs,
+            n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1], meta.max_kv_len, sms, float(scale),
+            _stream())
+    return out
 
 
 def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:

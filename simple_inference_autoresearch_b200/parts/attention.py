@@ -60,7 +60,7 @@ class GroupedQueryAttention(Mixer):
     def forward(self, ctx, x: torch.Tensor, cache_entry, writes_cache: bool = True) -> torch.Tensor:
         qkv = ops.linear(x, self.w_qkv, ctx.dtype)
         rotary = self.position.rotary() if self.position is not None else None
-        ops.rope_kv_write(qkv, rotary.inv_freq if rotary is not None else None, cache_entry, ctx.meta,
-                          self.n_heads, self.n_kv_heads, self.head_dim, write_kv=writes_cache)
-        attn = ops.attention(qkv, cache_entry, ctx.meta, self.n_heads, self.n_kv_heads, self.head_dim, self.scale)
+        attn = ops.rope_and_attention(qkv, rotary.inv_freq if rotary is not None else None, cache_entry, ctx.meta,
+                                      self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+                                      write_kv=writes_cache)
         return ops.linear(attn, self.w_o, torch.float32)

@@ -108,6 +108,11 @@ def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale):
     return out.to(qkv.dtype)
 
 
+def rope_and_attention(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, scale, write_kv=True):
+    rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
+    return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale)
+
+
 def swiglu(gate_up, interleaved=False):
     i = gate_up.shape[1] // 2
     x = gate_up.to(torch.float32)
@@ -142,6 +147,7 @@ def install(monkeypatch) -> None:
     """Swaps the functions above in for the CUDA ones (CPU tests of engine logic)."""
     from simple_inference_autoresearch_b200.kernels import ops
 
-    for name in ("embed", "gather_rows", "add_rmsnorm", "linear", "linear_swiglu", "rope_kv_write", "attention", "swiglu",
+    for name in ("embed", "gather_rows", "add_rmsnorm", "linear", "linear_swiglu", "rope_kv_write", "attention", "rope_and_attention",
+                 "swiglu",
                  "advance_lengths", "sample", "check_status"):
         monkeypatch.setattr(ops, name, globals()[name])

@@ -418,3 +418,41 @@ def test_mma_attention_far_key_and_rows_do_not_depend_on_batch():
     alone = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0], q_lens=[150])[DEV][0]
     both = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0], q_lens=[150, 77])[DEV][0]
     assert torch.equal(alone, both[:150])
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (6, 2, 128), (16, 4, 64), (4, 4, 64)])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_fused_rope_decode_attention_equals_the_two_kernels(hq, hkv, d, write_kv):
+    """One token per sequence: rotary + cache write + attention in one kernel against the separate
+    rotate-and-write kernel followed by attention (same cache contents afterwards, same output)."""
+    lens = [0, 15, 16, 63, 64, 700, 1029]
+    width = (hq + 2 * hkv) * d
+    inv_freq = plain_llama.rope_inv_freq(d, 10000.0, None).to(DEV)
+    results = []
+    for fused in (True, False):
+        c = make_cache(hkv, d, torch.bfloat16, DEV, max_tokens=8192, max_slots=8)
+        slots = [c.alloc() for _ in lens]
+        live = [(i, s) for i, s in enumerate(slots) if lens[i] > 0]
+        hist = torch.cat([rnd(lens[i], width, dtype=torch.bfloat16, seed=10 + i) for i, _ in live]).to(DEV)
+        c.reserve([s for _, s in live], [lens[i] for i, _ in live])
+        ops.rope_kv_write(hist, inv_freq, c.entry(0), BatchMeta.build([StepEntry(s, [0] * lens[i]) for i, s in live],
+                                                                      [0] * len(live), DEV), hq, hkv, d)
+        c.commit([s for _, s in live], [lens[i] for i, _ in live])
+        c.reserve(slots, [1] * len(lens))
+        if not write_kv:      # a layer that reads a cache another layer wrote: the new token is already there
+            other = rnd(len(lens), width, dtype=torch.bfloat16, seed=77).to(DEV)
+            ops.rope_kv_write(other, inv_freq, c.entry(0), BatchMeta.build([StepEntry(s, [0]) for s in slots], lens, DEV),
+                              hq, hkv, d)
+        new = rnd(len(lens), width, dtype=torch.bfloat16, seed=50).to(DEV)
+        meta = BatchMeta.build([StepEntry(s, [0]) for s in slots], lens, DEV)
+        ops.fuse_decode_rope = fused
+        try:
+            assert ops.decode_fuses_rope(meta, torch.bfloat16, hq, hkv, d, 64) == fused
+            out = ops.rope_and_attention(new, inv_freq, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d), write_kv=write_kv)
+        finally:
+            ops.fuse_decode_rope = True
+        results.append((out.float().cpu(), c.entry(0).k.float().cpu(), c.entry(0).v.float().cpu()))
+    ops.check_status(DEV)
+    torch.testing.assert_close(results[0][1], results[1][1], rtol=0, atol=0)     # cached keys: same rounding, same bits
+    torch.testing.assert_close(results[0][2], results[1][2], rtol=0, atol=0)
+    torch.testing.assert_close(results[0][0], results[1][0], rtol=2e-2, atol=2e-2)
