@@ -103,6 +103,7 @@ class DecoderModel:
     def tensor_specs(self) -> List[TensorSpec]:
         s = self.spec
         specs = [TensorSpec(s.embedding_name, (s.vocab_size, s.hidden_size), std=s.embedding_std)]
+        specs += self.position.tensor_specs()
         for layer in self.layers:
             specs += layer.tensor_specs()
         specs += self.final_norm.tensor_specs()
@@ -114,6 +115,7 @@ class DecoderModel:
         s = self.spec
         self.embedding = tensors[s.embedding_name].contiguous()
         self.head = self.embedding if s.head_name is None else tensors[s.head_name].contiguous()
+        self.position.load(tensors)
         for layer in self.layers:
             layer.load(tensors)
         self.final_norm.load(tensors)

@@ -17,7 +17,8 @@ from simple_inference_autoresearch_b200.engine.model import DecoderModel, ModelS
 from simple_inference_autoresearch_b200.architectures.llama import llama_model_spec
 from simple_inference_autoresearch_b200.cache import SequenceCache
 from simple_inference_autoresearch_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS,
-                                                      Mixer, PartSpec, StateNeed, TensorSpec)
+                                                      FeedForward, Mixer, PartSpec, PositionEncoding, StateNeed,
+                                                      TensorSpec)
 from simple_inference_autoresearch_b200.weights import random_tensors
 from tests import emulated_kernels, plain_llama, tiny_configs
 
@@ -251,6 +252,118 @@ def test_toy_mixer_with_its_own_state_registers_builds_and_steps(device):
     finally:
         MIXERS.unregister("running_mean")
         registry.unregister_architecture("ToyForCausalLM")
+
+
+# ----------------------------------------------------------------------------- a toy feed-forward with routing,
+# ----------------------------------------------------------------------------- a toy position encoding that adds at the embedding
+class RoutedFeedForward(FeedForward):
+    """Top-1 routing over E small experts, y = gate_prob * (relu(x W1_e) W2_e); router logits and
+    the softmax in 32-bit.  Torch ops; it stands for a feed-forward that is not dense."""
+
+    def __init__(self, prefix, hidden_size, n_experts, expert_size):
+        super().__init__(prefix)
+        self.h, self.e, self.f = hidden_size, n_experts, expert_size
+        self.router = self.w1 = self.w2 = None
+
+    def tensor_specs(self):
+        p = self.prefix
+        return [TensorSpec(p + "router", (self.e, self.h), std=0.5),
+                TensorSpec(p + "w1", (self.e, self.f, self.h), std=0.1),
+                TensorSpec(p + "w2", (self.e, self.h, self.f), std=0.1)]
+
+    def load(self, tensors):
+        p = self.prefix
+        self.router, self.w1, self.w2 = tensors[p + "router"], tensors[p + "w1"], tensors[p + "w2"]
+
+    def forward(self, ctx, x):
+        return routed_ffn_plain(x.float(), self.router.float(), self.w1.float(), self.w2.float())
+
+
+def routed_ffn_plain(x, router, w1, w2):
+    probs = torch.softmax(x @ router.T, dim=-1)
+    top = probs.argmax(dim=-1)
+    out = torch.zeros_like(x)
+    for e in range(router.shape[0]):
+        rows = (top == e).nonzero().flatten()
+        if rows.numel():
+            out[rows] = probs[rows, e:e + 1] * (torch.relu(x[rows] @ w1[e].T) @ w2[e].T)
+    return out
+
+
+class LearnedPositions(PositionEncoding):
+    """Absolute positions: a learned table row is added to each embedded token; mixers get no rotation."""
+
+    def __init__(self, prefix="pos.", *, hidden_size, max_position, device=None):
+        super().__init__(prefix)
+        self.h, self.n = hidden_size, max_position
+        self.table = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix + "table", (self.n, self.h), std=0.1)]
+
+    def load(self, tensors):
+        self.table = tensors[self.prefix + "table"]
+
+    def at_embedding(self, ctx, residual):
+        m = ctx.meta
+        pos = torch.cat([torch.arange(b, b + n) for b, n in zip(m.base_lens, m.q_lens)]).to(residual.device)
+        residual += self.table[pos].float()
+
+
+def test_toy_routed_feed_forward_and_learned_positions(device):
+    """Two more parts from outside the library: a routed feed-forward and a position encoding that
+    enters at the embedding, in a model whose layers differ (layer 0 dense, layer 1 routed)."""
+    FEED_FORWARDS.register("routed")(RoutedFeedForward)
+    POSITION_ENCODINGS.register("learned")(LearnedPositions)
+    try:
+        h, v = 32, 40
+        norm = lambda p: PartSpec("rmsnorm", {"prefix": p, "hidden_size": h, "eps": 1e-5})  # noqa: E731
+        attn = PartSpec("gqa_attention", {"prefix": "attn.", "hidden_size": h, "n_heads": 2, "n_kv_heads": 2, "head_dim": 16})
+        dense = PartSpec("swiglu", {"prefix": "ffn.", "hidden_size": h, "intermediate_size": 48})
+        routed = PartSpec("routed", {"prefix": "moe.", "hidden_size": h, "n_experts": 3, "expert_size": 24})
+        layer = lambda i, ffn: PartSpec("prenorm", {"prefix": f"l{i}.", "mixer": attn, "feed_forward": ffn,  # noqa: E731
+                                                    "mixer_norm": norm("n1."), "ffn_norm": norm("n2.")})
+        spec = ModelSpec(architecture="Toy2", vocab_size=v, hidden_size=h, max_position=64, embedding_name="emb",
+                         head_name="head", position=PartSpec("learned", {"hidden_size": h, "max_position": 64}),
+                         layers=(layer(0, dense), layer(1, routed)), final_norm=norm("nf."))
+        model = DecoderModel(spec, torch.float32, device)
+        assert "pos.table" in [t.name for t in model.tensor_specs()]
+        w = random_tensors(model.tensor_specs(), 5, torch.float32)
+        model.load({k: t.to(device) for k, t in w.items()})
+        eng = siar.Engine(model, max_batch=2, max_seq_len=64, use_cuda_graph=False)
+        g = torch.Generator().manual_seed(6)
+        reqs = [torch.randint(0, v, (n,), generator=g).tolist() for n in (19, 8)]
+        slots = [eng.open() for _ in reqs]
+        got = [[] for _ in reqs]
+        out = eng.step([StepEntry(s, r[:-3], range(len(r) - 3)) for s, r in zip(slots, reqs)])
+        o = 0
+        for i, r in enumerate(reqs):
+            got[i].append(out[o:o + len(r) - 3]); o += len(r) - 3
+        for k in range(3):
+            out = eng.step([StepEntry(s, [r[len(r) - 3 + k]], [0]) for s, r in zip(slots, reqs)])
+            for i in range(len(reqs)):
+                got[i].append(out[i:i + 1])
+        for i, r in enumerate(reqs):          # the same model written out plainly, whole sequence
+            x = w["emb"][torch.tensor(r)] + w["pos.table"][:len(r)]
+            c = {"H": h, "Hq": 2, "Hkv": 2, "D": 16}
+            for li, ffn in ((0, "dense"), (1, "routed")):
+                p = f"l{li}."
+                hn = plain_llama.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+                t = len(r)
+                q = (hn @ w[p + "attn.q_proj.weight"].T).view(t, 2, 16)       # no rotation in this model
+                kk = (hn @ w[p + "attn.k_proj.weight"].T).view(t, 2, 16)
+                vv = (hn @ w[p + "attn.v_proj.weight"].T).view(t, 2, 16)
+                x = x + plain_llama.attention_causal(q, kk, vv) @ w[p + "attn.o_proj.weight"].T
+                hn = plain_llama.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+                if ffn == "dense":
+                    x = x + plain_llama.swiglu_mlp(hn, w, p + "ffn.")
+                else:
+                    x = x + routed_ffn_plain(hn, w[p + "moe.router"], w[p + "moe.w1"], w[p + "moe.w2"])
+            ref = plain_llama.rmsnorm(x, w["nf.weight"], 1e-5) @ w["head"].T
+            torch.testing.assert_close(torch.cat(got[i]).cpu(), ref, rtol=2e-5, atol=2e-5)
+    finally:
+        FEED_FORWARDS.unregister("routed")
+        POSITION_ENCODINGS.unregister("learned")
 
 
 def test_unknown_part_kind_is_a_clear_error():
