@@ -136,7 +136,7 @@ def test_linear_with_swiglu_epilogue(dtype, m, i, k):
 
 
 # ----------------------------------------------------------------------------- attention over the cache
-def make_cache(n_kv, d, dtype, device, max_tokens=4096, max_slots=8, max_seq_len=2048):
+def make_cache(n_kv, d, dtype, device, max_tokens=8192, max_slots=12, max_seq_len=2048):
     return SequenceCache([KVNeed(n_kv, d)], max_tokens, max_slots, max_seq_len, dtype, device)
 
 
@@ -149,8 +149,18 @@ def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=100
     inv_freq = plain_llama.rope_inv_freq(d, theta, None)
     b = len(q_lens)
     width = (hq + 2 * hkv) * d
-    slots = {dev: [c.alloc() for _ in range(b)] for dev, c in caches.items()}
-    # a decoy slot in between so that slot ids and pages are not the identity
+    # Decoy sequences are opened, grown and partly closed first, so that the slots of the batch
+    # are not 0..b-1 in order and their pages are neither contiguous nor ascending: a kernel that
+    # took the batch index for the slot, or the page index for the page, would read the wrong keys.
+    slots = {}
+    for dev, c in caches.items():
+        decoys = [c.alloc() for _ in range(3)]
+        c.reserve(decoys, [70, 130, 5]); c.commit(decoys, [70, 130, 5])
+        real = [c.alloc() for _ in range(b)]
+        c.free(decoys[1])
+        if b >= 2:
+            real[0], real[-1] = real[-1], real[0]
+        slots[dev] = real
     hist = [rnd(max(n, 1), width, dtype=dtype, seed=10 + i) for i, n in enumerate(lens_before)]
     new = [rnd(n, width, dtype=dtype, seed=50 + i) for i, n in enumerate(q_lens)]
     if boost is not None:
