@@ -36,7 +36,7 @@ NVCC_FLAGS = [
 EXTRA_FLAGS = os.environ.get("SIAR_NVCC_FLAGS", "").split()
 
 #: every unit of the library, in the order ``build_all`` compiles them
-ALL_UNITS = ("elementwise", "gemm_simt", "attention", "attention_mma", "sampling", "gemm_tc")
+ALL_UNITS = ("elementwise", "gemm_simt", "attention", "attention_mma", "attention_tc", "sampling", "gemm_tc")
 
 
 class ExtensionError(RuntimeError):

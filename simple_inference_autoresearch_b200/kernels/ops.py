@@ -59,6 +59,14 @@ _signatures = {
         "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
         "siar_attn_mma_decode_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
+    "attention_tc": {
+        # qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, N, B, Hq, Hkv, D, page_tokens,
+        # max_pages, n_pages, max_q_len, scale, status, stream
+        "siar_attn_tc_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                 c_void_p],
+        "siar_attn_tc_supported": [c_int, c_int, c_int, c_int],
+    },
     "sampling": {
         "siar_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                         c_void_p, c_void_p],
@@ -194,6 +202,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
     _launch("gemm_simt", "siar_gemm_nt_simt", _is_bf16(x.dtype), int(out_dtype == torch.float32), _ptr(x),
             _ptr(w), _ptr(out), m, n, k, 1, _stream())
     return out
+
+
+#: set to False to keep prompts' attention on the warp-level tensor-core kernel (tests compare both)
+use_tc_attention = True
+
+
+def tc_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
+    """True when the tcgen05 kernel for prompts takes these sizes (bfloat16, head_dim 128, a
+    group size that divides 128, pages of 64 tokens or a multiple)."""
+    if dtype != torch.bfloat16 or not (use_tc_attention and use_mma_attention):
+        return False
+    return bool(_fn("attention_tc", "siar_attn_tc_supported")(n_heads, n_kv_heads, head_dim, page_tokens))
 
 
 def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, meta, n_heads: int, n_kv_heads: int,
@@ -350,6 +370,9 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
                                   dtype=torch.float32, device=qkv.device)
             _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
                     _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)
+    elif tc_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
+        _launch("attention_tc", "siar_attn_tc_prefill", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out), n,
+                *sizes, kv.k.shape[0], meta.max_q_len, float(scale), _ptr(status_word(qkv.device)), _stream())
     elif mma:
         _launch("attention_mma", "siar_attn_mma_prefill", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
                 *sizes, meta.max_q_len, float(scale), _stream())

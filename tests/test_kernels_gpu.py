@@ -140,7 +140,7 @@ def make_cache(n_kv, d, dtype, device, max_tokens=8192, max_slots=12, max_seq_le
     return SequenceCache([KVNeed(n_kv, d)], max_tokens, max_slots, max_seq_len, dtype, device)
 
 
-def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None):
+def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None, qk_scale=1.0):
     """Fills two caches (GPU kernel / CPU restatement) with the same history through
     rope_kv_write, then compares rope + attention of a last step."""
     torch.manual_seed(seed)
@@ -163,6 +163,9 @@ def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=100
         slots[dev] = real
     hist = [rnd(max(n, 1), width, dtype=dtype, seed=10 + i) for i, n in enumerate(lens_before)]
     new = [rnd(n, width, dtype=dtype, seed=50 + i) for i, n in enumerate(q_lens)]
+    if qk_scale != 1.0:
+        for x in hist + new:
+            x[:, :(hq + hkv) * d] *= qk_scale
     if boost is not None:
         # one far key whose score stands out for the last query of `seq` (no rotation,
         # so that the key can simply be a multiple of the query of head 0)
@@ -428,6 +431,53 @@ def test_mma_attention_far_key_and_rows_do_not_depend_on_batch():
     alone = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0], q_lens=[150])[DEV][0]
     both = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0], q_lens=[150, 77])[DEV][0]
     assert torch.equal(alone, both[:150])
+
+
+# ----------------------------------------------------------------------------- tcgen05 attention for prompts
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (4, 4), (32, 8), (16, 1), (2, 1), (64, 2)])
+def test_tc_attention_prefill_groups_and_lengths(hq, hkv):
+    """Query tiles that are full, half empty and absent; prompts that start at 0 and that continue a
+    cache whose length is no multiple of the key tile; one token among prompts."""
+    assert ops.tc_attention_takes(torch.bfloat16, hq, hkv, 128, 64)
+    run_attention_case(torch.bfloat16, hq, hkv, 128, lens_before=[0, 0, 300, 63, 64], q_lens=[1, 200, 150, 66, 129])
+
+
+def test_tc_attention_long_prompt_and_far_key():
+    hq, hkv, d = 8, 2, 128
+    outs = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[900, 0], q_lens=[300, 1100], boost=(0, 200, 8.0))
+    v_row = rnd(900, (hq + 2 * hkv) * d, dtype=torch.bfloat16, seed=10)[200, (hq + hkv) * d:(hq + hkv + 1) * d].float()
+    torch.testing.assert_close(outs[DEV][0][299, :d], v_row, rtol=5e-2, atol=5e-2)
+
+
+def test_tc_attention_large_scores_rescale():
+    """Scores that grow along the keys by far more than the lazy-rescale gap: every row has to
+    rescale its accumulator several times."""
+    hq, hkv, d = 4, 1, 128
+    torch.manual_seed(3)
+    outs = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0], q_lens=[400], qk_scale=6.0)
+    assert torch.isfinite(outs[DEV][0]).all()
+
+
+def test_tc_and_mma_attention_agree_and_rows_do_not_depend_on_batch():
+    hq, hkv, d = 8, 2, 128
+    a = run_attention_case(torch.bfloat16, hq, hkv, d, [100, 0], [90, 330])[DEV][0]
+    ops.use_tc_attention = False
+    try:
+        assert not ops.tc_attention_takes(torch.bfloat16, hq, hkv, d, 64)
+        b = run_attention_case(torch.bfloat16, hq, hkv, d, [100, 0], [90, 330])[DEV][0]
+    finally:
+        ops.use_tc_attention = True
+    torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
+    alone = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0], q_lens=[150])[DEV][0]
+    both = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0], q_lens=[150, 77])[DEV][0]
+    assert torch.equal(alone, both[:150])
+
+
+def test_tc_attention_is_refused_where_it_does_not_apply():
+    assert not ops.tc_attention_takes(torch.float32, 8, 2, 128, 64)
+    assert not ops.tc_attention_takes(torch.bfloat16, 8, 2, 64, 64)        # head_dim other than 128
+    assert not ops.tc_attention_takes(torch.bfloat16, 6, 2, 128, 64)       # a group of 3 does not divide 128
+    assert not ops.tc_attention_takes(torch.bfloat16, 8, 2, 128, 32)       # pages smaller than a key tile
 
 
 @pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (6, 2, 128), (16, 4, 64), (4, 4, 64)])
