@@ -40,10 +40,10 @@ constexpr int kStages = 3;       // K / V ring
 constexpr int kQBytes = kRows * kHd * 2;            // 32 KiB, two 64-dim halves of 16 KiB
 constexpr int kTileBytes = kKeys * kHd * 2;         // 16 KiB, two 64-dim halves of 8 KiB
 constexpr int kPBytes = kRows * kKeys * 2;          // 16 KiB
-constexpr int kSmemBytes = kQTiles * kQBytes + kStages * 2 * kTileBytes + kQTiles * kPBytes;
+constexpr int kSmemBytes = kQTiles * kQBytes + kStages * 2 * kTileBytes + kQTiles * 2 * kPBytes;
 constexpr uint32_t kTmemCols = 512;                 // S[q][buf]: 64 columns each from 0; O[q]: 128 each from 256
 constexpr float kRescaleGap = 8.f;                  // log2 of the growth that forces a rescale
-constexpr int kThreads = 64 + kQTiles * 128;
+constexpr int kThreads = 128 + kQTiles * 128;   // TMA warp, one MMA warp per query tile, a spare, the softmax warps
 
 struct AttnTcParams {
   __nv_bfloat16* out;
@@ -77,7 +77,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                        const __grid_constant__ CUtensorMap tmV, const AttnTcParams prm) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t q_full;
-  __shared__ __align__(8) uint64_t s_full[kQTiles][2], p_full[kQTiles], pv_full[kQTiles];
+  __shared__ __align__(8) uint64_t s_full[kQTiles][2], p_full[kQTiles][2], pv_full[kQTiles][2];
   __shared__ __align__(8) uint64_t kv_full[kStages], kv_empty[kStages];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -88,7 +88,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int t0 = prm.q_start[b];                 // batch description: written by no kernel of this step
   const int q_len = prm.q_start[b + 1] - t0;
   const int rows_total = q_len * G;
-  const int row0 = blockIdx.x * (kQTiles * kRows);
+  // blocks with the most keys (the last rows) start first: the tail of the grid is made of short blocks
+  const int row0 = (gridDim.x - 1 - blockIdx.x) * (kQTiles * kRows);
   if (row0 >= rows_total) return;
   const int base = prm.base_len[b];
   const int slot = prm.slot_ids[b];
@@ -101,14 +102,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     nt[g] = rows_q[g] > 0 ? (base + (row0 + g * kRows + rows_q[g] - 1) / G + 1 + kKeys - 1) / kKeys : 0;
     if (rows_q[g] > 0) n_q = g + 1;
   }
+  // Both query tiles walk all the key tiles of the block (the first tile's last one may be masked
+  // entirely): a stage of the ring is then released by as many MMA threads as there are tiles.
   const int nt_max = nt[n_q - 1];
+#pragma unroll
+  for (int g = 0; g < kQTiles; ++g)
+    if (rows_q[g] > 0) nt[g] = nt_max;
 
   const uint32_t dyn = smem_u32(smem_dyn);
   unsigned char* sm = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);
   unsigned char* q_s = sm;                                   // [q tile][half][128 rows][64 dims]
   unsigned char* k_s = q_s + kQTiles * kQBytes;              // [stage][half][64 keys][64 dims]
   unsigned char* v_s = k_s + kStages * kTileBytes;
-  unsigned char* p_s = v_s + kStages * kTileBytes;           // [q tile][128 rows][64 keys]
+  unsigned char* p_s = v_s + kStages * kTileBytes;           // [q tile][buffer][128 rows][64 keys]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -116,12 +122,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     for (int g = 0; g < kQTiles; ++g) {
       mbar_init(&s_full[g][0], 1);
       mbar_init(&s_full[g][1], 1);
-      mbar_init(&p_full[g], 1);
-      mbar_init(&pv_full[g], 1);
+      mbar_init(&p_full[g][0], 1);
+      mbar_init(&p_full[g][1], 1);
+      mbar_init(&pv_full[g][0], 1);
+      mbar_init(&pv_full[g][1], 1);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&kv_empty[s], n_q);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -174,59 +182,60 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int i = max(0, issued - kStages); i < issued; ++i) mbar_wait(&kv_full[i % kStages], (i / kStages) & 1);
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 2) {
+    // ---------------- MMA issue: one thread per query tile (the two tiles depend on nothing of
+    // each other but the K / V stages, and two issuing warps sit on two schedulers)
+    const int g = warp - 1;
+    if (lane == 0 && g < n_q) {
       constexpr uint32_t idesc_qk = instr_desc_bf16(kKeys);
       constexpr uint32_t idesc_pv = instr_desc_bf16(kHd, true);
+      // descriptors differ in their low word only (the address field, in units of 16 bytes)
+      const uint32_t hi_k = (uint32_t)(smem_desc_sw128(0) >> 32);
+      const uint32_t hi_v = (uint32_t)(smem_desc_sw128_mn(0, kTileBytes / 2) >> 32);
+      const uint32_t q_lo = (uint32_t)smem_desc_sw128(smem_u32(q_s + g * kQBytes));
+      const uint32_t k_lo = (uint32_t)smem_desc_sw128(smem_u32(k_s));
+      const uint32_t v_lo = (uint32_t)smem_desc_sw128_mn(smem_u32(v_s), kTileBytes / 2);
+      const uint32_t p_lo = (uint32_t)smem_desc_sw128(smem_u32(p_s + g * 2 * kPBytes));
+      const uint32_t tmem_o = tmem_base + 256u + (uint32_t)(g * kHd);
       // S[g][i & 1] = Q_g K_i^T over the two 64-dim halves, 4 steps of 16 dims (32 bytes) in each
-      auto issue_qk = [&](int g, int i) {
-        const int s = i % kStages;
+      auto issue_qk = [&](int i) {
+        const uint32_t ks = k_lo + (uint32_t)((i % kStages) * (kTileBytes >> 4));
         const uint32_t tmem_s = tmem_base + (uint32_t)((g * 2 + (i & 1)) * kKeys);
 #pragma unroll
-        for (int kk = 0; kk < kHd / kUmmaK; ++kk) {
-          const uint64_t da =
-              smem_desc_sw128(smem_u32(q_s + g * kQBytes + (kk / 4) * (kQBytes / 2))) + (uint64_t)((kk % 4) * 2);
-          const uint64_t db =
-              smem_desc_sw128(smem_u32(k_s + s * kTileBytes + (kk / 4) * (kTileBytes / 2))) + (uint64_t)((kk % 4) * 2);
-          umma_f16(tmem_s, da, db, idesc_qk, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < kHd / kUmmaK; ++kk)
+          umma_f16_words(tmem_s, q_lo + (uint32_t)((kk / 4) * (kQBytes / 2 >> 4) + (kk % 4) * 2), hi_k,
+                         ks + (uint32_t)((kk / 4) * (kTileBytes / 2 >> 4) + (kk % 4) * 2), hi_k, idesc_qk, kk > 0 ? 1u : 0u);
         umma_commit(&s_full[g][i & 1]);
       };
       bool ok = mbar_wait(&q_full, 0) && mbar_wait(&kv_full[0], 0);
       if (ok) {
         tc_fence_after();
-        for (int g = 0; g < n_q; ++g) issue_qk(g, 0);
+        issue_qk(0);
       }
       for (int i = 0; i < nt_max && ok; ++i) {
         if (i + 1 < nt_max) {
           if (!mbar_wait(&kv_full[(i + 1) % kStages], ((i + 1) / kStages) & 1) || SIAR_ABORTED()) { ok = false; break; }
           tc_fence_after();
-          for (int g = 0; g < n_q; ++g)
-            if (i + 1 < nt[g]) issue_qk(g, i + 1);
+          issue_qk(i + 1);
         }
-        const int s = i % kStages;
-        for (int g = 0; g < n_q && ok; ++g) {
-          if (i >= nt[g]) continue;
-          if (!mbar_wait(&p_full[g], i & 1) || SIAR_ABORTED()) { ok = false; break; }
-          tc_fence_after();
-          // O_g += P_g V_i: 4 steps of 16 keys; V rows (keys) are 128 bytes of one dim half,
-          // 8-row groups 1024 bytes apart, the two dim halves 8 KiB apart
-          const uint32_t tmem_o = tmem_base + 256u + (uint32_t)(g * kHd);
+        if (!mbar_wait(&p_full[g][i & 1], (i >> 1) & 1) || SIAR_ABORTED()) { ok = false; break; }
+        tc_fence_after();
+        // O_g += P_g V_i: 4 steps of 16 keys; V rows (keys) are 128 bytes of one dim half,
+        // 8-row groups 1024 bytes apart, the two dim halves 8 KiB apart
+        const uint32_t ps = p_lo + (uint32_t)((i & 1) * (kPBytes >> 4));
+        const uint32_t vs = v_lo + (uint32_t)((i % kStages) * (kTileBytes >> 4));
 #pragma unroll
-          for (int t = 0; t < kKeys / kUmmaK; ++t) {
-            const uint64_t da = smem_desc_sw128(smem_u32(p_s + g * kPBytes)) + (uint64_t)(t * 2);
-            const uint64_t db = smem_desc_sw128_mn(smem_u32(v_s + s * kTileBytes + t * 2048), kTileBytes / 2);
-            umma_f16(tmem_o, da, db, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
-          }
-          umma_commit(&pv_full[g]);
-        }
-        if (ok) umma_commit(&kv_empty[s]);
+        for (int t = 0; t < kKeys / kUmmaK; ++t)
+          umma_f16_words(tmem_o, ps + (uint32_t)(t * 2), hi_k, vs + (uint32_t)(t * (2048 >> 4)), hi_v, idesc_pv,
+                         (i > 0 || t > 0) ? 1u : 0u);
+        umma_commit(&pv_full[g][i & 1]);
+        umma_commit(&kv_empty[i % kStages]);
       }
       if (!ok) SIAR_FAIL();
     }
-  } else if ((warp - 2) / 4 < n_q) {
+  } else if (warp >= 4 && (warp - 4) / 4 < n_q) {
     // ---------------- softmax: one thread per row, one group of four warps per query tile
-    const int g = (warp - 2) / 4;
+    const int g = (warp - 4) / 4;
     const int quad = warp & 3;                 // the tensor-memory lanes this warp may touch
     const int row = quad * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
@@ -235,7 +244,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int kv_end = row < rows_q[g] ? base + rg / G + 1 : 0;
     const float sl2 = prm.scale * 1.4426950408889634f;
     const int n_tiles = nt[g];
-    unsigned char* prow = p_s + g * kPBytes + row * 128;
+    unsigned char* prow0 = p_s + g * 2 * kPBytes + row * 128;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
@@ -255,34 +264,41 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int j = 0; j < 64; ++j)
           if (j0 + j >= kv_end) sr[j] = 0xff800000u;      // -inf
       }
-      float raw = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < 64; ++j) raw = fmaxf(raw, __uint_as_float(sr[j]));
+      for (int j = 0; j < 64; j += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(sr[j + e]));
+      }
+      const float raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const float m_new = fmaxf(m_used, raw * sl2);
       const bool need = m_new > m_used + kRescaleGap;      // also true for the first finite maximum
-      if (i > 0) {
-        // P's buffer and O are free once the previous tile's P.V has completed
-        if (!mbar_wait(&pv_full[g], (i - 1) & 1) || SIAR_ABORTED()) { ok = false; break; }
+      if (i > 0 && __any_sync(0xffffffffu, need)) {
+        // O may be touched once the previous tile's P.V has completed
+        if (!mbar_wait(&pv_full[g][(i - 1) & 1], ((i - 1) >> 1) & 1) || SIAR_ABORTED()) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, need)) {
-          const float alpha = need ? (m_used == -INFINITY ? 0.f : ex2(m_used - m_new)) : 1.f;
-          l *= alpha;
+        const float alpha = need ? (m_used == -INFINITY ? 0.f : ex2(m_used - m_new)) : 1.f;
+        l *= alpha;
 #pragma unroll 1
-          for (int ch = 0; ch < kHd / 32; ++ch) {
-            uint32_t o[32];
-            SIAR_TMEM_LD_32(tmem_o + ch * 32, o);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int ch = 0; ch < kHd / 32; ++ch) {
+          uint32_t o[32];
+          SIAR_TMEM_LD_32(tmem_o + ch * 32, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            SIAR_TMEM_ST_32(tmem_o + ch * 32, o);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          SIAR_TMEM_ST_32(tmem_o + ch * 32, o);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       if (need) m_used = m_new;
       const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      // P's buffer is free once the P.V of two tiles ago has completed
+      if (i >= 2) {
+        if (!mbar_wait(&pv_full[g][i & 1], ((i - 2) >> 1) & 1) || SIAR_ABORTED()) { ok = false; break; }
+      }
       // P = 2^(s c - m) as bf16, written as this row's 128 bytes with the 16-byte pieces swizzled
-      float sum = 0.f;
+      unsigned char* prow = prow0 + (i & 1) * kPBytes;
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t pk[4];
@@ -290,22 +306,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int e = 0; e < 4; ++e) {
           const float p0 = ex2(fmaf(__uint_as_float(sr[c * 8 + 2 * e]), sl2, neg_m));
           const float p1 = ex2(fmaf(__uint_as_float(sr[c * 8 + 2 * e + 1]), sl2, neg_m));
-          sum += p0;
-          sum += p1;
+          sum[e] += p0 + p1;
           pk[e] = pack_bf16x2(p0, p1);
         }
         *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l += sum;
+      l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
       fence_async_smem();
       tc_fence_before();
       if (g == 0)
         asm volatile("bar.sync 1, 128;" ::: "memory");
       else
         asm volatile("bar.sync 2, 128;" ::: "memory");
-      if ((threadIdx.x & 127) == 64) mbar_arrive(&p_full[g]);
+      if ((threadIdx.x & 127) == 0) mbar_arrive(&p_full[g][i & 1]);
     }
-    if (ok) ok = mbar_wait(&pv_full[g], (n_tiles - 1) & 1);
+    if (ok) ok = mbar_wait(&pv_full[g][(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
     if (!ok) {
       SIAR_FAIL();
     } else {
