@@ -79,16 +79,34 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
 
   const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
-  const int kv_len = base_len[b] + 1;
+  // The prologue is a chain of dependent reads (lengths -> table -> tiles; row -> query), each a
+  // trip to L2: everything that has its address is asked for before anything is used.
+  const int base_b = base_len[b], slot = slot_ids[b], row_b = q_start[b];
+  const int kv_len = base_b + 1;
   const int c0 = c * chunk_keys;
   if (c0 >= kv_len) return;
   SIAR_STAMP(0);
   const int c_end = min(kv_len, c0 + chunk_keys);
   const int n_it = (c_end - c0 + 4 * WK - 1) / (4 * WK);
-  const int slot = slot_ids[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int* table = block_table + (size_t)slot * max_pages;
+  static_assert(D / 2 <= 128, "one thread per rotation frequency");
+  const float freq = fuse_rope && inv_freq != nullptr && threadIdx.x < D / 2 ? __ldg(inv_freq + threadIdx.x) : 0.f;
+  // query fragments straight from global memory: rows g and g + 8 of the (padded) group
+  const size_t tok_row = (size_t)row_b * (Hq + 2 * Hkv) * D;
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qrow = qkv + tok_row + (size_t)kvh * G * D;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int col = kk * 16 + q * 2;
+      qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
+      qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
+      qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
+      qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+  }
 
   // The page of a tile is read from the block table one step before the tile is requested, so
   // that the (dependent) table read never sits in front of the loads it feeds.
@@ -123,31 +141,19 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     if (pre < n_it) load_tile(pre, pre, pages[pre]);
     cp_async_commit();
   }
+  SIAR_STAMP(7);
   int page_ahead = pages[kDecodeStages - 1];      // page of tile it + kDecodeStages - 1 at step it
   const int pos = kv_len - 1;                      // position of the new token
   if (fuse_rope) {
-    for (int i = threadIdx.x; i < D / 2; i += blockDim.x) {
+    if (threadIdx.x < D / 2) {
       float sn = 0.f, cs = 1.f;
-      if (inv_freq != nullptr) sincosf((float)pos * __ldg(inv_freq + i), &sn, &cs);
-      cs_s[i] = cs;
-      cs_s[D / 2 + i] = sn;
+      if (inv_freq != nullptr) sincosf((float)pos * freq, &sn, &cs);
+      cs_s[threadIdx.x] = cs;
+      cs_s[D / 2 + threadIdx.x] = sn;
     }
     __syncthreads();
   }
-  const size_t tok_row = (size_t)q_start[b] * (Hq + 2 * Hkv) * D;
-
-  // query fragments straight from global memory: rows g and g + 8 of the (padded) group
-  uint32_t qa[D / 16][4];
   {
-    const __nv_bfloat16* qrow = qkv + (size_t)q_start[b] * (Hq + 2 * Hkv) * D + (size_t)kvh * G * D;
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      const int col = kk * 16 + q * 2;
-      qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
-      qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
-      qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
-      qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
-    }
     if (fuse_rope) {
       // columns c < D/2 pair with c + D/2: fragment kk pairs with fragment kk + D/32, same register
 #pragma unroll

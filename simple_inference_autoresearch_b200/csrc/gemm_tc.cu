@@ -49,6 +49,19 @@ struct GemmParams {
   int kb_per_split;   // k-blocks of 64 per split
   int x_is_weight;    // X is written by no kernel (swap-AB): its tiles may load before pdl_wait()
   int swiglu;         // weight rows interleaved (gate_j, up_j): write silu(gate) * up, half as many outputs
+  // Fused residual stream (small-batch kernel with BN = 16 only):
+  //  * accumulate: C (float32) += D instead of C = D, and ss_out[q][tile] receives the sum of squares
+  //    of the new C over the 128 outputs of tile blockIdx.x, for the norm that follows;
+  //  * y_resid: the activation operand is not loaded but made: row q of it is
+  //    rmsnorm(y_resid[q]) * norm_w, with the sum of squares taken from ss_in[q][0..ss_tiles).
+  int accumulate;
+  float* ss_out;
+  const float* y_resid;
+  const float* ss_in;
+  const __nv_bfloat16* norm_w;
+  float eps;
+  int ss_tiles;
+  int y_ld;
 #ifdef SIAR_TIMING
   unsigned long long* stamps;   // [blocks][8] globaltimer marks, for profiling builds only
 #endif
@@ -81,9 +94,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   __shared__ __align__(8) uint64_t tmem_full_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float ss_red[4][16];
 
   const uint32_t dyn = smem_u32(smem_dyn);
   unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
+  const bool make_y = BN == 16 && prm.y_resid != nullptr;   // the epilogue warps produce the activation tiles
 
   pdl_launch_dependents();
   SIAR_TRACE(10, 0);
@@ -98,7 +113,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], make_y ? 129 : 1);     // the TMA thread, and the 128 threads that write Y
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full_bar, 1);
@@ -118,6 +133,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   float* stage = reinterpret_cast<float*>(tiles);
   TOut* C = (TOut*)prm.C;
   bool acc_ok = false;      // epilogue threads: the accumulator in tensor memory is complete
+  float old_c[16];          // accumulate: the values of C this thread adds to
+#pragma unroll
+  for (int j = 0; j < 16; ++j) old_c[j] = 0.f;
 
   {
   if (dead) {
@@ -131,16 +149,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // Weights do not depend on earlier kernels: when X is the weight, the first STAGES
       // tiles of it are requested before this grid waits for its predecessors.
       const int pre = prm.x_is_weight ? min(STAGES, num_kb) : 0;
+      const uint32_t tx_bytes = make_y ? kXBytes : kStageBytes;
       for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&full_bar[i], kStageBytes);
+        mbar_expect_tx(&full_bar[i], tx_bytes);
         tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
       }
       SIAR_STAMP(1);
       pdl_wait();
       SIAR_TRACE(10, 2);
       SIAR_STAMP(2);
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
+      if (!make_y)
+        for (int i = 0; i < pre; ++i)
+          tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
       issued = pre;
       for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
@@ -151,9 +171,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           break;
         }
         unsigned char* xs = tiles + (size_t)s * kStageBytes;
-        mbar_expect_tx(&full_bar[s], kStageBytes);
+        mbar_expect_tx(&full_bar[s], tx_bytes);
         tma_load_2d(xs, &tmX, &full_bar[s], (kb_begin + i) * kBK, p0);
-        tma_load_2d(xs + kXBytes, &tmY, &full_bar[s], (kb_begin + i) * kBK, q0);
+        if (!make_y) tma_load_2d(xs + kXBytes, &tmY, &full_bar[s], (kb_begin + i) * kBK, q0);
         issued = i + 1;
       }
       if (*(volatile int*)&abort_flag) {
@@ -192,8 +212,86 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const int quad = warp & 3;
     pdl_wait();   // C may still be read by an earlier kernel
     bool ok = true;
+    if constexpr (BN == 16 && sizeof(TOut) == 4) {
+      // accumulate: this thread's outputs (tile row threadIdx.x - 64, its rank's columns) are read
+      // now, long before the sums arrive
+      if (prm.accumulate && !make_y) {
+        const int pp = p0 + (int)threadIdx.x - 64;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int jq = splits > 1 ? j * splits + (int)blockIdx.z : j;
+          const int q = q0 + jq;
+          old_c[j] = (jq < BN && q < prm.Q && pp < prm.P)
+                         ? reinterpret_cast<const float*>(C)[(long long)q * prm.ldc + pp] : 0.f;
+        }
+      }
+    }
+    if constexpr (BN == 16) {
+      if (make_y) {
+        // ---------------- the activation tiles, made here: thread (row, piece) owns 8 consecutive
+        // columns of one of the 16 rows in every k-block; values are read PF k-blocks ahead.
+        const int pt = threadIdx.x - 64, row = pt >> 3, piece = pt & 7;
+        const int qrow = q0 + row;
+        const bool live = qrow < prm.Q;
+        const float* src = prm.y_resid + (size_t)(live ? qrow : 0) * prm.y_ld + piece * 8;
+        const __nv_bfloat16* wsrc = prm.norm_w + piece * 8;
+        constexpr int PF = 6;
+        float4 a0[PF], a1[PF];
+        uint4 wv[PF];
+        auto fetch = [&](int i, float4& x0, float4& x1, uint4& w) {
+          const int k = (kb_begin + i) * kBK;
+          if (live && i < num_kb && k + piece * 8 < prm.K) {
+            x0 = *reinterpret_cast<const float4*>(src + k);
+            x1 = *reinterpret_cast<const float4*>(src + k + 4);
+            w = *reinterpret_cast<const uint4*>(wsrc + k);
+          } else {
+            x0 = x1 = make_float4(0.f, 0.f, 0.f, 0.f);
+            w = make_uint4(0u, 0u, 0u, 0u);
+          }
+        };
+#pragma unroll
+        for (int j = 0; j < PF; ++j) fetch(j, a0[j], a1[j], wv[j]);
+        // the row's sum of squares, asked for after the first values so that both are on their way together
+        float part = 0.f;
+        if (live)
+          for (int t = piece; t < prm.ss_tiles; t += 8) part += __ldg(prm.ss_in + (size_t)qrow * prm.ss_tiles + t);
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        const float inv = rsqrtf(part / (float)prm.K + prm.eps);
+        // k-blocks in groups of PF, so that every buffer has a fixed register and a value is
+        // touched only when its k-block comes up (PF k-blocks after it was asked for)
+        for (int i0 = 0; i0 < num_kb && ok; i0 += PF) {
+#pragma unroll
+          for (int u = 0; u < PF; ++u) {
+            const int i = i0 + u;
+            if (i >= num_kb) break;
+            const int s = i % STAGES;
+            if (!mbar_wait(&empty_bar[s], ((i / STAGES) & 1) ^ 1) || *(volatile int*)&abort_flag) {
+              abort_flag = 1;
+              atomicOr(prm.status, kStatusWaitExpired);
+              ok = false;
+              break;
+            }
+            const float2 w01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].x));
+            const float2 w23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].y));
+            const float2 w45 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].z));
+            const float2 w67 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].w));
+            uint4 pk;
+            pk.x = pack_bf16x2(a0[u].x * inv * w01.x, a0[u].y * inv * w01.y);
+            pk.y = pack_bf16x2(a0[u].z * inv * w23.x, a0[u].w * inv * w23.y);
+            pk.z = pack_bf16x2(a1[u].x * inv * w45.x, a1[u].y * inv * w45.y);
+            pk.w = pack_bf16x2(a1[u].z * inv * w67.x, a1[u].w * inv * w67.y);
+            *reinterpret_cast<uint4*>(tiles + (size_t)s * kStageBytes + kXBytes + row * 128 + ((piece ^ (row & 7)) << 4)) = pk;
+            fence_async_smem();
+            mbar_arrive(&full_bar[s]);
+            fetch(i + PF, a0[u], a1[u], wv[u]);
+          }
+        }
+      }
+    }
     if (num_kb > 0) {
-      ok = mbar_wait(&tmem_full_bar, 0);
+      ok = mbar_wait(&tmem_full_bar, 0) && ok;
       if (!ok) { abort_flag = 1; atomicOr(prm.status, kStatusWaitExpired); }
     }
     tc_fence_after();
@@ -267,13 +365,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     if (warp >= 2 && !dead) {
       const int pp = p0 + et;
       const float* mine = reinterpret_cast<const float*>(tiles);
-      for (int jl = 0; jl < NL; ++jl) {
+      bool stored = false;
+      if constexpr (BN == 16 && sizeof(TOut) == 4) {
+        if (prm.accumulate) {
+          stored = true;
+#pragma unroll
+          for (int jl = 0; jl < 8; ++jl) {               // NL <= 8: 16 outputs over at least 2 ranks
+            const int jq = jl * splits + rank;
+            const int q = q0 + jq;
+            if (jl >= NL || jq >= BN || q >= prm.Q) break;
+            float acc = 0.f;
+            for (int z = 0; z < splits; ++z) acc += mine[(z * NL + jl) * 128 + et];
+            float r = 0.f;
+            if (pp < prm.P) {
+              r = old_c[jl] + acc;
+              reinterpret_cast<float*>(C)[(long long)q * prm.ldc + pp] = r;
+            }
+            const float v = warp_sum(r * r);
+            if (lane == 0) ss_red[et >> 5][jl] = v;
+          }
+        }
+      }
+      for (int jl = 0; jl < NL && !stored; ++jl) {
         const int jq = jl * splits + rank;
         const int q = q0 + jq;
         if (jq >= BN || q >= prm.Q) break;
         float acc = 0.f;
         for (int z = 0; z < splits; ++z) acc += mine[(z * NL + jl) * 128 + et];
         if (pp < prm.P) store_out<TOut>(C + (long long)q * prm.ldc + pp, acc);
+      }
+      if constexpr (BN == 16 && sizeof(TOut) == 4) {
+        if (prm.accumulate) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int jq = et * splits + rank;
+          if (et < NL && jq < BN && q0 + jq < prm.Q)
+            prm.ss_out[(size_t)(q0 + jq) * gridDim.x + blockIdx.x] =
+                (ss_red[0][et] + ss_red[1][et]) + (ss_red[2][et] + ss_red[3][et]);
+        }
       }
     }
   } else if (warp >= 2 && !dead) {
@@ -291,8 +419,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     } else if (prm.transpose_out) {
       // C[q][p]: for a fixed q the 128 tile rows are contiguous
       const int pp = p0 + et;
-      if (pp < prm.P) {
-        const int cols = min(BN, prm.Q - q0);
+      const int cols = min(BN, prm.Q - q0);
+      bool stored = false;
+      if constexpr (BN == 16 && sizeof(TOut) == 4) {
+        if (prm.accumulate) {
+#pragma unroll
+          for (int jq = 0; jq < 16; ++jq) {
+            if (jq >= cols) break;
+            float r = 0.f;
+            if (pp < prm.P) {
+              r = old_c[jq] + stage[et * LD + jq];
+              reinterpret_cast<float*>(C)[(long long)(q0 + jq) * prm.ldc + pp] = r;
+            }
+            const float v = warp_sum(r * r);
+            if (lane == 0) ss_red[ew][jq] = v;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et < cols)
+            prm.ss_out[(size_t)(q0 + et) * gridDim.x + blockIdx.x] =
+                (ss_red[0][et] + ss_red[1][et]) + (ss_red[2][et] + ss_red[3][et]);
+          stored = true;
+        }
+      }
+      if (!stored && pp < prm.P) {
         for (int jq = 0; jq < cols; ++jq)
           store_out<TOut>(C + (long long)(q0 + jq) * prm.ldc + pp, stage[et * LD + jq]);
       }
@@ -639,13 +788,23 @@ extern "C" void siar_gemm_tc_set_split_target(int blocks_per_sm) { g_split_targe
 //   max_splits caps the split along K (1 = never split; at most 8, the portable cluster size).
 //   epilogue 1: W's rows are interleaved (gate_0, up_0, gate_1, up_1, ...) and C [M, N/2] bf16 receives
 //   silu(gate) * up (never split along K).
-extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
-                                 int max_splits, int epilogue, int* status, int sm_count, void* stream) {
+//   epilogue 2 (at most 16 rows): C [M,N] float32 += the product, and ss_out [M, ceil(N/128)] receives, per
+//   block of 128 outputs, the sum of squares of the new C (what the rmsnorm that follows needs).
+//   resid != nullptr (at most 16 rows; A is not read): the activations are rmsnorm(resid [M,K] float32) *
+//   norm_w with eps, the sums of squares of the rows given in pieces as ss_in [M, ss_tiles].
+static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, int out_f32, int max_splits,
+                    int epilogue, int* status, int sm_count, void* stream, const float* resid, const float* ss_in,
+                    int ss_tiles, const void* norm_w, float eps, float* ss_out) {
   if (M <= 0 || N <= 0) return 0;
-  if (epilogue != 0 && (epilogue != 1 || out_f32 || (N & 1))) return -1;
+  if (epilogue < 0 || epilogue > 2) return -1;
+  if (epilogue == 1 && (out_f32 || (N & 1))) return -1;
+  if (epilogue == 2 && (!out_f32 || M > 16 || ss_out == nullptr)) return -1;
+  if (resid != nullptr && epilogue == 2) return -1;
+  if (resid != nullptr && (M > 16 || ss_in == nullptr || norm_w == nullptr || ss_tiles <= 0)) return -1;
   if (epilogue == 1) max_splits = 1;
   if (K % 8 != 0 || K < 8) return -1;                       // TMA needs 16-byte row strides
-  if (((uintptr_t)A | (uintptr_t)W) & 15) return -1;
+  if (resid != nullptr) A = W;                               // a valid (unused) operand for the tensor map
+  if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)resid | (uintptr_t)norm_w) & 15) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   const bool swap = M <= 128;
   const void* X = swap ? W : A;
@@ -655,7 +814,9 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   if (swap) BN = Q <= 16 ? 16 : Q <= 32 ? 32 : Q <= 64 ? 64 : 128;
   else BN = Q >= 256 ? 256 : 128;
   CUtensorMap tmX, tmY;
-  if (!tensor_map(X, P, K, kBM, &tmX) || !tensor_map(Y, Q, K, BN, &tmY)) return -1;
+  if (!tensor_map(X, P, K, kBM, &tmX)) return -1;
+  if (resid != nullptr) tmY = tmX;
+  else if (!tensor_map(Y, Q, K, BN, &tmY)) return -1;
 
   const int tiles = ((P + kBM - 1) / kBM) * ((Q + BN - 1) / BN);
   const int num_kb = (K + kBK - 1) / kBK;
@@ -679,6 +840,14 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
   prm.transpose_out = swap ? 1 : 0;
   prm.kb_per_split = kbps;
   prm.x_is_weight = swap ? 1 : 0;
+  prm.accumulate = epilogue == 2 ? 1 : 0;
+  prm.ss_out = ss_out;
+  prm.y_resid = resid;
+  prm.ss_in = ss_in;
+  prm.norm_w = (const __nv_bfloat16*)norm_w;
+  prm.eps = eps;
+  prm.ss_tiles = ss_tiles;
+  prm.y_ld = K;
 #ifdef SIAR_TIMING
   prm.stamps = g_stamps;
 #endif
@@ -701,4 +870,20 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
     default: SIAR_GO(256, 4);
   }
 #undef SIAR_GO
+}
+
+extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
+                                 int max_splits, int epilogue, int* status, int sm_count, void* stream) {
+  if (epilogue == 2) return -1;
+  return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, nullptr, nullptr, 0,
+                  nullptr, 0.f, nullptr);
+}
+
+// The same product inside a float32 residual stream, for at most 16 rows (see run_gemm).
+extern "C" int siar_gemm_tc_bf16_fused(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
+                                       int max_splits, int epilogue, int* status, int sm_count, void* stream,
+                                       const float* resid, const float* ss_in, int ss_tiles, const void* norm_w,
+                                       float eps, float* ss_out) {
+  return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, resid, ss_in, ss_tiles,
+                  norm_w, eps, ss_out);
 }

@@ -62,6 +62,7 @@ class StepContext:
         self.dtype = dtype
         self.meta = meta
         self.cache = cache
+        self.residual = None      # set by a block: the stream a sublayer's last product may add into
 
 
 class DecoderModel:
@@ -154,6 +155,8 @@ class DecoderModel:
                                                              e.writes_cache)
         if meta.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
+        if isinstance(pending, ops.Added):      # the last sublayer added itself
+            pending = None
         if not meta.want_is_identity:
             residual = ops.gather_rows(residual, meta.want_rows)
             if pending is not None:

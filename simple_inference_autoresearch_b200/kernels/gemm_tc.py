@@ -17,6 +17,7 @@ _state = {}
 #: cap of the split along K for products with few output tiles (1 disables it)
 max_splits = 8
 _fn = None
+_fn_fused = None
 enabled = True
 
 
@@ -33,6 +34,19 @@ def _bind():
     return _fn
 
 
+def _bind_fused():
+    global _fn_fused
+    if _fn_fused is None:
+        f = build.load_unit("gemm_tc").siar_gemm_tc_bf16_fused
+        c = ctypes
+        f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                      c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_float,
+                      c.c_void_p]
+        f.restype = c.c_int
+        _fn_fused = f
+    return _fn_fused
+
+
 def _device_state(device: torch.device):
     key = device.index if device.index is not None else torch.cuda.current_device()
     st = _state.get(key)
@@ -42,22 +56,43 @@ def _device_state(device: torch.device):
     return st
 
 
-def try_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> bool:
+def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=None, ss_out=None) -> bool:
     """out[M, N] = x[M, K] @ w[N, K]^T; False when the shape is refused (nothing launched).
-    ``epilogue=1``: w's rows alternate (gate, up) and out[M, N/2] = silu(gate) * up."""
+    ``epilogue=1``: w's rows alternate (gate, up) and out[M, N/2] = silu(gate) * up.
+    ``epilogue=2`` (at most 16 rows): out (float32) += the product and ``ss_out`` [M, ceil(N/128)]
+    receives partial sums of squares of the new rows of out.
+    ``normed`` (an ``ops.NormedResidual`` of at most 16 rows; x is None): the kernel makes the
+    activations rmsnorm(residual) * weight itself."""
     if not enabled:
         return False
     from . import ops
 
-    fn = _bind()
-    m, k = x.shape
     n = w.shape[0]
-    st = _device_state(x.device)
-    err = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32), max_splits,
-             int(epilogue), ops.status_word(x.device).data_ptr(), st["sms"], torch.cuda.current_stream().cuda_stream)
+    dev = w.device
+    st = _device_state(dev)
+    status = ops.status_word(dev).data_ptr()
+    stream = torch.cuda.current_stream().cuda_stream
+    if normed is not None or epilogue == 2:
+        if normed is not None:
+            m, k = normed.residual.shape
+            assert k == w.shape[1] and normed.ss_parts.shape[0] == m and normed.ss_parts.is_contiguous()
+            extra = (normed.residual.data_ptr(), normed.ss_parts.data_ptr(), normed.ss_parts.shape[1],
+                     normed.weight.data_ptr(), float(normed.eps))
+            xp = None
+        else:
+            m, k = x.shape
+            extra = (None, None, 0, None, 0.0)
+            xp = x.data_ptr()
+        err = _bind_fused()(xp, w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32), max_splits,
+                            int(epilogue), status, st["sms"], stream, *extra,
+                            None if ss_out is None else ss_out.data_ptr())
+    else:
+        m, k = x.shape
+        err = _bind()(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
+                      max_splits, int(epilogue), status, st["sms"], stream)
     if err == -1:
         return False
     if err != 0:
-        raise RuntimeError(f"siar_gemm_tc_bf16 failed to launch: CUDA error {err}")
+        raise RuntimeError(f"the tensor-core product failed to launch: CUDA error {err}")
     ops.launch_count += 1
     return True

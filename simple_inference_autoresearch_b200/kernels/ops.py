@@ -185,8 +185,61 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """y[M, N] = x[M, K] @ w[N, K]^T with 32-bit accumulation."""
+#: False = the products never take over the residual add and the norm (tests compare both ways)
+fuse_residual_stream = True
+
+
+class Added:
+    """Stands for a sublayer output that the product kernel has already added into the residual
+    stream.  ``ss_parts`` [rows, pieces] float32 holds, for every row, partial sums of squares of
+    the updated residual: what the rmsnorm that follows needs instead of a pass over the row."""
+
+    __slots__ = ("ss_parts",)
+
+    def __init__(self, ss_parts: torch.Tensor):
+        self.ss_parts = ss_parts
+
+
+class NormedResidual:
+    """``rmsnorm(residual) * weight`` that has not been computed: ``linear`` and ``linear_swiglu``
+    take it in place of their input and, where their kernel can, make the normed activations
+    themselves from the float32 residual and the sums of squares an ``Added`` carried.  Anything
+    else calls ``materialize``."""
+
+    __slots__ = ("residual", "ss_parts", "weight", "eps", "dtype")
+
+    def __init__(self, residual: torch.Tensor, ss_parts: torch.Tensor, weight: torch.Tensor, eps: float,
+                 dtype: torch.dtype):
+        self.residual, self.ss_parts, self.weight, self.eps, self.dtype = residual, ss_parts, weight, eps, dtype
+
+    @property
+    def shape(self):
+        return self.residual.shape
+
+    def materialize(self) -> torch.Tensor:
+        return add_rmsnorm(self.residual, None, self.weight, self.eps, self.dtype)
+
+
+def _fused_input(x: "NormedResidual", w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
+    if not (fuse_residual_stream and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.weight.dtype == torch.bfloat16 and x.residual.shape[0] <= 16):
+        return False
+    from . import gemm_tc
+    return gemm_tc.try_linear(None, w, out, epilogue=epilogue, normed=x)
+
+
+def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Tensor] = None):
+    """y[M, N] = x[M, K] @ w[N, K]^T with 32-bit accumulation.
+
+    ``x`` may be a ``NormedResidual``.  With ``add_to`` (the float32 residual [M, N]) the kernel may
+    add y into it instead of returning it; the result is then an ``Added``, otherwise y as always
+    (the caller adds it later)."""
+    if isinstance(x, NormedResidual):
+        if add_to is None and out_dtype in (torch.float32, x.dtype):
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=w.device)
+            if _fused_input(x, w, out, 0):
+                return out
+        x = x.materialize()
     _need_cuda(x, w)
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous()
@@ -197,6 +250,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
         raise TypeError(f"linear: output dtype {out_dtype} with input dtype {x.dtype}")
     if x.dtype == torch.bfloat16:
         from . import gemm_tc
+        if (add_to is not None and fuse_residual_stream and out_dtype == torch.float32 and m <= 16
+                and add_to.dtype == torch.float32 and add_to.shape == (m, n) and add_to.is_contiguous()):
+            ss = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device)
+            if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss):
+                return Added(ss)
         if gemm_tc.try_linear(x, w, out):
             return out
     _launch("gemm_simt", "siar_gemm_nt_simt", _is_bf16(x.dtype), int(out_dtype == torch.float32), _ptr(x),
@@ -397,7 +455,13 @@ def swiglu(gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wg^T) * (x @ Wu^T) for a weight whose rows alternate (gate_0, up_0, gate_1, ...);
     returns [M, N/2] in x's dtype.  On the bfloat16 path the activation runs in the product's
-    epilogue on the float32 accumulators; otherwise it is a product followed by ``swiglu``."""
+    epilogue on the float32 accumulators; otherwise it is a product followed by ``swiglu``.
+    ``x`` may be a ``NormedResidual``."""
+    if isinstance(x, NormedResidual):
+        out = torch.empty((x.shape[0], w_interleaved.shape[0] // 2), dtype=x.dtype, device=w_interleaved.device)
+        if w_interleaved.shape[0] % 2 == 0 and _fused_input(x, w_interleaved, out, 1):
+            return out
+        x = x.materialize()
     _need_cuda(x, w_interleaved)
     assert x.dim() == 2 and w_interleaved.dim() == 2 and x.shape[1] == w_interleaved.shape[1]
     assert w_interleaved.shape[0] % 2 == 0 and x.dtype == w_interleaved.dtype

@@ -57,10 +57,12 @@ class GroupedQueryAttention(Mixer):
     def extension_units(self):
         return ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
 
-    def forward(self, ctx, x: torch.Tensor, cache_entry, writes_cache: bool = True) -> torch.Tensor:
+    takes_deferred_norm = True
+
+    def forward(self, ctx, x, cache_entry, writes_cache: bool = True):
         qkv = ops.linear(x, self.w_qkv, ctx.dtype)
         rotary = self.position.rotary() if self.position is not None else None
         attn = ops.rope_and_attention(qkv, rotary.inv_freq if rotary is not None else None, cache_entry, ctx.meta,
                                       self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                       write_kv=writes_cache)
-        return ops.linear(attn, self.w_o, torch.float32)
+        return ops.linear(attn, self.w_o, torch.float32, add_to=ctx.residual)

@@ -142,6 +142,12 @@ class Norm(Part):
         """residual += delta (in place, 32-bit), then return normed(residual)."""
         raise NotImplementedError
 
+    def deferred(self, ctx, residual: torch.Tensor, added):
+        """normed(residual) for a consumer that ``takes_deferred_norm``, after a sublayer whose
+        output is already in ``residual`` (``added``: an ``ops.Added``).  A norm whose arithmetic
+        the product kernels can take over returns an ``ops.NormedResidual``; the default computes."""
+        return self.norm(ctx, residual)
+
 
 class PositionEncoding(Part):
     def rotary(self):
@@ -155,18 +161,27 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: True when ``forward`` hands x to ``ops.linear`` / ``ops.linear_swiglu`` only, so that x may be
+    #: an ``ops.NormedResidual`` instead of a tensor
+    takes_deferred_norm = False
+
     def cache_need(self):
         """``KVNeed``, ``StateNeed`` or None."""
         return None
 
     def forward(self, ctx, x: torch.Tensor, cache_entry, writes_cache: bool) -> torch.Tensor:
-        """x: normed activations [N, H] (compute dtype) -> float32 delta [N, H]."""
+        """x: normed activations [N, H] (compute dtype) -> float32 delta [N, H].  A part whose last
+        step is ``ops.linear(..., torch.float32, add_to=ctx.residual)`` may return what that call
+        returns: the delta, or the mark that it is already in the residual."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
+    takes_deferred_norm = False       # as for Mixer
+
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        """x: normed activations [N, H] (compute dtype) -> float32 delta [N, H]."""
+        """x: normed activations [N, H] (compute dtype) -> float32 delta [N, H] (or, as for a
+        mixer, the result of ``ops.linear(..., add_to=ctx.residual)``)."""
         raise NotImplementedError
 
 

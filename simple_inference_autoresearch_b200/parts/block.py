@@ -2,7 +2,8 @@
 
 The adds are threaded the way the reference threads them (model/block.py:154-183):
 each sublayer's output is left *pending* and added inside the next norm's kernel,
-so no separate add is launched; the last block's pending delta is resolved by the
+so no separate add is launched (for a few rows the products themselves add into the
+residual and make the normed input of the next product: ``ops.Added``, ``ops.NormedResidual``); the last block's pending delta is resolved by the
 model's final norm (model/llama.py:194).  A first block that receives no pending
 delta only norms (model/block.py:164-166).
 """
@@ -13,6 +14,7 @@ from typing import List, Mapping
 
 import torch
 
+from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, PartSpec, TensorSpec
 
 
@@ -49,12 +51,22 @@ class PreNormBlock(Block):
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, ctx, residual, pending, cache_entry, writes_cache: bool = True):
+    @staticmethod
+    def _normed(norm, consumer, ctx, residual, pending):
+        """The consumer's input: norm(residual + pending), the add and the norm in one kernel, or
+        left to the consumer's first product where the sublayer before already added itself."""
         if pending is None:
-            h = self.mixer_norm.norm(ctx, residual)
-        else:
-            h = self.mixer_norm.add_norm(ctx, residual, pending)
+            return norm.norm(ctx, residual)
+        if isinstance(pending, ops.Added):
+            if consumer.takes_deferred_norm:
+                return norm.deferred(ctx, residual, pending)
+            return norm.norm(ctx, residual)
+        return norm.add_norm(ctx, residual, pending)
+
+    def forward(self, ctx, residual, pending, cache_entry, writes_cache: bool = True):
+        ctx.residual = residual       # where a sublayer's last product may add its output itself
+        h = self._normed(self.mixer_norm, self.mixer, ctx, residual, pending)
         a = self.mixer.forward(ctx, h, cache_entry, writes_cache)
-        h = self.ffn_norm.add_norm(ctx, residual, a)
+        h = self._normed(self.ffn_norm, self.ffn, ctx, residual, a)
         m = self.ffn.forward(ctx, h)
         return residual, m

@@ -47,6 +47,8 @@ class SwiGLU(FeedForward):
     def extension_units(self):
         return ("elementwise", "gemm_simt", "gemm_tc")
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+    takes_deferred_norm = True
+
+    def forward(self, ctx, x):
         f = ops.linear_swiglu(x, self.w_gate_up)
-        return ops.linear(f, self.w_down, torch.float32)
+        return ops.linear(f, self.w_down, torch.float32, add_to=ctx.residual)

@@ -46,3 +46,6 @@ class RMSNorm(Norm):
 
     def add_norm(self, ctx, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype)
+
+    def deferred(self, ctx, residual: torch.Tensor, added):
+        return ops.NormedResidual(residual, added.ss_parts, self.weight, self.eps, ctx.dtype)

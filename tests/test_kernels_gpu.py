@@ -392,6 +392,79 @@ def test_tensor_core_rows_do_not_depend_on_batch_within_an_orientation():
         assert torch.equal(part, whole[:rows])
 
 
+# ----------------------------------------------------------------------------- products inside the residual stream
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 4096, 14336), (8, 256, 128), (16, 384, 512), (5, 200, 72),
+                                   (3, 128, 4096), (16, 2048, 8192)])
+def test_product_adds_into_the_residual_and_leaves_sums_of_squares(m, n, k):
+    """epilogue 2: residual += x @ w^T in float32, and the per-piece sums of squares of the new
+    rows add up to the rows' sums of squares (split along K or not, ragged last piece)."""
+    from simple_inference_autoresearch_b200.kernels import gemm_tc
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    res0 = rnd(m, n, seed=3)
+    want = res0.double() + x.double() @ w.double().T
+    res = res0.to(DEV)
+    ss = torch.full((m, (n + 127) // 128), float("nan"), dtype=torch.float32, device=DEV)
+    assert gemm_tc.try_linear(x.to(DEV), w.to(DEV), res, epilogue=2, ss_out=ss), "shape refused"
+    ops.check_status(DEV)
+    bound = 1e-5 * k ** 0.5 + 1e-4
+    assert (res.cpu().double() - want).abs().max().item() <= bound
+    got_ss = ss.cpu().double()
+    assert not torch.isnan(got_ss).any()
+    for t in range(got_ss.shape[1]):
+        piece = res.cpu().double()[:, t * 128:(t + 1) * 128].pow(2).sum(1)
+        torch.testing.assert_close(got_ss[:, t], piece, rtol=1e-5, atol=1e-6)
+    # through ops.linear: the mark instead of a tensor, and the same residual
+    res2 = res0.to(DEV)
+    out = ops.linear(x.to(DEV), w.to(DEV), torch.float32, add_to=res2)
+    assert isinstance(out, ops.Added) and torch.equal(res2, res) and torch.equal(out.ss_parts, ss)
+
+
+@pytest.mark.parametrize("m,n,k,pieces", [(1, 6144, 4096, 32), (8, 28672, 4096, 32), (8, 256, 128, 1), (16, 384, 520, 5),
+                                          (5, 200, 72, 1), (3, 1024, 14336, 112)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_product_makes_its_own_normed_input(m, n, k, pieces, swiglu):
+    """The activation operand made inside the kernel from the float32 residual, the sums of squares
+    given in pieces, against add_rmsnorm followed by the plain product."""
+    eps = 1e-5
+    resid = rnd(m, k, seed=4, scale=2.0).to(DEV)
+    norm_w = (1.0 + rnd(k, seed=5, scale=0.1)).to(torch.bfloat16).to(DEV)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=6, scale=0.05).to(DEV)
+    # any split of the rows' sums of squares into pieces will do
+    cols = [resid[:, (k * i) // pieces:(k * (i + 1)) // pieces].double().pow(2).sum(1) for i in range(pieces)]
+    ss = torch.stack(cols, 1).float().contiguous()
+    lazy = ops.NormedResidual(resid, ss, norm_w, eps, torch.bfloat16)
+    x = ops.add_rmsnorm(resid.clone(), None, norm_w, eps, torch.bfloat16)
+    if swiglu:
+        got = ops.linear_swiglu(lazy, w)
+        ref = ops.linear_swiglu(x, w)
+    else:
+        got = ops.linear(lazy, w, torch.float32)
+        ref = ops.linear(x, w, torch.float32)
+    ops.check_status(DEV)
+    # the normed activations are rounded to bfloat16 in both; the sums of squares differ in their
+    # order of addition only, which may move single activations by one rounding step
+    plain = emu.add_rmsnorm(resid.cpu().clone(), None, norm_w.cpu(), eps, torch.bfloat16)
+    assert (x.cpu().float() - plain.float()).abs().max() <= 2e-2
+    scale = ref.float().abs().max().item()
+    assert (got.float() - ref.float()).abs().max().item() <= 4e-3 * scale + 1e-4, (m, n, k)
+
+
+def test_fused_residual_stream_is_refused_beyond_sixteen_rows_and_can_be_switched_off():
+    x = rnd(17, 256, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rnd(128, 256, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    res = rnd(17, 128, seed=3).to(DEV)
+    before = res.clone()
+    out = ops.linear(x, w, torch.float32, add_to=res)
+    assert isinstance(out, torch.Tensor) and torch.equal(res, before)       # the caller adds later
+    ops.fuse_residual_stream = False
+    try:
+        out8 = ops.linear(x[:8].contiguous(), w, torch.float32, add_to=res[:8].contiguous())
+    finally:
+        ops.fuse_residual_stream = True
+    assert isinstance(out8, torch.Tensor)
+
+
 # ----------------------------------------------------------------------------- tensor-core attention
 @pytest.mark.parametrize("hq,hkv,d", [(6, 2, 128), (16, 1, 64), (4, 4, 128), (32, 8, 128), (8, 4, 64)])
 def test_mma_attention_decode_groups_and_lengths(hq, hkv, d):
