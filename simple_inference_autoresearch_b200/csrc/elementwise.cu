@@ -214,6 +214,115 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
   }
 }
 
+// The same for many bfloat16 tokens, 16 bytes at a time: one block of 128 threads per token,
+// thread (head slot, piece) rotates 8 pairs of one head per pass; all loads of up to kRopePasses
+// passes are asked for before the first value is used.  D % 16 == 0.
+constexpr int kRopePasses = 4;
+
+__global__ void __launch_bounds__(128)
+rope_kv_write_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ inv_freq,
+                            __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+                            const int* __restrict__ block_table, const int* __restrict__ slot_ids,
+                            const int* __restrict__ q_start, const int* __restrict__ base_len, int B, int Hq,
+                            int Hkv, int D, int page_tokens, int max_pages, int n_pages, int write_kv,
+                            int* __restrict__ status) {
+  pdl_launch_dependents();
+  SIAR_TRACE(3, 0);
+  extern __shared__ float cs[];   // cos[half], sin[half]
+  const int half = D >> 1;
+  const int tid = threadIdx.x;
+  float freq = 0.f;
+  if (tid < half && inv_freq != nullptr) freq = inv_freq[tid];     // half <= 128
+  pdl_wait();
+  SIAR_TRACE(3, 2);
+  const int t = blockIdx.x;
+  const int b = find_sequence(q_start, B, t);
+  const int pos = base_len[b] + (t - q_start[b]);
+  __nv_bfloat16* row = qkv + (size_t)t * (Hq + 2 * Hkv) * D;
+  // thread -> (head slot, piece of 8 pairs)
+  const int pieces = half >> 3;
+  const int slots = 128 / pieces;
+  const int hs = tid / pieces, pc = tid % pieces;
+  const bool active = hs < slots;
+  const int n_heads_rot = Hq + Hkv;
+  uint4 lo[kRopePasses], hi[kRopePasses];
+#pragma unroll
+  for (int p = 0; p < kRopePasses; ++p) {
+    const int head = p * slots + hs;
+    if (active && head < n_heads_rot) {
+      lo[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + pc * 8);
+      hi[p] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + half + pc * 8);
+    }
+  }
+  if (tid < half) {
+    float sn = 0.f, c = 1.f;
+    if (inv_freq != nullptr) sincosf((float)pos * freq, &sn, &c);
+    cs[tid] = c;
+    cs[half + tid] = sn;
+  }
+  __nv_bfloat16* kdst = nullptr;
+  __nv_bfloat16* vdst = nullptr;
+  if (write_kv) {
+    const int slot = slot_ids[b];
+    const int page = block_table[(size_t)slot * max_pages + pos / page_tokens];
+    if (page < 0 || page >= n_pages) {
+      if (tid == 0) atomicOr(status, kStatusBadPage);
+    } else {
+      const size_t off = ((size_t)page * Hkv * page_tokens + (pos % page_tokens)) * D;   // kv head 0
+      kdst = k_pool + off;
+      vdst = v_pool + off;
+    }
+  }
+  __syncthreads();
+  const size_t head_stride = (size_t)page_tokens * D;   // between kv heads inside a page
+  const int n_rot = Hq + (kdst != nullptr ? Hkv : 0);
+  float cv[8], sv[8];
+  if (active) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { cv[e] = cs[pc * 8 + e]; sv[e] = cs[half + pc * 8 + e]; }
+  }
+  auto rotate_store = [&](int head, const uint4& a4, const uint4& c4) {
+    __nv_bfloat16* dst = head < Hq ? row + (size_t)head * D : kdst + (size_t)(head - Hq) * head_stride;
+    const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a4);
+    const __nv_bfloat162* cp = reinterpret_cast<const __nv_bfloat162*>(&c4);
+    uint4 o_lo, o_hi;
+    uint32_t* ol = reinterpret_cast<uint32_t*>(&o_lo);
+    uint32_t* oh = reinterpret_cast<uint32_t*>(&o_hi);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(ap[e]), c = __bfloat1622float2(cp[e]);
+      __nv_bfloat162 l2 = __floats2bfloat162_rn(a.x * cv[2 * e] - c.x * sv[2 * e], a.y * cv[2 * e + 1] - c.y * sv[2 * e + 1]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(c.x * cv[2 * e] + a.x * sv[2 * e], c.y * cv[2 * e + 1] + a.y * sv[2 * e + 1]);
+      ol[e] = *reinterpret_cast<uint32_t*>(&l2);
+      oh[e] = *reinterpret_cast<uint32_t*>(&h2);
+    }
+    *reinterpret_cast<uint4*>(dst + pc * 8) = o_lo;
+    *reinterpret_cast<uint4*>(dst + half + pc * 8) = o_hi;
+  };
+  if (active) {
+#pragma unroll
+    for (int p = 0; p < kRopePasses; ++p) {
+      const int head = p * slots + hs;
+      if (head < n_rot) rotate_store(head, lo[p], hi[p]);
+    }
+    // more heads than kRopePasses passes cover: the rest one pass at a time
+    for (int head = kRopePasses * slots + hs; head < n_rot; head += slots) {
+      const uint4 a4 = *reinterpret_cast<const uint4*>(row + (size_t)head * D + pc * 8);
+      const uint4 c4 = *reinterpret_cast<const uint4*>(row + (size_t)head * D + half + pc * 8);
+      rotate_store(head, a4, c4);
+    }
+  }
+  if (vdst != nullptr) {
+    const __nv_bfloat16* vrow = row + (size_t)(Hq + Hkv) * D;
+    const int per_head = D >> 3;
+    for (int idx = tid; idx < Hkv * per_head; idx += 128) {
+      const int head = idx / per_head, c = idx % per_head;
+      *reinterpret_cast<uint4*>(vdst + (size_t)head * head_stride + c * 8) =
+          *reinterpret_cast<const uint4*>(vrow + (size_t)head * D + c * 8);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ SwiGLU
 // interleaved == 0: rows are [gate (I) | up (I)]; interleaved == 1: rows are (gate_0, up_0, gate_1, ...).
 template <typename T>
@@ -340,6 +449,12 @@ extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq,
   const int tx = D / 2 > 64 ? 128 : D / 2 > 32 ? 64 : 32;   // one pass over the D/2 pairs of a head
   const dim3 threads(tx, ysplit == 1 ? 256 / tx : 1);        // many tokens: several heads at a time per block
   const size_t smem = sizeof(float) * D;
+  if (is_bf16 && N >= 256 && D % 16 == 0 && D <= 256 && (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) == 0) {
+    launch_kernel(rope_kv_write_bf16x8_kernel, dim3(N), dim3(128), smem, s, (__nv_bfloat16*)qkv, inv_freq,
+                  (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv,
+                  D, page_tokens, max_pages, n_pages, write_kv, status);
+    LAUNCH_END();
+  }
   if (is_bf16)
     launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(N, ysplit), dim3(threads), smem, s, (__nv_bfloat16*)qkv, inv_freq,
                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv,

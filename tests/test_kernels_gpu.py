@@ -253,6 +253,36 @@ def test_decode_and_prefill_kernels_agree():
     torch.testing.assert_close(dec, pre, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(32, 8, 128), (6, 2, 48), (40, 8, 256), (5, 5, 80), (16, 2, 64)])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_rotate_and_write_of_many_bfloat16_tokens(hq, hkv, d, write_kv):
+    """256 tokens and more take the 16-byte kernel: two prompts, one of them continuing a cache,
+    against the restatement (rotated q in place, k rotated into the pages, v copied)."""
+    lens_before, q_lens = [0, 70], [190, 130]
+    width = (hq + 2 * hkv) * d
+    inv_freq = plain_llama.rope_inv_freq(d, 10000.0, None)
+    res = {}
+    for dev, be in (("cpu", emu), (DEV, ops)):
+        c = make_cache(hkv, d, torch.bfloat16, dev)
+        decoy = c.alloc()
+        c.reserve([decoy], [100]); c.commit([decoy], [100])
+        slots = [c.alloc(), c.alloc()][::-1]
+        hist = rnd(70, width, dtype=torch.bfloat16, seed=3).to(dev)
+        c.reserve([slots[1]], [70])
+        be.rope_kv_write(hist, inv_freq.to(dev), c.entry(0), BatchMeta.build([StepEntry(slots[1], [0] * 70)], [0], dev), hq, hkv, d)
+        c.commit([slots[1]], [70])
+        c.reserve(slots, q_lens)
+        qkv = rnd(sum(q_lens), width, dtype=torch.bfloat16, seed=4).to(dev)
+        meta = BatchMeta.build([StepEntry(s, [0] * n) for s, n in zip(slots, q_lens)], lens_before, dev)
+        be.rope_kv_write(qkv, inv_freq.to(dev), c.entry(0), meta, hq, hkv, d, write_kv)
+        res[dev] = (qkv.float().cpu(), c.entry(0).k.float().cpu(), c.entry(0).v.float().cpu())
+    ops.check_status(DEV)
+    for got, want in zip(res[DEV], res["cpu"]):
+        torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
+    if not write_kv:      # the pages hold the 70 earlier tokens only
+        assert torch.equal(res[DEV][1], res["cpu"][1]) or (res[DEV][1] - res["cpu"][1]).abs().max() <= 2e-2
+
+
 def test_attention_refuses_sizes_it_cannot_take():
     with pytest.raises(ValueError, match="head_dim"):
         ops.check_attention_sizes(4, 2, 24)
