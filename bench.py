@@ -247,7 +247,8 @@ def main() -> int:
         engine.generate(prompts, greedy, max_new_tokens=1, ignore_eos=True)
         torch.cuda.synchronize()
         t1 = time.perf_counter()
-        outs = engine.generate(prompts, greedy, max_new_tokens=1 + args.steps, ignore_eos=True)
+        outs, gen_stats = engine.generate(prompts, greedy, max_new_tokens=1 + args.steps, ignore_eos=True,
+                                          return_stats=True)
         torch.cuda.synchronize()
         t2 = time.perf_counter()
         assert all(len(o) == 1 + args.steps for o in outs)
@@ -276,6 +277,8 @@ def main() -> int:
         },
         "e2e": {"value": round(generate_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
                 "d2h_bytes_per_step": 4 * args.batch + 4, "via": "Engine.generate (difference of two runs, median of 3 pairs)",
+                "step_ms_first16": gen_stats["tpot_ms_first16"], "step_ms_last16": gen_stats["tpot_ms_last16"],
+                "note": "the steps right after the prompts run at the clocks the prefill left (power cap)",
                 "step_call": round(head["e2e_tok_s"], 1)},
         "gpu_launches": head["launches"],
         "prefill": prefill,

@@ -67,8 +67,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   __shared__ float cs_s[D];                     // cos[D/2], sin[D/2] of the new token's position
   pdl_launch_dependents();
   SIAR_TRACE(20, 0);
-  pdl_wait();
-  SIAR_TRACE(20, 2);
+  // What the kernel in front (the qkv product) writes is the fused row only.  When this kernel
+  // itself writes the new token's k and v, everything else it reads (lengths, block table, pages
+  // of earlier tokens) was complete before this step began (the step's first kernel is a full
+  // barrier, see embed_gather_kernel), so the look-ups and the first tiles are asked for BEFORE
+  // the wait and are on their way, or there, when the product finishes.
+  const bool early = fuse_rope && write_kv;
+  if (!early) {
+    pdl_wait();
+    SIAR_TRACE(20, 2);
+  }
   constexpr int RS = D + kPad;                 // row stride in elements
   constexpr int CPR = D / 8;                   // 16-byte pieces per row
   constexpr int WK = kDecodeWarpKeys;          // keys per warp and step
@@ -91,23 +99,6 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int* table = block_table + (size_t)slot * max_pages;
-  static_assert(D / 2 <= 128, "one thread per rotation frequency");
-  const float freq = fuse_rope && inv_freq != nullptr && threadIdx.x < D / 2 ? __ldg(inv_freq + threadIdx.x) : 0.f;
-  // query fragments straight from global memory: rows g and g + 8 of the (padded) group
-  const size_t tok_row = (size_t)row_b * (Hq + 2 * Hkv) * D;
-  uint32_t qa[D / 16][4];
-  {
-    const __nv_bfloat16* qrow = qkv + tok_row + (size_t)kvh * G * D;
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      const int col = kk * 16 + q * 2;
-      qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
-      qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
-      qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
-      qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
-    }
-  }
-
   // The page of a tile is read from the block table one step before the tile is requested, so
   // that the (dependent) table read never sits in front of the loads it feeds.
   auto page_of = [&](int it) {
@@ -143,6 +134,27 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   }
   SIAR_STAMP(7);
   int page_ahead = pages[kDecodeStages - 1];      // page of tile it + kDecodeStages - 1 at step it
+  if (early) {
+    pdl_wait();
+    SIAR_TRACE(20, 2);
+  }
+  static_assert(D / 2 <= 128, "one thread per rotation frequency");
+  const float freq = fuse_rope && inv_freq != nullptr && threadIdx.x < D / 2 ? __ldg(inv_freq + threadIdx.x) : 0.f;
+  // query fragments straight from global memory: rows g and g + 8 of the (padded) group
+  const size_t tok_row = (size_t)row_b * (Hq + 2 * Hkv) * D;
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qrow = qkv + tok_row + (size_t)kvh * G * D;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int col = kk * 16 + q * 2;
+      qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
+      qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
+      qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
+      qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+  }
+
   const int pos = kv_len - 1;                      // position of the new token
   if (fuse_rope) {
     if (threadIdx.x < D / 2) {

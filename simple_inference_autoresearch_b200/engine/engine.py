@@ -189,6 +189,10 @@ class Engine:
             "total_tok_s": round((sum(len(p) for p in prompts) + new) / wall, 1) if wall > 0 else 0.0,
             "peak_vram_gb": round(torch.cuda.max_memory_allocated(self.device) / 1e9, 2) if self._cuda else 0.0,
             "finish_reasons": [r.finish_reason for r in reqs],
+            # median step time right after the prompts and at the end: after a long prefill at the
+            # power cap the clocks take some tens of milliseconds to come back
+            "tpot_ms_first16": round(1e3 * sorted(decode[:16])[len(decode[:16]) // 2], 3) if decode else 0.0,
+            "tpot_ms_last16": round(1e3 * sorted(decode[-16:])[len(decode[-16:]) // 2], 3) if decode else 0.0,
         }
         return outs, stats
 
