@@ -135,7 +135,7 @@ class DecoderModel:
         for layer in self.layers:
             units += list(layer.extension_units())
         if self.dtype != torch.bfloat16:   # the tensor-core units are bfloat16 only
-            units = [u for u in units if u not in ("gemm_tc", "attention_mma")]
+            units = [u for u in units if u not in ("gemm_tc", "attention_mma", "attention_tc")]
         return sorted(set(units))
 
     def weight_bytes(self) -> int:

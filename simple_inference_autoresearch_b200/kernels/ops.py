@@ -271,6 +271,8 @@ def tc_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_d
     group size that divides 128, pages of 64 tokens or a multiple)."""
     if dtype != torch.bfloat16 or not (use_tc_attention and use_mma_attention):
         return False
+    if head_dim != 128 or n_kv_heads <= 0 or n_heads % n_kv_heads:      # the unit is not even compiled for these
+        return False
     return bool(_fn("attention_tc", "siar_attn_tc_supported")(n_heads, n_kv_heads, head_dim, page_tokens))
 
 

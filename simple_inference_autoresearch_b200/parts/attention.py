@@ -55,7 +55,10 @@ class GroupedQueryAttention(Mixer):
         return KVNeed(self.n_kv_heads, self.head_dim)
 
     def extension_units(self):
-        return ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
+        units = ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
+        if self.head_dim == 128 and 128 % (self.n_heads // self.n_kv_heads) == 0:
+            units += ("attention_tc",)        # prompts of bfloat16 models with these sizes
+        return units
 
     takes_deferred_norm = True
 
