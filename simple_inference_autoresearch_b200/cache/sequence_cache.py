@@ -92,10 +92,8 @@ class StateEntry:
 class KVGroup:
     def __init__(self, need: KVNeed, n_entries: int, n_slots: int, n_pages: int, max_pages_per_seq: int,
                  page_tokens: int, dtype: torch.dtype, device):
-        if need.window is not None:
-            raise NotImplementedError(
-                "a kv group with a window is declared by the interface but no kernel here reads a "
-                "window of keys (the Llama decoder keeps all keys); refusing rather than attending wrongly")
+        if need.window is not None and need.window <= 0:
+            raise CacheError(f"a window of keys must be positive, got {need.window}")
         self.need = need
         self.n_entries = n_entries
         self.page_tokens = page_tokens
@@ -106,7 +104,8 @@ class KVGroup:
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         # -1 marks "no page"; the cache-write kernel flags a write through it.
         self.block_table = torch.full((n_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
-        self.slot_pages: Dict[int, List[int]] = {}
+        # per slot: the page of every page index so far; None once a windowed group gave it back
+        self.slot_pages: Dict[int, List[Optional[int]]] = {}
 
     def entry(self, i: int) -> KVEntry:
         return KVEntry(self.k[i], self.v[i], self.block_table, self.page_tokens)
@@ -132,9 +131,29 @@ class KVGroup:
             pages.append(p)
         return added
 
+    def release_before(self, slot: int, length: int) -> List[Tuple[int, int, int]]:
+        """A group with a window: after the sequence has reached ``length`` tokens, the next query
+        (position ``length``) sees keys from ``length - window + 1`` on, so pages that lie wholly in
+        front of that are given back.  Returns (slot, page index, -1) rows for the block table."""
+        if self.need.window is None:
+            return []
+        first_needed = max(0, length - self.need.window + 1)
+        pages = self.slot_pages[slot]
+        cells = []
+        for idx in range(min(first_needed // self.page_tokens, len(pages))):
+            if pages[idx] is not None:
+                self.pages.give(pages[idx])
+                pages[idx] = None
+                cells.append((slot, idx, -1))
+        return cells
+
+    def held_pages(self, slot: int) -> int:
+        return sum(p is not None for p in self.slot_pages[slot])
+
     def close_slot(self, slot: int) -> None:
         for p in self.slot_pages.pop(slot):
-            self.pages.give(p)
+            if p is not None:
+                self.pages.give(p)
 
     def bytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
@@ -259,17 +278,29 @@ class SequenceCache:
             cells = []
             for s, n in zip(slots, new_tokens):
                 cells += g.grow(s, self.lengths[s] + n)
-            if cells:
-                idx = torch.tensor([[c[0], c[1]] for c in cells], dtype=torch.int64)
-                val = torch.tensor([c[2] for c in cells], dtype=torch.int32)
-                if torch.device(self.device).type == "cuda":
-                    idx = idx.pin_memory().to(self.device, non_blocking=True)
-                    val = val.pin_memory().to(self.device, non_blocking=True)
-                g.block_table[idx[:, 0], idx[:, 1]] = val
+            self._upload_cells(g, cells)
+
+    def _upload_cells(self, g: "KVGroup", cells) -> None:
+        if not cells:
+            return
+        idx = torch.tensor([[c[0], c[1]] for c in cells], dtype=torch.int64)
+        val = torch.tensor([c[2] for c in cells], dtype=torch.int32)
+        if torch.device(self.device).type == "cuda":
+            idx = idx.pin_memory().to(self.device, non_blocking=True)
+            val = val.pin_memory().to(self.device, non_blocking=True)
+        g.block_table[idx[:, 0], idx[:, 1]] = val
 
     def commit(self, slots: Sequence[int], new_tokens: Sequence[int]) -> None:
+        """The step ran: lengths advance, and groups that keep a window of keys give back the
+        pages that no later query can see."""
         for s, n in zip(slots, new_tokens):
             self.lengths[s] += n
+        for g in self.groups:
+            if isinstance(g, KVGroup) and g.need.window is not None:
+                cells = []
+                for s in slots:
+                    cells += g.release_before(s, self.lengths[s])
+                self._upload_cells(g, cells)
 
     # ---- accounting
     def held_tokens(self) -> int:

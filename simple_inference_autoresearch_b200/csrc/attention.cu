@@ -50,7 +50,9 @@ __global__ void __launch_bounds__(kPrefillWarps * 32)
 attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                     const int* __restrict__ block_table, const int* __restrict__ slot_ids,
                     const int* __restrict__ q_start, const int* __restrict__ base_len, T* __restrict__ out,
-                    int Hq, int Hkv, int D, int page_tokens, int max_pages, float scale) {
+                    int Hq, int Hkv, int D, int page_tokens, int max_pages, float scale, int window) {
+  // window > 0: a query at position p sees keys p - window + 1 .. p only (0 = all keys up to p);
+  // keys in front of a block's first window are never touched (their pages may be gone).
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -83,25 +85,27 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pool, con
 
   constexpr int RPW = kPrefillRows / kPrefillWarps;
   float m[RPW], l[RPW], acc[RPW][NDIM];
-  int kv_end[RPW];
+  int kv_end[RPW], kv_begin[RPW];
 #pragma unroll
   for (int i = 0; i < RPW; ++i) {
     m[i] = -INFINITY;
     l[i] = 0.f;
     const int r = warp * RPW + i;
     kv_end[i] = (r < rows_here) ? base + (row0 + r) / G + 1 : 0;
+    kv_begin[i] = window > 0 ? max(0, kv_end[i] - window) : 0;
 #pragma unroll
     for (int n = 0; n < NDIM; ++n) acc[i][n] = 0.f;
   }
   const int block_kv_end = base + (row0 + rows_here - 1) / G + 1;
+  const int block_kv_begin = window > 0 ? max(0, base + row0 / G + 1 - window) : 0;
 
-  for (int j0 = 0; j0 < block_kv_end; j0 += kTile) {
+  for (int j0 = (block_kv_begin / kTile) * kTile; j0 < block_kv_end; j0 += kTile) {
     __syncthreads();
     for (int idx = threadIdx.x; idx < kTile * D; idx += blockDim.x) {
       const int j = idx / D, d = idx % D;
       const int key = j0 + j;
       float kval = 0.f, vval = 0.f;
-      if (key < block_kv_end) {
+      if (key < block_kv_end && key >= block_kv_begin) {
         kval = to_f32(key_row(k_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d]);
         vval = to_f32(key_row(v_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d]);
       }
@@ -111,12 +115,12 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pool, con
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
-      if (j0 >= kv_end[i]) continue;  // whole tile masked for this row (warp-uniform)
+      if (j0 >= kv_end[i] || j0 + kTile <= kv_begin[i]) continue;  // whole tile masked for this row (warp-uniform)
       const float* q = q_s + (warp * RPW + i) * D;
       const float* kr = k_s + lane * (D + 1);
       float s = 0.f;
       for (int d = 0; d < D; ++d) s = fmaf(q[d], kr[d], s);
-      const bool valid = (j0 + lane) < kv_end[i];
+      const bool valid = (j0 + lane) < kv_end[i] && (j0 + lane) >= kv_begin[i];
       s = valid ? s * scale : -INFINITY;
       const float m_new = fmaxf(m[i], warp_max(s));
       const float alpha = expf(m[i] - m_new);
@@ -162,7 +166,7 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
                            const int* __restrict__ block_table, const int* __restrict__ slot_ids,
                            const int* __restrict__ q_start, const int* __restrict__ base_len,
                            float* __restrict__ part_ml, float* __restrict__ part_acc, int Hq, int Hkv, int D,
-                           int page_tokens, int max_pages, int max_chunks, float scale) {
+                           int page_tokens, int max_pages, int max_chunks, float scale, int window) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -174,6 +178,19 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
   const int c_end = min(kv_len, c0 + kDecodeChunk);
   const int slot = slot_ids[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_begin = window > 0 ? max(0, kv_len - window) : 0;   // first key the new token sees
+  if (c_end <= kv_begin) {
+    // a chunk in front of the window: an empty partial, so that the join needs no special case
+    for (int g = warp; g < G; g += kDecodeWarps) {
+      const size_t pidx = ((size_t)b * Hq + kvh * G + g) * max_chunks + c;
+      if (lane == 0) {
+        part_ml[pidx * 2] = -INFINITY;
+        part_ml[pidx * 2 + 1] = 0.f;
+      }
+      for (int d = lane; d < D; d += 32) part_acc[pidx * D + d] = 0.f;
+    }
+    return;
+  }
   constexpr int KPAD = (sizeof(T) == 2) ? 2 : 1;
   const int ks = D + KPAD;
 
@@ -194,13 +211,14 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
   }
   for (int idx = threadIdx.x; idx < kDecodeWarps * G * D; idx += blockDim.x) st_acc[idx] = 0.f;
 
-  for (int r0 = c0; r0 < c_end; r0 += kDecodeRound) {
+  const int first_round = kv_begin > c0 ? c0 + ((kv_begin - c0) / kDecodeRound) * kDecodeRound : c0;
+  for (int r0 = first_round; r0 < c_end; r0 += kDecodeRound) {
     __syncthreads();
     for (int idx = threadIdx.x; idx < kDecodeRound * D; idx += blockDim.x) {
       const int j = idx / D, d = idx % D;
       const int key = r0 + j;
       T kval = from_f32<T>(0.f), vval = from_f32<T>(0.f);
-      if (key < c_end) {
+      if (key < c_end && key >= kv_begin) {
         kval = key_row(k_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d];
         vval = key_row(v_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d];
       }
@@ -209,8 +227,8 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
     }
     __syncthreads();
     const int w0 = r0 + warp * kTile;
-    if (w0 < c_end) {
-      const bool valid = (w0 + lane) < c_end;
+    if (w0 < c_end && w0 + kTile > kv_begin) {
+      const bool valid = (w0 + lane) < c_end && (w0 + lane) >= kv_begin;
       const T* kr = k_s + (warp * kTile + lane) * ks;
       for (int g = 0; g < G; ++g) {
         const float* q = q_s + g * D;
@@ -305,7 +323,7 @@ static size_t decode_smem_bytes(int G, int D) {
 template <typename T, int NDIM>
 static int launch_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                           const int* slot_ids, const int* q_start, const int* base_len, void* out, int B, int Hq,
-                          int Hkv, int D, int page_tokens, int max_pages, int max_q_len, float scale,
+                          int Hkv, int D, int page_tokens, int max_pages, int max_q_len, float scale, int window,
                           cudaStream_t s) {
   const int G = Hq / Hkv;
   const size_t smem = sizeof(float) * ((size_t)kPrefillRows * D + kTile * (D + 1) + kTile * D);
@@ -317,7 +335,7 @@ static int launch_prefill(const void* qkv, const void* k_pool, const void* v_poo
   dim3 grid((max_q_len * G + kPrefillRows - 1) / kPrefillRows, Hkv, B);
   launch_kernel(kern, grid, kPrefillWarps * 32, smem, s, (const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
                                               slot_ids, q_start, base_len, (T*)out, Hq, Hkv, D, page_tokens,
-                                              max_pages, scale);
+                                              max_pages, scale, window);
   return (int)cudaGetLastError();
 }
 
@@ -335,14 +353,14 @@ extern "C" int siar_attn_max_head_dim() { return 256; }
 extern "C" int siar_attn_prefill(int is_bf16, const void* qkv, const void* k_pool, const void* v_pool,
                                  const int* block_table, const int* slot_ids, const int* q_start,
                                  const int* base_len, void* out, int B, int Hq, int Hkv, int D, int page_tokens,
-                                 int max_pages, int max_q_len, float scale, void* stream) {
+                                 int max_pages, int max_q_len, int window, float scale, void* stream) {
   if (B == 0 || max_q_len == 0) return 0;
-  if (D % 16 != 0 || D > 256 || D <= 0 || Hq % Hkv != 0 || Hkv > 65535 || B > 65535)
+  if (D % 16 != 0 || D > 256 || D <= 0 || Hq % Hkv != 0 || Hkv > 65535 || B > 65535 || window < 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
 #define SIAR_PREFILL(T, ND)                                                                                   \
   return launch_prefill<T, ND>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv, \
-                               D, page_tokens, max_pages, max_q_len, scale, s)
+                               D, page_tokens, max_pages, max_q_len, scale, window, s)
   const int nd = (D + 31) / 32;
   if (is_bf16) {
     if (nd <= 1) SIAR_PREFILL(__nv_bfloat16, 1);
@@ -368,7 +386,7 @@ template <typename T>
 static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                          const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
                          int B, int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_kv_len,
-                         float scale, cudaStream_t s) {
+                         float scale, int window, cudaStream_t s) {
   const int G = Hq / Hkv;
   const int max_chunks = (max_kv_len + kDecodeChunk - 1) / kDecodeChunk;
   float* part_ml = scratch;
@@ -383,7 +401,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   dim3 grid(max_chunks, Hkv, B);
   launch_kernel(kern, grid, kDecodeWarps * 32, smem, s, (const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
                                              slot_ids, q_start, base_len, part_ml, part_acc, Hq, Hkv, D,
-                                             page_tokens, max_pages, max_chunks, scale);
+                                             page_tokens, max_pages, max_chunks, scale, window);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   dim3 grid2(Hq, B);
@@ -398,14 +416,15 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
 extern "C" int siar_attn_decode(int is_bf16, const void* qkv, const void* k_pool, const void* v_pool,
                                 const int* block_table, const int* slot_ids, const int* q_start,
                                 const int* base_len, void* out, float* scratch, int B, int Hq, int Hkv, int D,
-                                int page_tokens, int max_pages, int max_kv_len, float scale, void* stream) {
+                                int page_tokens, int max_pages, int max_kv_len, int window, float scale,
+                                void* stream) {
   if (B == 0) return 0;
-  if (D % 16 != 0 || D > 256 || D <= 0 || Hq % Hkv != 0 || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
+  if (D % 16 != 0 || D > 256 || D <= 0 || Hq % Hkv != 0 || Hkv > 65535 || B > 65535 || max_kv_len <= 0 || window < 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (is_bf16)
     return launch_decode<__nv_bfloat16>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out,
-                                        scratch, B, Hq, Hkv, D, page_tokens, max_pages, max_kv_len, scale, s);
+                                        scratch, B, Hq, Hkv, D, page_tokens, max_pages, max_kv_len, scale, window, s);
   return launch_decode<float>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, B, Hq,
-                              Hkv, D, page_tokens, max_pages, max_kv_len, scale, s);
+                              Hkv, D, page_tokens, max_pages, max_kv_len, scale, window, s);
 }

@@ -40,9 +40,9 @@ _signatures = {
     },
     "attention": {
         "siar_attn_prefill": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
         "siar_attn_decode": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                              c_void_p],
         "siar_attn_decode_chunk": [],
         "siar_attn_max_head_dim": [],
@@ -376,14 +376,14 @@ fuse_decode_rope = True
 
 
 def rope_and_attention(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, meta, n_heads: int, n_kv_heads: int,
-                       head_dim: int, scale: float, write_kv: bool = True) -> torch.Tensor:
+                       head_dim: int, scale: float, write_kv: bool = True, window: Optional[int] = None) -> torch.Tensor:
     """Rotates q and k by the tokens' positions, writes k and v to the cache entry and attends:
     what a rotary attention mixer does between its two products.  For steps of one token per
     sequence on the tensor-core path this is ONE kernel (q is rotated in registers, the new k and
-    v go to the cache and are used from shared memory); otherwise two."""
-    if not decode_fuses_rope(meta, qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
+    v go to the cache and are used from shared memory); otherwise two.  ``window``: see ``attention``."""
+    if window is not None or not decode_fuses_rope(meta, qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
         rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
-        return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale)
+        return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=window)
     _need_cuda(qkv, kv.k, inv_freq)
     check_attention_sizes(n_heads, n_kv_heads, head_dim)
     assert qkv.is_contiguous() and qkv.shape == (meta.n_seqs, (n_heads + 2 * n_kv_heads) * head_dim)
@@ -403,17 +403,22 @@ def rope_and_attention(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, 
     return out
 
 
-def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
+def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+              window: Optional[int] = None) -> torch.Tensor:
     """Causal attention of the new tokens' (already rotated) queries over the
     cache entry ``kv``; returns [N, n_heads * head_dim] in qkv's dtype.  bfloat16
-    with head_dim 64 or 128 runs on the tensor cores, everything else on the CUDA cores."""
+    with head_dim 64 or 128 runs on the tensor cores, everything else on the CUDA cores.
+    ``window`` = w: a query at position p sees keys p - w + 1 .. p only (CUDA-core kernels)."""
+    if window is not None and window <= 0:
+        raise ValueError(f"an attention window must be positive, got {window}")
     _need_cuda(qkv, kv.k)
     check_attention_sizes(n_heads, n_kv_heads, head_dim)
     n = qkv.shape[0]
     out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     common = (_ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len))
     sizes = (meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1])
-    mma = mma_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens)
+    mma = window is None and mma_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens)
+    win = int(window or 0)
     if meta.is_decode:
         if mma:
             sms = _sm_count(qkv.device)
@@ -429,8 +434,8 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
             scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len, chunk),
                                   dtype=torch.float32, device=qkv.device)
             _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
-                    _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, float(scale), _stream(), kernels=2)
-    elif tc_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
+                    _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, win, float(scale), _stream(), kernels=2)
+    elif window is None and tc_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
         _launch("attention_tc", "siar_attn_tc_prefill", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out), n,
                 *sizes, kv.k.shape[0], meta.max_q_len, float(scale), _ptr(status_word(qkv.device)), _stream())
     elif mma:
@@ -438,7 +443,7 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
                 *sizes, meta.max_q_len, float(scale), _stream())
     else:
         _launch("attention", "siar_attn_prefill", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
-                _ptr(out), *sizes, meta.max_q_len, float(scale), _stream())
+                _ptr(out), *sizes, meta.max_q_len, win, float(scale), _stream())
     return out
 
 

@@ -8,12 +8,16 @@ cache (k is cached rotated), causal attention of each new token over keys
 ``[0, position]`` of its own sequence with scale ``1/sqrt(D)`` and query head
 ``hq`` reading kv head ``hq // (Hq/Hkv)``, and the output product with ``Wo``.
 There are no biases (loader.py:74-93 reads none).
+
+``window`` (not a Llama option; the reference has none, ops/attention.py:337-342) limits a
+token to the last ``window`` keys, itself included; layers with a window get a cache group of
+their own that gives pages back as they fall out of every later query's sight.
 """
 
 from __future__ import annotations
 
 import math
-from typing import List, Mapping
+from typing import List, Mapping, Optional
 
 import torch
 
@@ -24,8 +28,11 @@ from .base import KVNeed, MIXERS, Mixer, TensorSpec
 @MIXERS.register("gqa_attention")
 class GroupedQueryAttention(Mixer):
     def __init__(self, prefix: str, position, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, window: Optional[int] = None):
         super().__init__(prefix)
+        if window is not None and int(window) <= 0:
+            raise ValueError(f"an attention window must be positive, got {window}")
+        self.window = None if window is None else int(window)
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = (
             int(hidden_size), int(n_heads), int(n_kv_heads), int(head_dim))
         ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim)
@@ -52,7 +59,7 @@ class GroupedQueryAttention(Mixer):
         self.w_o = tensors[p + "o_proj.weight"].contiguous()
 
     def cache_need(self):
-        return KVNeed(self.n_kv_heads, self.head_dim)
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
 
     def extension_units(self):
         units = ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
@@ -67,5 +74,5 @@ class GroupedQueryAttention(Mixer):
         rotary = self.position.rotary() if self.position is not None else None
         attn = ops.rope_and_attention(qkv, rotary.inv_freq if rotary is not None else None, cache_entry, ctx.meta,
                                       self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
-                                      write_kv=writes_cache)
+                                      write_kv=writes_cache, window=self.window)
         return ops.linear(attn, self.w_o, torch.float32, add_to=ctx.residual)

@@ -89,7 +89,7 @@ def _gather_kv(kv, slot, length):
     return k.to(torch.float32), v.to(torch.float32)
 
 
-def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale):
+def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=None):
     n = qkv.shape[0]
     out = torch.zeros(n, n_heads * head_dim, dtype=torch.float32)
     q_all = qkv.view(n, n_heads + 2 * n_kv_heads, head_dim)[:, :n_heads].to(torch.float32)
@@ -101,16 +101,17 @@ def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale):
         for i in range(ql):
             t = qs[b] + i
             visible = base[b] + i + 1
+            first = 0 if window is None else max(0, visible - window)
             for hq in range(n_heads):
-                s = (k[hq // g, :visible] @ q_all[t, hq]) * scale
+                s = (k[hq // g, first:visible] @ q_all[t, hq]) * scale
                 p = torch.softmax(s, dim=0)
-                out[t, hq * head_dim:(hq + 1) * head_dim] = p @ v[hq // g, :visible]
+                out[t, hq * head_dim:(hq + 1) * head_dim] = p @ v[hq // g, first:visible]
     return out.to(qkv.dtype)
 
 
-def rope_and_attention(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, scale, write_kv=True):
+def rope_and_attention(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, scale, write_kv=True, window=None):
     rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
-    return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale)
+    return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=window)
 
 
 def swiglu(gate_up, interleaved=False):

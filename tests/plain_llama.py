@@ -87,18 +87,22 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return x * torch.rsqrt(var + eps) * w.to(torch.float32)
 
 
-def attention_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+def attention_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None) -> torch.Tensor:
     """q: [T, Hq, D], k, v: [T, Hkv, D] -> [T, Hq*D].
     Query head hq reads kv head hq // G (kernels/attention_kernel.py:169); scores
     (q.k) * 1/sqrt(D), the scale after the dot (kernels/attention_kernel.py:204,275-276);
     key j visible to row i iff j <= i (kernels/attention_kernel.py:184,206-209 with
-    Tq == Tk); softmax over the visible keys (kernels/attention_kernel.py:212-226)."""
+    Tq == Tk); softmax over the visible keys (kernels/attention_kernel.py:212-226).
+    ``window`` is not the reference's (it has no sliding window, ops/attention.py:337-342): the
+    test of a windowed cache group uses it; row i then sees keys i - window + 1 .. i."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
     scale = 1.0 / math.sqrt(D)
     out = torch.empty(T, Hq, D, dtype=torch.float32)
     mask = torch.ones(T, T, dtype=torch.bool).tril()
+    if window is not None:
+        mask &= torch.ones(T, T, dtype=torch.bool).triu(-(window - 1))
     for hq in range(Hq):
         hkv = hq // G
         s = (q[:, hq, :] @ k[:, hkv, :].T) * scale
@@ -109,7 +113,7 @@ def attention_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
 
 
 def attention_block(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, c: dict,
-                    inv_freq: torch.Tensor, kv_override=None, return_kv: bool = False):
+                    inv_freq: torch.Tensor, kv_override=None, return_kv: bool = False, window: Optional[int] = None):
     """ops/attention.py:139-178 (q, k, v projections, head index the slow axis),
     :291-292 (rotate q and k), :315-332 (attention), :348 (output projection)."""
     T = h.shape[0]
@@ -121,7 +125,7 @@ def attention_block(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, c:
     k = rope_apply(k, cos, sin)
     if kv_override is not None:       # a run that reads the cache another run wrote
         k, v = kv_override
-    a = attention_causal(q, k, v)
+    a = attention_causal(q, k, v, window)
     out = a @ w[prefix + "o_proj.weight"].T
     return (out, (k, v)) if return_kv else out
 
@@ -136,11 +140,11 @@ def swiglu_mlp(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str) -> torc
 
 
 def block(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, c: dict, inv_freq: torch.Tensor,
-          kv_override=None, return_kv: bool = False):
+          kv_override=None, return_kv: bool = False, window: Optional[int] = None):
     """model/block.py:8-9: x += Attn(norm(x)); x += MLP(norm(x))."""
     p = f"model.layers.{i}."
     h = rmsnorm(x, w[p + "input_layernorm.weight"], c["eps"])
-    a = attention_block(h, w, p + "self_attn.", c, inv_freq, kv_override, return_kv)
+    a = attention_block(h, w, p + "self_attn.", c, inv_freq, kv_override, return_kv, window)
     kv = None
     if return_kv:
         a, kv = a
@@ -152,10 +156,12 @@ def block(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, c: dict, inv_freq
 
 # ----------------------------------------------------------------------------- whole model
 def forward(weights: Dict[str, torch.Tensor], raw_config: dict, tokens: Sequence[int],
-            schedule: Optional[List[tuple]] = None) -> torch.Tensor:
+            schedule: Optional[List[tuple]] = None, windows: Optional[dict] = None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence (model/llama.py:170-199,
     without its last-position slice).  ``schedule``: optional run order as
-    (layer, cache_entry, writes_cache) tuples; default layer 0..L-1."""
+    (layer, cache_entry, writes_cache) tuples; default layer 0..L-1.  ``windows``: layer -> key
+    window, for tests of windowed layers only (see ``attention_causal``)."""
+    windows = windows or {}
     c = parse_config(raw_config)
     w = {k: v.to(torch.float32) for k, v in weights.items()}
     inv_freq = rope_inv_freq(c["D"], c["theta"], c["scaling"])
@@ -163,7 +169,7 @@ def forward(weights: Dict[str, torch.Tensor], raw_config: dict, tokens: Sequence
     x = w["model.embed_tokens.weight"][ids]                      # ops/embedding.py:62-65
     if schedule is None:
         for i in range(c["L"]):
-            x = block(x, w, i, c, inv_freq)
+            x = block(x, w, i, c, inv_freq, window=windows.get(i))
     else:
         stored = {}
         for layer, entry, writes in schedule:

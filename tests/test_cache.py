@@ -122,6 +122,28 @@ def test_groups_by_need_and_state_is_zeroed_on_alloc():
     assert s2 == s and torch.all(c.entry(1).state[s2] == 0) and torch.all(c.entry(5).state[s2] == 0)
 
 
-def test_a_window_group_is_refused_not_misserved():
-    with pytest.raises(NotImplementedError, match="window"):
-        make([KVNeed(2, 16, window=128)])
+def test_a_window_group_keeps_its_own_pages_and_gives_back_what_no_query_can_see():
+    """Two groups from two needs (all keys / the last 100): same slots, storage of their own.  The
+    windowed one frees a page as soon as the next query's window starts behind it, marks the cell
+    -1, never frees twice, and ends with every page free."""
+    c = make([KVNeed(2, 16), KVNeed(2, 16, window=100), KVNeed(2, 16, window=100)], max_tokens=1280, max_seq_len=640)
+    assert len(c.groups) == 2 and c.groups[1].n_entries == 2
+    full, win = c.groups
+    a, b = c.alloc(), c.alloc()
+    c.reserve([a, b], [300, 70]); c.commit([a, b], [300, 70])
+    # a: next query at 300 sees keys 201..300 -> pages 0..2 (keys 0..191) are gone, 3 and 4 stay
+    assert [p is None for p in win.slot_pages[a]] == [True, True, True, False, False]
+    assert [p is None for p in win.slot_pages[b]] == [False, False]
+    assert win.block_table[a, :5].tolist()[:3] == [-1, -1, -1] and win.block_table[a, 3] >= 0
+    assert full.held_pages(a) == 5 and win.held_pages(a) == 2
+    for _ in range(200):                      # one token at a time: at most ceil(100/64) + 1 pages stay
+        c.reserve([a, b], [1, 1]); c.commit([a, b], [1, 1])
+        assert win.held_pages(a) <= 3 and win.held_pages(b) <= 3
+    assert c.length(a) == 500 and full.held_pages(a) == 8
+    free_before = len(win.pages)
+    c.free(a)
+    assert len(win.pages) > free_before
+    c.free(b)
+    assert len(win.pages) == win.pages.n and len(full.pages) == full.pages.n
+    with pytest.raises(CacheError, match="positive"):
+        make([KVNeed(2, 16, window=0)])

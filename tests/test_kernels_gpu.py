@@ -136,15 +136,17 @@ def test_linear_with_swiglu_epilogue(dtype, m, i, k):
 
 
 # ----------------------------------------------------------------------------- attention over the cache
-def make_cache(n_kv, d, dtype, device, max_tokens=8192, max_slots=12, max_seq_len=2048):
-    return SequenceCache([KVNeed(n_kv, d)], max_tokens, max_slots, max_seq_len, dtype, device)
+def make_cache(n_kv, d, dtype, device, max_tokens=8192, max_slots=12, max_seq_len=2048, window=None):
+    return SequenceCache([KVNeed(n_kv, d, window)], max_tokens, max_slots, max_seq_len, dtype, device)
 
 
-def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None, qk_scale=1.0):
+def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None, qk_scale=1.0,
+                       window=None):
     """Fills two caches (GPU kernel / CPU restatement) with the same history through
     rope_kv_write, then compares rope + attention of a last step."""
     torch.manual_seed(seed)
-    caches = {dev: make_cache(hkv, d, dtype, dev) for dev in ("cpu", DEV)}
+    caches = {dev: make_cache(hkv, d, dtype, dev, window=window) for dev in ("cpu", DEV)}
+    kw = {} if window is None else {"window": window}
     backends = {"cpu": emu, DEV: ops}
     inv_freq = plain_llama.rope_inv_freq(d, theta, None)
     b = len(q_lens)
@@ -188,7 +190,7 @@ def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=100
         meta = BatchMeta.build(ent, list(lens_before), dev)
         qkv = torch.cat(new).to(dev)
         be.rope_kv_write(qkv, None if inv_freq is None else inv_freq.to(dev), c.entry(0), meta, hq, hkv, d, True)
-        out = be.attention(qkv, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d))
+        out = be.attention(qkv, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d), **kw)
         outs[dev] = (out.cpu().float(), qkv.cpu().float(), c.entry(0).k.cpu().float(), c.entry(0).v.cpu().float())
     t = tol(dtype)
     torch.testing.assert_close(outs[DEV][1], outs["cpu"][1], **t)   # rotated q (and untouched k, v columns)
@@ -281,6 +283,23 @@ def test_rotate_and_write_of_many_bfloat16_tokens(hq, hkv, d, write_kv):
         torch.testing.assert_close(got, want, rtol=2e-2, atol=2e-2)
     if not write_kv:      # the pages hold the 70 earlier tokens only
         assert torch.equal(res[DEV][1], res["cpu"][1]) or (res[DEV][1] - res["cpu"][1]).abs().max() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [1, 33, 100, 700])
+def test_attention_over_a_window_of_keys(dtype, window):
+    """Keys in front of the window are not seen, and their pages have been given back (the
+    block table says -1 there): prompts that continue a cache, and single tokens."""
+    hq, hkv, d = 6, 2, 48
+    run_attention_case(dtype, hq, hkv, d, lens_before=[0, 300, 63], q_lens=[200, 150, 66], window=window)
+    run_attention_case(dtype, hq, hkv, d, lens_before=[0, 31, 127, 128, 129, 1000], q_lens=[1] * 6, window=window)
+    # a far key that would dominate is out of sight (or, with the widest window, still in)
+    outs = run_attention_case(dtype, 8, 2, 128, lens_before=[700], q_lens=[1], boost=(0, 200, 8.0), window=window)
+    v_row = rnd(700, 12 * 128, dtype=dtype, seed=10)[200, 10 * 128:11 * 128].float()
+    if window < 500:
+        assert (outs[DEV][0][0, :128] - v_row).abs().max() > 0.1
+    else:                 # position 700 sees keys 1..700: the far key is in sight and wins
+        torch.testing.assert_close(outs[DEV][0][0, :128], v_row, rtol=5e-2, atol=5e-2)
 
 
 def test_attention_refuses_sizes_it_cannot_take():

@@ -152,6 +152,42 @@ def test_schedule_may_repeat_a_layer_and_share_a_cache(device, tmp_path):
             DecoderModel(ModelSpec(**{**base.__dict__, "schedule": bad}), torch.float32, device)
 
 
+def test_layers_with_a_window_get_a_cache_group_of_their_own(device, tmp_path):
+    """Layer 0 keeps all keys, layers 1 and 2 the last 37 (no multiple of a page, shorter than the
+    prompt): two storage groups; whole prompt, then one token at a time far past the window,
+    against the plain implementation with the same masks; the windowed group holds a bounded
+    number of pages meanwhile and every page is free at the end."""
+    folder = tiny_configs.make_folder(tmp_path, "B", seed=5)        # three layers
+    raw, w = tiny_configs.read_folder(folder)
+    cfg = LlamaConfig.from_dict(raw)
+    base = llama_model_spec(cfg)
+    window = 37
+    layers = list(base.layers)
+    for i in (1, 2):
+        p = dict(layers[i].params)
+        p["mixer"] = PartSpec("gqa_attention", {**p["mixer"].params, "window": window})
+        layers[i] = PartSpec(layers[i].kind, p)
+    model = DecoderModel(ModelSpec(**{**base.__dict__, "layers": tuple(layers)}), torch.float32, device)
+    assert model.cache_needs[0].window is None and model.cache_needs[1].window == window
+    model.load({k: v.float().to(device) for k, v in w.items()})
+    eng = siar.Engine(model, max_batch=2, max_seq_len=256, use_cuda_graph=False)
+    full, win = eng.cache.groups
+    assert full.need.window is None and win.need.window == window and win.n_entries == 2
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, raw["vocab_size"], (150,), generator=g).tolist()
+    other = torch.randint(0, raw["vocab_size"], (20,), generator=g).tolist()
+    a, b = eng.open(), eng.open()
+    outs = [eng.step([StepEntry(a, toks[:90], range(90)), StepEntry(b, other, [])])[:90]]
+    for t in toks[90:]:
+        outs.append(eng.step([StepEntry(a, [t], [0])]))
+        assert win.held_pages(a) <= 2 and full.held_pages(a) == -(-eng.cache.length(a) // 64)
+    ref = plain_llama.forward(w, raw, toks, windows={1: window, 2: window})
+    torch.testing.assert_close(torch.cat(outs).cpu(), ref, rtol=2e-5, atol=2e-5)
+    assert (ref - plain_llama.forward(w, raw, toks)).abs().max() > 1e-3      # the window really matters
+    eng.close(a); eng.close(b)
+    assert len(win.pages) == win.pages.n and len(full.pages) == full.pages.n
+
+
 # ----------------------------------------------------------------------------- a toy mixer with state of its own
 class RunningMeanMixer(Mixer):
     """y_t = W * mean(x_0 .. x_t): per-sequence state = (sum [H], count [1]).
