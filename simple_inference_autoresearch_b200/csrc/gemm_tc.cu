@@ -80,8 +80,11 @@ __device__ __forceinline__ unsigned long long gtime() {
 #endif
 
 // ------------------------------------------------------------------ kernel
+// At most 112 registers per thread (three blocks' worth per SM): a block of this kernel then fits
+// on an SM beside two blocks of the decode attention kernel, so it starts, sets up and asks for
+// its first weight tiles while the attention in front of it is still running.
 template <int BN, int STAGES, typename TOut>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 3)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY, const GemmParams prm) {
   constexpr uint32_t kXBytes = kBM * kBK * 2;
   constexpr uint32_t kYBytes = BN * kBK * 2;
@@ -134,8 +137,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   TOut* C = (TOut*)prm.C;
   bool acc_ok = false;      // epilogue threads: the accumulator in tensor memory is complete
   float old_c[16];          // accumulate: the values of C this thread adds to
-#pragma unroll
-  for (int j = 0; j < 16; ++j) old_c[j] = 0.f;
 
   {
   if (dead) {
@@ -215,13 +216,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     if constexpr (BN == 16 && sizeof(TOut) == 4) {
       // accumulate: this thread's outputs (tile row threadIdx.x - 64, its rank's columns) are read
       // now, long before the sums arrive
-      if (prm.accumulate && !make_y) {
+      if (!make_y) {        // (never together with a made activation operand: the launcher refuses that)
         const int pp = p0 + (int)threadIdx.x - 64;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int jq = splits > 1 ? j * splits + (int)blockIdx.z : j;
           const int q = q0 + jq;
-          old_c[j] = (jq < BN && q < prm.Q && pp < prm.P)
+          old_c[j] = (prm.accumulate && jq < BN && q < prm.Q && pp < prm.P)
                          ? reinterpret_cast<const float*>(C)[(long long)q * prm.ldc + pp] : 0.f;
         }
       }
@@ -235,7 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const bool live = qrow < prm.Q;
         const float* src = prm.y_resid + (size_t)(live ? qrow : 0) * prm.y_ld + piece * 8;
         const __nv_bfloat16* wsrc = prm.norm_w + piece * 8;
-        constexpr int PF = 6;
+        constexpr int PF = 4;
         float4 a0[PF], a1[PF];
         uint4 wv[PF];
         auto fetch = [&](int i, float4& x0, float4& x1, uint4& w) {
