@@ -28,6 +28,7 @@ constexpr int kMmaDecodeChunk = 128;   // granularity of a decode block's key ra
 constexpr int kDecodeWarpKeys = 16;    // keys per warp and pipeline step in the decode kernel
 constexpr int kDecodeStages = 3;       // pipeline depth per warp
 constexpr int kDecodeBlocksPerSM = 2;  // what shared memory allows with that depth
+constexpr int kJoinPad = 8;            // floats of padding per row of the warps' join buffer (decode)
 constexpr int kMmaPrefillRows = 64;
 constexpr int kMmaKeyTile = 64;
 
@@ -302,14 +303,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   // join the four warps: reuse the tile memory as float buffers
   SIAR_STAMP(3);
   __syncthreads();
-  float* mo = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
-  float* mm = mo + 4 * 16 * D;                                // [4][16]
+  constexpr int MS = D + kJoinPad;                            // padded row: the eight rows a warp stores at once
+                                                              // fall into different banks
+  float* mo = reinterpret_cast<float*>(smem_raw);            // [4][16][MS]
+  float* mm = mo + 4 * 16 * MS;                               // [4][16]
   float* ml = mm + 4 * 16;                                    // [4][16]
 #pragma unroll
   for (int j = 0; j < D / 8; ++j) {
     const int d = 8 * j + 2 * q;
-    if (g < G) { mo[(warp * 16 + g) * D + d] = o[j][0]; mo[(warp * 16 + g) * D + d + 1] = o[j][1]; }
-    if (g + 8 < G) { mo[(warp * 16 + g + 8) * D + d] = o[j][2]; mo[(warp * 16 + g + 8) * D + d + 1] = o[j][3]; }
+    if (g < G) *reinterpret_cast<float2*>(mo + (warp * 16 + g) * MS + d) = make_float2(o[j][0], o[j][1]);
+    if (g + 8 < G) *reinterpret_cast<float2*>(mo + (warp * 16 + g + 8) * MS + d) = make_float2(o[j][2], o[j][3]);
   }
   if (q == 0) {
     mm[warp * 16 + g] = m_row[0]; ml[warp * 16 + g] = l_row[0];
@@ -329,7 +332,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       const float mw = mm[w * 16 + h];
       if (mw != -INFINITY) {
         const float f = expf(mw - mx);
-        acc += mo[(w * 16 + h) * D + d] * f;
+        acc += mo[(w * 16 + h) * MS + d] * f;
         lsum += ml[w * 16 + h] * f;
       }
     }
@@ -627,7 +630,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   float* part_ml = scratch;
   float* part_acc = scratch + (size_t)B * Hq * max_chunks * 2;
   size_t smem = (size_t)kDecodeStages * 2 * 4 * kDecodeWarpKeys * (D + kPad) * 2;       // stages of K and V tiles
-  const size_t merge = sizeof(float) * (4 * 16 * D + 2 * 4 * 16);
+  const size_t merge = sizeof(float) * (4 * 16 * (D + kJoinPad) + 2 * 4 * 16);
   if (merge > smem) smem = merge;
   auto kern = attn_decode_mma_kernel<D>;
   static bool attr = false;
