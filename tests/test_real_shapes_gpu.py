@@ -37,3 +37,22 @@ def test_bfloat16_path_at_real_layer_shapes(preset):
     assert torch.isfinite(got).all()
     err = (got - ref).abs().max().item()
     assert err <= REL_TOL[torch.bfloat16] * ref.abs().max().item(), err
+
+
+def test_captured_decode_steps_across_a_length_bucket_equal_eager_steps():
+    """Greedy decoding at the 8B layer shapes from a 2,040-token prompt: the captured step (graphs per
+    512-key bucket, products inside the residual stream, attention with the rotary fused) crosses
+    the 2,048-key bucket and draws the same tokens as eager steps."""
+    cfg = dataclasses.replace(LlamaConfig.from_json(preset_path("llama-3.1-8b")), num_hidden_layers=2)
+    loaded = siar.init_random(siar.build_model(cfg, torch.bfloat16, "cuda"), seed=3)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (2040, 1500)]
+    outs = []
+    for graph in (True, False):
+        eng = siar.Engine(loaded.model, max_batch=2, max_seq_len=4096, use_cuda_graph=graph)
+        outs.append(eng.generate(prompts, siar.SamplingParams(temperature=0.0), max_new_tokens=24, ignore_eos=True))
+        if graph:
+            assert len(eng._graphs) >= 2          # one per bucket crossed
+        del eng
+    assert outs[0] == outs[1]
+    assert all(len(o) == 24 for o in outs[0])
