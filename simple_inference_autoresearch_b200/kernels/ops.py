@@ -245,7 +245,6 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Te
     assert x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous()
     m, k = x.shape
     n = w.shape[0]
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     if out_dtype not in (torch.float32, x.dtype):
         raise TypeError(f"linear: output dtype {out_dtype} with input dtype {x.dtype}")
     if x.dtype == torch.bfloat16:
@@ -255,6 +254,8 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Te
             ss = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device)
             if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss):
                 return Added(ss)
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if x.dtype == torch.bfloat16:
         if gemm_tc.try_linear(x, w, out):
             return out
     _launch("gemm_simt", "siar_gemm_nt_simt", _is_bf16(x.dtype), int(out_dtype == torch.float32), _ptr(x),
