@@ -647,11 +647,22 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         } else if (p < prm.P && q < prm.Q) {
           if (vec_ok && q + 32 <= prm.Q) {
             if constexpr (sizeof(TOut) == 4) {
+              if (prm.accumulate) {          // C += D: the product adds itself into the residual stream
+                float4 old[8];
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(crow + q + j) =
-                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                __uint_as_float(r[j + 3]));
+                for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(crow + q + 4 * j);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  *reinterpret_cast<float4*>(crow + q + 4 * j) =
+                      make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
+                                  old[j].z + __uint_as_float(r[4 * j + 2]), old[j].w + __uint_as_float(r[4 * j + 3]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(crow + q + j) =
+                      make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                  __uint_as_float(r[j + 3]));
+              }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -666,7 +677,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (q + j < prm.Q) store_out<TOut>(crow + q + j, __uint_as_float(r[j]));
+              if (q + j < prm.Q) {
+                float v = __uint_as_float(r[j]);
+                if constexpr (sizeof(TOut) == 4) {
+                  if (prm.accumulate) v += reinterpret_cast<const float*>(crow)[q + j];
+                }
+                store_out<TOut>(crow + q + j, v);
+              }
           }
         }
       }
@@ -789,8 +806,9 @@ extern "C" void siar_gemm_tc_set_split_target(int blocks_per_sm) { g_split_targe
 //   max_splits caps the split along K (1 = never split; at most 8, the portable cluster size).
 //   epilogue 1: W's rows are interleaved (gate_0, up_0, gate_1, up_1, ...) and C [M, N/2] bf16 receives
 //   silu(gate) * up (never split along K).
-//   epilogue 2 (at most 16 rows): C [M,N] float32 += the product, and ss_out [M, ceil(N/128)] receives, per
-//   block of 128 outputs, the sum of squares of the new C (what the rmsnorm that follows needs).
+//   epilogue 2: C [M,N] float32 += the product.  At most 16 rows: ss_out [M, ceil(N/128)] also receives, per
+//   block of 128 outputs, the sum of squares of the new C (what the rmsnorm that follows needs).  More than
+//   128 rows (the persistent kernel): the sum only.  17..128 rows: refused.
 //   resid != nullptr (at most 16 rows; A is not read): the activations are rmsnorm(resid [M,K] float32) *
 //   norm_w with eps, the sums of squares of the rows given in pieces as ss_in [M, ss_tiles].
 static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, int out_f32, int max_splits,
@@ -799,7 +817,7 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
   if (M <= 0 || N <= 0) return 0;
   if (epilogue < 0 || epilogue > 2) return -1;
   if (epilogue == 1 && (out_f32 || (N & 1))) return -1;
-  if (epilogue == 2 && (!out_f32 || M > 16 || ss_out == nullptr)) return -1;
+  if (epilogue == 2 && (!out_f32 || (M <= 16 && ss_out == nullptr) || (M > 16 && M <= 128))) return -1;
   if (resid != nullptr && epilogue == 2) return -1;
   if (resid != nullptr && (M > 16 || ss_in == nullptr || norm_w == nullptr || ss_tiles <= 0)) return -1;
   if (epilogue == 1) max_splits = 1;

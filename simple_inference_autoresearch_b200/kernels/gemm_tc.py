@@ -59,8 +59,9 @@ def _device_state(device: torch.device):
 def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=None, ss_out=None) -> bool:
     """out[M, N] = x[M, K] @ w[N, K]^T; False when the shape is refused (nothing launched).
     ``epilogue=1``: w's rows alternate (gate, up) and out[M, N/2] = silu(gate) * up.
-    ``epilogue=2`` (at most 16 rows): out (float32) += the product and ``ss_out`` [M, ceil(N/128)]
-    receives partial sums of squares of the new rows of out.
+    ``epilogue=2``: out (float32) += the product; for at most 16 rows ``ss_out`` [M, ceil(N/128)]
+    also receives partial sums of squares of the new rows of out (more than 128 rows: no sums;
+    17..128 rows are refused).
     ``normed`` (an ``ops.NormedResidual`` of at most 16 rows; x is None): the kernel makes the
     activations rmsnorm(residual) * weight itself."""
     if not enabled:

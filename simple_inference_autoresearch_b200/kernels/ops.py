@@ -192,7 +192,8 @@ fuse_residual_stream = True
 class Added:
     """Stands for a sublayer output that the product kernel has already added into the residual
     stream.  ``ss_parts`` [rows, pieces] float32 holds, for every row, partial sums of squares of
-    the updated residual: what the rmsnorm that follows needs instead of a pass over the row."""
+    the updated residual: what the rmsnorm that follows needs instead of a pass over the row
+    (None when the kernel only added: the norm then runs as a kernel, without an add)."""
 
     __slots__ = ("ss_parts",)
 
@@ -249,9 +250,10 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Te
         raise TypeError(f"linear: output dtype {out_dtype} with input dtype {x.dtype}")
     if x.dtype == torch.bfloat16:
         from . import gemm_tc
-        if (add_to is not None and fuse_residual_stream and out_dtype == torch.float32 and m <= 16
+        if (add_to is not None and fuse_residual_stream and out_dtype == torch.float32 and (m <= 16 or m > 128)
                 and add_to.dtype == torch.float32 and add_to.shape == (m, n) and add_to.is_contiguous()):
-            ss = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device)
+            # few rows: with the sums of squares for the norm that follows; many rows: the sum only
+            ss = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device) if m <= 16 else None
             if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss):
                 return Added(ss)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)

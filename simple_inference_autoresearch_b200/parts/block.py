@@ -58,7 +58,7 @@ class PreNormBlock(Block):
         if pending is None:
             return norm.norm(ctx, residual)
         if isinstance(pending, ops.Added):
-            if consumer.takes_deferred_norm:
+            if consumer.takes_deferred_norm and pending.ss_parts is not None:
                 return norm.deferred(ctx, residual, pending)
             return norm.norm(ctx, residual)
         return norm.add_norm(ctx, residual, pending)

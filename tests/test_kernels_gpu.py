@@ -499,8 +499,25 @@ def test_product_makes_its_own_normed_input(m, n, k, pieces, swiglu):
     assert (got.float() - ref.float()).abs().max().item() <= 4e-3 * scale + 1e-4, (m, n, k)
 
 
-def test_fused_residual_stream_is_refused_beyond_sixteen_rows_and_can_be_switched_off():
-    x = rnd(17, 256, dtype=torch.bfloat16, seed=1).to(DEV)
+@pytest.mark.parametrize("m,n,k", [(129, 256, 256), (300, 520, 136), (2048, 4096, 512), (1000, 331 * 4, 264)])
+def test_product_of_many_rows_adds_into_the_residual(m, n, k):
+    """The persistent kernel's epilogue: residual += x @ w^T (no sums of squares), whole and ragged tiles."""
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    res0 = rnd(m, n, seed=3)
+    res = res0.to(DEV)
+    out = ops.linear(x, w, torch.float32, add_to=res)
+    ops.check_status(DEV)
+    assert isinstance(out, ops.Added) and out.ss_parts is None
+    want = res0.double() + x.cpu().double() @ w.cpu().double().T
+    assert (res.cpu().double() - want).abs().max().item() <= 1e-5 * k ** 0.5 + 1e-4
+    # the same numbers as the product alone followed by the add
+    delta = ops.linear(x, w, torch.float32)
+    assert torch.equal(res, res0.to(DEV) + delta)
+
+
+def test_fused_residual_stream_is_refused_from_17_to_128_rows_and_can_be_switched_off():
+    x = rnd(17, 256, dtype=torch.bfloat16, seed=1).to(DEV)            # 17..128 rows: neither kernel adds
     w = rnd(128, 256, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
     res = rnd(17, 128, seed=3).to(DEV)
     before = res.clone()
