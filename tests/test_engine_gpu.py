@@ -244,6 +244,32 @@ def test_programmatic_launch_on_and_off_give_the_same_tokens_and_logits(folders)
     assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][1], results[2][1])
 
 
+@pytest.mark.parametrize("name", "ABC")
+def test_products_inside_the_residual_stream_change_rounding_only(folders, oracle, name):
+    """Decode steps with the residual add and the norm inside the products, and with the separate
+    norm kernel: both within the bfloat16 tolerance of the plain implementation, and close to each
+    other (same arithmetic, another order of the sums of squares)."""
+    from simple_inference_autoresearch_b200.kernels import ops
+    vocab = tiny_configs.CONFIGS[name]["vocab_size"]
+    req = prompts(vocab, [50], seed=11)[0]
+    ref = oracle(name, req)
+    outs = []
+    for fuse in (True, False):
+        ops.fuse_residual_stream = fuse
+        try:
+            eng = engine_for(folders, name, torch.bfloat16, max_batch=1)
+            s = eng.open()
+            o = [eng.step([StepEntry(s, req[:10], range(10))])]
+            o += [eng.step([StepEntry(s, [t], [0])]) for t in req[10:]]
+            outs.append(torch.cat(o).float().cpu())
+        finally:
+            ops.fuse_residual_stream = True
+    scale = ref.abs().max().item()
+    for o in outs:
+        assert (o - ref).abs().max().item() <= REL_TOL[torch.bfloat16] * scale
+    assert (outs[0] - outs[1]).abs().max().item() <= REL_TOL[torch.bfloat16] * scale
+
+
 def test_command_line(folders, capsys):
     from simple_inference_autoresearch_b200 import inference
     rc = inference.main(["--model", str(folders["A"]), "--prompt-ids", "5,17,3", "--max-new-tokens", "6",
