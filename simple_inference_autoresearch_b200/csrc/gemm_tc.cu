@@ -338,6 +338,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     if (warp >= 2) {
       const int quad = warp & 3;
       const int tr = quad * 32 + lane;                  // the tile row this thread reads from TMEM
+      int push_owner = 0, push_jl = 0;
 #pragma unroll 1
       for (int ch = 0; ch < kChunks; ++ch) {
         uint32_t r[16];
@@ -348,15 +349,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
+        // output jq goes to rank jq % splits, slot jq / splits: both kept as running counters
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int jq = ch * 16 + j;
-          if (jq < BN) {
-            const int owner = jq % splits, jl = jq / splits;
-            const uint32_t local = recv + (uint32_t)(((rank * NL + jl) * 128 + tr) * 4);
+          if (ch * 16 + j < BN) {
+            const uint32_t local = recv + (uint32_t)(((rank * NL + push_jl) * 128 + tr) * 4);
             uint32_t remote;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(push_owner));
             asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(r[j]) : "memory");
+            if (++push_owner == splits) { push_owner = 0; ++push_jl; }
           }
         }
       }
