@@ -56,3 +56,34 @@ def test_captured_decode_steps_across_a_length_bucket_equal_eager_steps():
         del eng
     assert outs[0] == outs[1]
     assert all(len(o) == 24 for o in outs[0])
+
+
+@pytest.mark.parametrize("preset,batch,lo,hi,new,temperature", [
+    ("llama-3.2-1b", 16, 64, 2048, 24, 0.0),      # head_dim 64, tied embeddings, greedy
+    ("llama-3.2-3b", 32, 128, 4096, 12, 0.7),     # three query heads per kv head, seeded sampling
+])
+def test_unequal_batches_of_long_prompts_at_real_layer_shapes(preset, batch, lo, hi, new, temperature):
+    """The two workloads the smaller presets are meant for (an unequal batch of long prompts in one
+    step, then decoding; two layers here): every request gets its tokens, the same seed draws the
+    same tokens again, captured and eager steps agree, and a request alone draws what it drew in
+    the batch."""
+    cfg = dataclasses.replace(LlamaConfig.from_json(preset_path(preset)), num_hidden_layers=2)
+    loaded = siar.init_random(siar.build_model(cfg, torch.bfloat16, "cuda"), seed=5)
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
+    lens[0], lens[-1] = hi, lo
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    params = siar.SamplingParams(temperature=temperature, top_k=50 if temperature else 0, top_p=0.9 if temperature else 1.0,
+                                 seed=11)
+    runs = []
+    for graph in (True, False, True):
+        eng = siar.Engine(loaded.model, max_batch=batch, max_seq_len=hi + 64, use_cuda_graph=graph)
+        runs.append(eng.generate(prompts, params, max_new_tokens=new, ignore_eos=True))
+        if graph and len(runs) == 1:
+            alone = eng.generate(prompts[3:4], params, max_new_tokens=new, ignore_eos=True)
+        del eng
+    assert all(len(o) == new for o in runs[0])
+    assert runs[0] == runs[2]                       # same seed, same tokens
+    if temperature == 0.0:
+        assert runs[0] == runs[1]                   # captured steps == eager steps
+        assert alone[0] == runs[0][3]               # a request alone == the same request in the batch
