@@ -87,3 +87,25 @@ def test_unequal_batches_of_long_prompts_at_real_layer_shapes(preset, batch, lo,
     if temperature == 0.0:
         assert runs[0] == runs[1]                   # captured steps == eager steps
         assert alone[0] == runs[0][3]               # a request alone == the same request in the batch
+
+
+def test_float32_path_at_the_8b_layer_shapes_equals_the_plain_implementation():
+    """One layer of the Llama-3.1-8B shape (all its sizes, its vocabulary, its scaled rotary) with
+    random weights: the true 32-bit path, a prompt whole and its last tokens one by one, against
+    the plain implementation on the CPU."""
+    from simple_inference_autoresearch_b200.weights import random_tensors
+    from tests import plain_llama
+
+    cfg = dataclasses.replace(LlamaConfig.from_json(preset_path("llama-3.1-8b")), num_hidden_layers=1)
+    built = siar.build_model(cfg, torch.float32, "cuda")
+    w = random_tensors(built.model.tensor_specs(), 9, torch.float32)
+    built.model.load({k: v.to("cuda") for k, v in w.items()})
+    toks = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(3)).tolist()
+    eng = siar.Engine(built.model, max_batch=1, max_seq_len=128, use_cuda_graph=False)
+    s = eng.open()
+    outs = [eng.step([StepEntry(s, toks[:32], range(32))])]
+    outs += [eng.step([StepEntry(s, [t], [0])]) for t in toks[32:]]
+    got = torch.cat(outs).cpu()
+    ref = plain_llama.forward(w, cfg.to_dict(), toks)
+    err = (got - ref).abs().max().item()
+    assert err <= REL_TOL[torch.float32] * ref.abs().max().item(), err
