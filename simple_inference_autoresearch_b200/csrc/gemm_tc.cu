@@ -486,6 +486,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   }
 }
 
+// 32 consecutive accumulators of tile row p (columns q .. q + 31) to C: plain, added into C
+// (accumulate), or as 16 silu(gate) * up values (swiglu).
+template <typename TOut>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], TOut* crow, int p, int q, const GemmParams& prm,
+                                            bool vec_ok) {
+  if (prm.swiglu) {
+    // columns are (gate_j, up_j) pairs: 16 outputs from these 32 accumulators
+    if (p < prm.P && q < prm.Q) {
+      TOut* orow = crow + (q >> 1);
+      if (vec_ok && q + 32 <= prm.Q && sizeof(TOut) == 2) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 16) {
+          uint4 pk;
+          pk.x = pack_bf16x2(swiglu_f(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                             swiglu_f(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+          pk.y = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                             swiglu_f(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+          pk.z = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 8]), __uint_as_float(r[j + 9])),
+                             swiglu_f(__uint_as_float(r[j + 10]), __uint_as_float(r[j + 11])));
+          pk.w = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 12]), __uint_as_float(r[j + 13])),
+                             swiglu_f(__uint_as_float(r[j + 14]), __uint_as_float(r[j + 15])));
+          *reinterpret_cast<uint4*>(orow + (j >> 1)) = pk;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          if (q + j + 1 < prm.Q)
+            store_out<TOut>(orow + (j >> 1), swiglu_f(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
+      }
+    }
+  } else if (p < prm.P && q < prm.Q) {
+    if (vec_ok && q + 32 <= prm.Q) {
+      if constexpr (sizeof(TOut) == 4) {
+        if (prm.accumulate) {          // C += D: the product adds itself into the residual stream
+          float4 old[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(crow + q + 4 * j);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(crow + q + 4 * j) =
+                make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
+                            old[j].z + __uint_as_float(r[4 * j + 2]), old[j].w + __uint_as_float(r[4 * j + 3]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(crow + q + j) =
+                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                            __uint_as_float(r[j + 3]));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk;
+          pk.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+          pk.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          pk.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+          pk.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+          *reinterpret_cast<uint4*>(crow + q + j) = pk;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (q + j < prm.Q) {
+          float v = __uint_as_float(r[j]);
+          if constexpr (sizeof(TOut) == 4) {
+            if (prm.accumulate) v += reinterpret_cast<const float*>(crow)[q + j];
+          }
+          store_out<TOut>(crow + q + j, v);
+        }
+    }
+  }
+
+}
+
 // ------------------------------------------------------------------ persistent kernel (many rows)
 // The prefill orientation (X = activations, C[p][q] = D[p][q]) as persistent blocks: one block
 // per SM walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tile rows fastest, so
@@ -620,73 +695,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int q = q0 + ch * 32;
-        if (prm.swiglu) {
-          // columns are (gate_j, up_j) pairs: 16 outputs from these 32 accumulators
-          if (p < prm.P && q < prm.Q) {
-            TOut* orow = crow + (q >> 1);
-            if (vec_ok && q + 32 <= prm.Q && sizeof(TOut) == 2) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 16) {
-                uint4 pk;
-                pk.x = pack_bf16x2(swiglu_f(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
-                                   swiglu_f(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
-                pk.y = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
-                                   swiglu_f(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
-                pk.z = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 8]), __uint_as_float(r[j + 9])),
-                                   swiglu_f(__uint_as_float(r[j + 10]), __uint_as_float(r[j + 11])));
-                pk.w = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 12]), __uint_as_float(r[j + 13])),
-                                   swiglu_f(__uint_as_float(r[j + 14]), __uint_as_float(r[j + 15])));
-                *reinterpret_cast<uint4*>(orow + (j >> 1)) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 2)
-                if (q + j + 1 < prm.Q)
-                  store_out<TOut>(orow + (j >> 1), swiglu_f(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
-            }
-          }
-        } else if (p < prm.P && q < prm.Q) {
-          if (vec_ok && q + 32 <= prm.Q) {
-            if constexpr (sizeof(TOut) == 4) {
-              if (prm.accumulate) {          // C += D: the product adds itself into the residual stream
-                float4 old[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(crow + q + 4 * j);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  *reinterpret_cast<float4*>(crow + q + 4 * j) =
-                      make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
-                                  old[j].z + __uint_as_float(r[4 * j + 2]), old[j].w + __uint_as_float(r[4 * j + 3]));
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                  *reinterpret_cast<float4*>(crow + q + j) =
-                      make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                  __uint_as_float(r[j + 3]));
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                pk.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                pk.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                pk.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                pk.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                *reinterpret_cast<uint4*>(crow + q + j) = pk;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (q + j < prm.Q) {
-                float v = __uint_as_float(r[j]);
-                if constexpr (sizeof(TOut) == 4) {
-                  if (prm.accumulate) v += reinterpret_cast<const float*>(crow)[q + j];
-                }
-                store_out<TOut>(crow + q + j, v);
-              }
-          }
-        }
+        store_chunk<TOut>(r, crow, p, q, prm, vec_ok);
       }
       // this accumulator may be overwritten once all four epilogue warps have read it
       tc_fence_before();
@@ -699,6 +708,157 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ persistent kernel, two SMs per tile
+// The same orientation with cta_group::2: a cluster of two blocks (two SMs) owns a 256 x 256 output
+// tile.  Each block loads 128 of the tile's A rows and 128 of its B rows, so a block brings in
+// (128 + 128) x 64 elements per k-block for its 128 x 256 outputs instead of (128 + 256) x 64: a
+// third less traffic from L2, which is what bounds the one-SM kernel.  The even block's MMA thread
+// issues M = 256, N = 256 MMAs that read both blocks' shared memory and write both blocks' tensor
+// memory; both blocks' TMA loads count on the even block's barrier; tcgen05.commit arrives on both
+// blocks' barriers at once; both blocks' epilogues release the accumulator on the even block's
+// barrier.  Everything else (persistent walk over tiles, two accumulators, epilogues) is as above.
+template <int STAGES, typename TOut>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
+                    const GemmParams prm) {
+  constexpr int BN = 256;                               // the MMA's N; a block holds BN / 2 rows of B
+  constexpr uint32_t kXBytes = kBM * kBK * 2;
+  constexpr uint32_t kYBytes = (BN / 2) * kBK * 2;
+  constexpr uint32_t kStageBytes = kXBytes + kYBytes;
+  constexpr uint32_t kTmemCols = 2 * BN;               // two accumulators
+
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];    // used in the even block
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];       // used in the even block
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  pdl_launch_dependents();
+  const uint32_t dyn = smem_u32(smem_dyn);
+  unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_rank();                 // 0: issues the MMAs
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_p = (prm.P + 2 * kBM - 1) / (2 * kBM), tiles_q = (prm.Q + BN - 1) / BN;
+  const int n_tiles = tiles_p * tiles_q;
+  const int num_kb = (prm.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2);                     // one arrival from each block's epilogue
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(&tmem_base_slot, kTmemCols);
+  tc_fence_before();
+  cluster_sync_all();                                   // both blocks' barriers exist before either is signalled
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const bool dead = (*(volatile int*)prm.status & kStatusWaitExpired) != 0;
+
+  if (dead) {
+    // nothing
+  } else if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmY) : "memory");
+      pdl_wait();
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+        const int p0 = (t % tiles_p) * 2 * kBM + rank * kBM;        // this block's rows of A (and of the output)
+        const int q0 = (t / tiles_p) * BN + rank * (BN / 2);        // this block's rows of B
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1) || *(volatile int*)&abort_flag) { ok = false; break; }
+          unsigned char* xs = tiles + (size_t)s * kStageBytes;
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * kStageBytes);   // both blocks' bytes
+          tma_load_2d_pair(xs, &tmX, &full_bar[s], kb * kBK, p0);
+          tma_load_2d_pair(xs + kXBytes, &tmY, &full_bar[s], kb * kBK, q0);
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16_pair(BN);
+      int it = 0, i = 0;
+      bool ok = true;
+      for (int t = pair; t < n_tiles && ok; t += n_pairs, ++i) {
+        const int acc = i & 1;
+        // both epilogues have drained this accumulator (passes at once for the first two tiles)
+        if (!mbar_wait(&tempty_bar[acc], ((i >> 1) & 1) ^ 1) || *(volatile int*)&abort_flag) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph) || *(volatile int*)&abort_flag) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t xs = smem_u32(tiles + (size_t)s * kStageBytes);
+          const uint64_t da = smem_desc_sw128(xs), db = smem_desc_sw128(xs + kXBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_f16_pair(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(&empty_bar[s]);              // the stage is free in both blocks
+        }
+        if (ok) umma_commit_pair(&tfull_bar[acc]);      // both blocks' halves of the tile are complete
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    TOut* C = (TOut*)prm.C;
+    pdl_wait();
+    const bool vec_ok = (prm.ldc % (prm.swiglu ? 16 : 8) == 0) && ((reinterpret_cast<uintptr_t>(C) % 16) == 0);
+    int i = 0;
+    for (int t = pair; t < n_tiles; t += n_pairs, ++i) {
+      const int acc = i & 1;
+      const int p0 = (t % tiles_p) * 2 * kBM + rank * kBM, q0 = (t / tiles_p) * BN;
+      if (!mbar_wait(&tfull_bar[acc], (i >> 1) & 1) || *(volatile int*)&abort_flag) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+        break;
+      }
+      tc_fence_after();
+      const int p = p0 + quad * 32 + lane;
+      TOut* crow = C + (long long)p * prm.ldc;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t r[32];
+        SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        store_chunk<TOut>(r, crow, p, q0 + ch * 32, prm, vec_ok);
+      }
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) mbar_arrive_even(&tempty_bar[acc]);
+    }
+  }
+  // neither block leaves (or gives its tensor memory back) while the other may still touch it
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -785,6 +945,36 @@ static int launch_persistent(const CUtensorMap& tmX, const CUtensorMap& tmY, con
   return (int)launch_kernel(kern, dim3(blocks), dim3(192), smem, s, tmX, tmY, prm);
 }
 
+template <int STAGES, typename TOut>
+static int launch_pair(const CUtensorMap& tmX, const CUtensorMap& tmY, const GemmParams& prm, int sm_count,
+                       cudaStream_t s) {
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK * 2 + 128 * kBK * 2) + 1024;
+  auto kern = gemm_tc_pair_kernel<STAGES, TOut>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int n_tiles = ((prm.P + 2 * kBM - 1) / (2 * kBM)) * ((prm.Q + 255) / 256);
+  const int pairs = n_tiles < sm_count / 2 ? n_tiles : sm_count / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, kern, tmX, tmY, prm);
+}
+
 }  // namespace siar
 
 using namespace siar;
@@ -796,6 +986,14 @@ SIAR_DEFINE_PDL_SWITCH()
 static unsigned long long* g_stamps = nullptr;
 extern "C" void siar_gemm_tc_set_stamps(unsigned long long* p) { g_stamps = p; }
 #endif
+
+// Products of many rows with at least 256 output columns: two SMs per 256 x 256 tile or one SM per
+// 128 x 256 tile.  0 = never pairs, 2 = always, 1 = pairs from kPairRows rows on (measured on B200 with
+// the Llama-3.1-8B products: at 8,192 rows pairs are 2% faster, at 2,048 rows 1.5% slower; both run
+// near the clocks the power cap allows, so the third less traffic from L2 buys little).
+static int g_pairs = 1;
+constexpr int kPairRows = 4096;
+extern "C" void siar_gemm_tc_set_pairs(int mode) { g_pairs = mode < 0 ? 0 : mode > 2 ? 2 : mode; }
 
 // Products with fewer output tiles than this many per SM are split along K.
 static int g_split_target = 1;
@@ -872,6 +1070,12 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
   prm.stamps = g_stamps;
 #endif
 
+  if (!swap && BN == 256 && sm_count >= 2 && (g_pairs == 2 || (g_pairs == 1 && P >= kPairRows))) {
+    CUtensorMap tmY2;
+    if (tensor_map(Y, Q, K, 128, &tmY2))
+      return out_f32 ? launch_pair<6, float>(tmX, tmY2, prm, sm_count, s)
+                     : launch_pair<6, __nv_bfloat16>(tmX, tmY2, prm, sm_count, s);
+  }
   if (!swap) {
     if (BN == 256)
       return out_f32 ? launch_persistent<256, 4, float>(tmX, tmY, prm, sm_count, s)

@@ -47,6 +47,12 @@ def _bind_fused():
     return _fn_fused
 
 
+def set_pairs(mode: int) -> None:
+    """Products of many rows: two SMs on one 256 x 256 tile (cta_group::2) or one SM per 128 x 256
+    tile.  0 = never pairs, 1 = pairs from 4,096 rows on (the default), 2 = always pairs."""
+    build.load_unit("gemm_tc").siar_gemm_tc_set_pairs(int(mode))
+
+
 def _device_state(device: torch.device):
     key = device.index if device.index is not None else torch.cuda.current_device()
     st = _state.get(key)

@@ -422,6 +422,33 @@ def test_tensor_core_linear(m, n, k):
     torch.testing.assert_close(tc, simt, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 4096, 4096), (256, 512, 128), (129, 256, 72), (1500, 1000, 2048), (384, 28672 // 8, 512)])
+def test_two_sms_on_one_tile_give_the_one_sm_kernels_numbers(m, n, k):
+    """Products of many rows with cta_group::2 (a pair of blocks per 256 x 256 tile) and with one
+    block per 128 x 256 tile: the same k order, so the same numbers; plain, SwiGLU and adding epilogues,
+    whole and ragged tiles, an odd number of 128-row blocks."""
+    from simple_inference_autoresearch_b200.kernels import gemm_tc
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    outs = []
+    for pairs in (2, 0):
+        gemm_tc.set_pairs(pairs)
+        try:
+            a = ops.linear(x, w, torch.float32)
+            b = ops.linear(x, w, torch.bfloat16)
+            c = ops.linear_swiglu(x, w)
+            res = torch.ones(m, n, device=DEV)
+            assert isinstance(ops.linear(x, w, torch.float32, add_to=res), ops.Added)
+        finally:
+            gemm_tc.set_pairs(1)
+        ops.check_status(DEV)
+        outs.append((a.cpu(), b.float().cpu(), c.float().cpu(), res.cpu()))
+    ref = x.cpu().double() @ w.cpu().double().T
+    assert (outs[0][0].double() - ref).abs().max().item() <= 1e-5 * k ** 0.5 + 1e-4
+    for u, v in zip(*outs):
+        assert torch.equal(u, v)
+
+
 def test_tensor_core_linear_refuses_unaligned_k():
     from simple_inference_autoresearch_b200.kernels import gemm_tc
     x, w = rnd(4, 20, dtype=torch.bfloat16).to(DEV), rnd(8, 20, dtype=torch.bfloat16).to(DEV)
