@@ -360,45 +360,45 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   SIAR_STAMP(5);
   if (!is_last) { SIAR_TRACE(20, 1); return; }
   __threadfence();
-  // weights of the chunks: wgt[h][c] = exp(m_c - max) / sum, formed once per head
-  float* cm = reinterpret_cast<float*>(smem_raw);            // [G][n_chunks] maxima, then weights
-  float* cl = cm + G * n_chunks;                              // [G][n_chunks] sums
+  // Each thread joins its output's partials itself, chunk after chunk with a running maximum (the
+  // order of a sequential softmax, whatever block does it): the maxima, sums and values of eight
+  // chunks are asked for together, so the join costs one trip to L2 per eight chunks and no barrier.
   const size_t pbase = ((size_t)b * Hq + kvh * G) * max_chunks;
-  for (int idx = threadIdx.x; idx < G * n_chunks; idx += blockDim.x) {
-    const int h = idx / n_chunks, cc = idx % n_chunks;
-    cm[idx] = __ldcg(part_ml + (pbase + (size_t)h * max_chunks + cc) * 2);
-    cl[idx] = __ldcg(part_ml + (pbase + (size_t)h * max_chunks + cc) * 2 + 1);
-  }
-  __syncthreads();
-  if (threadIdx.x < G) {
-    const int h = threadIdx.x;
-    float mx = -INFINITY;
-    for (int cc = 0; cc < n_chunks; ++cc) mx = fmaxf(mx, cm[h * n_chunks + cc]);
-    float lsum = 0.f;
-    for (int cc = 0; cc < n_chunks; ++cc) {
-      const float f = expf(cm[h * n_chunks + cc] - mx);
-      lsum += cl[h * n_chunks + cc] * f;
-      cm[h * n_chunks + cc] = f;
-    }
-    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-    for (int cc = 0; cc < n_chunks; ++cc) cm[h * n_chunks + cc] *= inv;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int h = idx / D, d = idx % D;
+  for (int item = threadIdx.x; item < G * (D / 4); item += blockDim.x) {     // four outputs of one head per thread
+    const int h = item / (D / 4), d = (item % (D / 4)) * 4;
+    const float2* pml = reinterpret_cast<const float2*>(part_ml) + pbase + (size_t)h * max_chunks;
     const float* pa = part_acc + (pbase + (size_t)h * max_chunks) * D + d;
-    float acc = 0.f;
-    int cc = 0;
-    for (; cc + 4 <= n_chunks; cc += 4) {
-      const float v0 = __ldcg(pa + (size_t)cc * D), v1 = __ldcg(pa + (size_t)(cc + 1) * D);
-      const float v2 = __ldcg(pa + (size_t)(cc + 2) * D), v3 = __ldcg(pa + (size_t)(cc + 3) * D);
-      acc += v0 * cm[h * n_chunks + cc];
-      acc += v1 * cm[h * n_chunks + cc + 1];
-      acc += v2 * cm[h * n_chunks + cc + 2];
-      acc += v3 * cm[h * n_chunks + cc + 3];
+    float run_m = -INFINITY, run_l = 0.f;
+    float4 run_a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int cc = 0; cc < n_chunks; cc += 8) {
+      float2 ml8[8];
+      float4 a8[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = cc + u < n_chunks;
+        ml8[u] = in ? __ldcg(pml + cc + u) : make_float2(-INFINITY, 0.f);
+        a8[u] = in ? __ldcg(reinterpret_cast<const float4*>(pa + (size_t)(cc + u) * D)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float m_new = fmaxf(run_m, ml8[u].x);
+        if (m_new != -INFINITY) {
+          // (the fast exponential: about 1e-6 relative here; the outputs are rounded to bfloat16)
+          const float f_old = __expf(run_m - m_new), f_new = __expf(ml8[u].x - m_new);
+          run_a.x = run_a.x * f_old + a8[u].x * f_new;
+          run_a.y = run_a.y * f_old + a8[u].y * f_new;
+          run_a.z = run_a.z * f_old + a8[u].z * f_new;
+          run_a.w = run_a.w * f_old + a8[u].w * f_new;
+          run_l = run_l * f_old + ml8[u].y * f_new;
+          run_m = m_new;
+        }
+      }
     }
-    for (; cc < n_chunks; ++cc) acc += __ldcg(pa + (size_t)cc * D) * cm[h * n_chunks + cc];
-    orow[h * D + d] = __float2bfloat16_rn(acc);
+    const float inv = run_l > 0.f ? 1.f / run_l : 0.f;
+    uint2 pk;
+    pk.x = pack_bf16(run_a.x * inv, run_a.y * inv);
+    pk.y = pack_bf16(run_a.z * inv, run_a.w * inv);
+    *reinterpret_cast<uint2*>(orow + h * D + d) = pk;
   }
   SIAR_STAMP(6);
   SIAR_TRACE(20, 1);
