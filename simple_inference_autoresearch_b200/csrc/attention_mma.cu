@@ -68,16 +68,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   __shared__ float cs_s[D];                     // cos[D/2], sin[D/2] of the new token's position
   pdl_launch_dependents();
   SIAR_TRACE(20, 0);
-  // What the kernel in front (the qkv product) writes is the fused row only.  When this kernel
-  // itself writes the new token's k and v, everything else it reads (lengths, block table, pages
-  // of earlier tokens) was complete before this step began (the step's first kernel is a full
-  // barrier, see embed_gather_kernel), so the look-ups and the first tiles are asked for BEFORE
-  // the wait and are on their way, or there, when the product finishes.
-  const bool early = fuse_rope && write_kv;
-  if (!early) {
-    pdl_wait();
-    SIAR_TRACE(20, 2);
-  }
+  pdl_wait();
+  SIAR_TRACE(20, 2);
   constexpr int RS = D + kPad;                 // row stride in elements
   constexpr int CPR = D / 8;                   // 16-byte pieces per row
   constexpr int WK = kDecodeWarpKeys;          // keys per warp and step
@@ -92,6 +84,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   // trip to L2: everything that has its address is asked for before anything is used.
   const int base_b = base_len[b], slot = slot_ids[b], row_b = q_start[b];
   const int kv_len = base_b + 1;
+  const float sl2 = scale * 1.4426950408889634f;     // scores, maxima and the partials' maxima are in the base-2 domain
   const int c0 = c * chunk_keys;
   if (c0 >= kv_len) return;
   SIAR_STAMP(0);
@@ -135,12 +128,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   }
   SIAR_STAMP(7);
   int page_ahead = pages[kDecodeStages - 1];      // page of tile it + kDecodeStages - 1 at step it
-  if (early) {
-    pdl_wait();
-    SIAR_TRACE(20, 2);
-  }
   static_assert(D / 2 <= 128, "one thread per rotation frequency");
-  const float freq = fuse_rope && inv_freq != nullptr && threadIdx.x < D / 2 ? __ldg(inv_freq + threadIdx.x) : 0.f;
+  const int pos = kv_len - 1;                      // position of the new token
+  if (fuse_rope) {
+    if (threadIdx.x < D / 2) {
+      float sn = 0.f, cs = 1.f;
+      if (inv_freq != nullptr) sincosf((float)pos * __ldg(inv_freq + threadIdx.x), &sn, &cs);
+      cs_s[threadIdx.x] = cs;
+      cs_s[D / 2 + threadIdx.x] = sn;
+    }
+  }
   // query fragments straight from global memory: rows g and g + 8 of the (padded) group
   const size_t tok_row = (size_t)row_b * (Hq + 2 * Hkv) * D;
   uint32_t qa[D / 16][4];
@@ -156,16 +153,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     }
   }
 
-  const int pos = kv_len - 1;                      // position of the new token
-  if (fuse_rope) {
-    if (threadIdx.x < D / 2) {
-      float sn = 0.f, cs = 1.f;
-      if (inv_freq != nullptr) sincosf((float)pos * freq, &sn, &cs);
-      cs_s[threadIdx.x] = cs;
-      cs_s[D / 2 + threadIdx.x] = sn;
-    }
-    __syncthreads();
-  }
+  if (fuse_rope) __syncthreads();                  // cos / sin are in shared memory
   {
     if (fuse_rope) {
       // columns c < D/2 pair with c + D/2: fragment kk pairs with fragment kk + D/32, same register
@@ -251,7 +239,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = 8 * j + 2 * q + (e & 1);
-        const float v = key < valid ? s[j][e] * scale : -INFINITY;
+        const float v = key < valid ? s[j][e] * sl2 : -INFINITY;      // scores in the base-2 domain
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -260,12 +248,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     mx[1] = quad_max(mx[1]);
     float alpha[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int h = 0; h < 2; ++h) alpha[h] = mx[h] == -INFINITY ? 1.f : expf(m_row[h] - mx[h]);
+    for (int h = 0; h < 2; ++h) alpha[h] = mx[h] == -INFINITY ? 1.f : fast_exp2(m_row[h] - mx[h]);
 #pragma unroll
     for (int j = 0; j < WK / 8; ++j) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float p = s[j][e] == -INFINITY ? 0.f : expf(s[j][e] - mx[e >> 1]);
+        const float p = s[j][e] == -INFINITY ? 0.f : fast_exp2(s[j][e] - mx[e >> 1]);
         s[j][e] = p;
         sum[e >> 1] += p;
       }
@@ -331,7 +319,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     for (int w = 0; w < 4; ++w) {
       const float mw = mm[w * 16 + h];
       if (mw != -INFINITY) {
-        const float f = expf(mw - mx);
+        const float f = fast_exp2(mw - mx);
         acc += mo[(w * 16 + h) * MS + d] * f;
         lsum += ml[w * 16 + h] * f;
       }
@@ -383,8 +371,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       for (int u = 0; u < 8; ++u) {
         const float m_new = fmaxf(run_m, ml8[u].x);
         if (m_new != -INFINITY) {
-          // (the fast exponential: about 1e-6 relative here; the outputs are rounded to bfloat16)
-          const float f_old = __expf(run_m - m_new), f_new = __expf(ml8[u].x - m_new);
+          const float f_old = fast_exp2(run_m - m_new), f_new = fast_exp2(ml8[u].x - m_new);
           run_a.x = run_a.x * f_old + a8[u].x * f_new;
           run_a.y = run_a.y * f_old + a8[u].y * f_new;
           run_a.z = run_a.z * f_old + a8[u].z * f_new;

@@ -20,13 +20,9 @@ namespace siar {
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                     float* __restrict__ out, int H, int V, int* __restrict__ status) {
-  // The first kernel of every step lets its dependents start only after its own wait has
-  // returned, i.e. after everything in front of it is complete: the kernels of a step never run
-  // beside those of the step before.  (Every other kernel triggers at its top; the decode
-  // attention relies on this when it reads cache pages of earlier steps before its wait.)
+  pdl_launch_dependents();
   SIAR_TRACE(1, 0);
   pdl_wait();
-  pdl_launch_dependents();
   SIAR_TRACE(1, 2);
   const int t = blockIdx.x;
   int id = tokens[t];
