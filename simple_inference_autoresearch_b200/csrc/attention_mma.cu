@@ -263,7 +263,8 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       l_row[h] = l_row[h] * alpha[h] + quad_sum(sum[h]);
       m_row[h] = mx[h];
     }
-    if (it > 0) {
+    // the accumulators are rescaled only when some row's maximum moved (rare after the first tiles)
+    if (it > 0 && __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
       for (int j = 0; j < D / 8; ++j) {
         o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
