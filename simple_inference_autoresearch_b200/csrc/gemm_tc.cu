@@ -312,8 +312,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
+        if (BN >= 32 && prm.transpose_out) {
+          // wide tiles are staged column by column (stage[column][tile row]): a warp writes 32
+          // consecutive words, and the write-out reads four tile rows of a column as one float4
 #pragma unroll
-        for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 16; ++j) stage[(ch * 16 + j) * kBM + tr] = __uint_as_float(r[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stage[tr * LD + ch * 16 + j] = __uint_as_float(r[j]);
+        }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
@@ -335,7 +342,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     const int NL = (BN + splits - 1) / splits;          // outputs per owner
     const int et = threadIdx.x - 64;                    // epilogue thread = tile row p
     const uint32_t recv = smem_u32(tiles);              // float recv[splits][NL][128]
-    if (warp >= 2) {
+    // Tiles of 32 and more columns hand over groups of four columns: group gq belongs to rank
+    // gq % splits, and a thread sends a group as one 16-byte remote store
+    // (float4 recv[sender][group slot][128 tile rows]).
+    constexpr int kGroups = BN / 4;
+    const int NLg = (kGroups + splits - 1) / splits;    // groups per owner
+    if constexpr (BN >= 32) {
+      if (warp >= 2) {
+        const int quad = warp & 3;
+        const int tr = quad * 32 + lane;
+        int push_owner = 0, push_gl = 0;
+#pragma unroll 1
+        for (int ch = 0; ch < kChunks; ++ch) {
+          uint32_t r[16];
+          if (num_kb > 0 && acc_ok) {
+            SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0u;
+          }
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            const uint32_t local = recv + (uint32_t)(((rank * NLg + push_gl) * 128 + tr) * 16);
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(push_owner));
+            asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(r[4 * g4]),
+                         "r"(r[4 * g4 + 1]), "r"(r[4 * g4 + 2]), "r"(r[4 * g4 + 3])
+                         : "memory");
+            if (++push_owner == splits) { push_owner = 0; ++push_gl; }
+          }
+        }
+      }
+    } else if (warp >= 2) {
       const int quad = warp & 3;
       const int tr = quad * 32 + lane;                  // the tile row this thread reads from TMEM
       int push_owner = 0, push_jl = 0;
@@ -388,6 +427,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           }
         }
       }
+      if constexpr (BN >= 32) {
+        const float4* mine4 = reinterpret_cast<const float4*>(tiles);
+        for (int gl = 0; gl < NLg; ++gl) {
+          const int gq = gl * splits + rank;
+          if (gq >= kGroups || q0 + 4 * gq >= prm.Q) break;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int z = 0; z < splits; ++z) {
+            const float4 v = mine4[(z * NLg + gl) * 128 + et];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          if (pp < prm.P) {
+            const int q = q0 + 4 * gq;
+            TOut* dst = C + (long long)q * prm.ldc + pp;
+            store_out<TOut>(dst, acc.x);
+            if (q + 1 < prm.Q) store_out<TOut>(dst + prm.ldc, acc.y);
+            if (q + 2 < prm.Q) store_out<TOut>(dst + 2 * (long long)prm.ldc, acc.z);
+            if (q + 3 < prm.Q) store_out<TOut>(dst + 3 * (long long)prm.ldc, acc.w);
+          }
+        }
+        stored = true;
+      }
       for (int jl = 0; jl < NL && !stored; ++jl) {
         const int jq = jl * splits + rank;
         const int q = q0 + jq;
@@ -409,7 +469,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   } else if (warp >= 2 && !dead) {
     const int et = threadIdx.x - 64;          // 0..127
     const int ew = et >> 5;
-    if (prm.transpose_out && prm.swiglu) {
+    if (BN >= 32 && prm.transpose_out) {
+      // wide tiles: warp ew takes columns ew, ew + 4, ...; a lane holds four consecutive tile rows
+      // of the column, which are four (or, as two (gate, up) pairs, two) consecutive outputs
+      const int cols = min(BN, prm.Q - q0);
+      const int pp = p0 + 4 * lane;
+      const bool vec_ok = prm.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(C) % 16) == 0 && pp + 3 < prm.P;
+      for (int jq = ew; jq < cols; jq += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(stage + jq * kBM + 4 * lane);
+        if (prm.swiglu) {
+          TOut* dst = C + (long long)(q0 + jq) * prm.ldc + (pp >> 1);
+          const float o0 = swiglu_f(v.x, v.y), o1 = swiglu_f(v.z, v.w);
+          if (sizeof(TOut) == 2 && vec_ok) {
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(o0, o1);
+          } else {
+            if (pp + 1 < prm.P) store_out<TOut>(dst, o0);
+            if (pp + 3 < prm.P) store_out<TOut>(dst + 1, o1);
+          }
+        } else {
+          TOut* dst = C + (long long)(q0 + jq) * prm.ldc + pp;
+          if (vec_ok) {
+            if constexpr (sizeof(TOut) == 4) {
+              *reinterpret_cast<float4*>(dst) = v;
+            } else {
+              uint2 pk;
+              pk.x = pack_bf16x2(v.x, v.y);
+              pk.y = pack_bf16x2(v.z, v.w);
+              *reinterpret_cast<uint2*>(dst) = pk;
+            }
+          } else {
+            if (pp < prm.P) store_out<TOut>(dst, v.x);
+            if (pp + 1 < prm.P) store_out<TOut>(dst + 1, v.y);
+            if (pp + 2 < prm.P) store_out<TOut>(dst + 2, v.z);
+            if (pp + 3 < prm.P) store_out<TOut>(dst + 3, v.w);
+          }
+        }
+      }
+    } else if (prm.transpose_out && prm.swiglu) {
       // tile rows are weight rows (gate_j, up_j, gate_j+1, ...): even rows write silu(gate) * up
       const int pp = p0 + et;
       if ((et & 1) == 0 && pp + 1 < prm.P) {

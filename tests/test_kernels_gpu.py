@@ -121,7 +121,8 @@ def test_swiglu(dtype, interleaved, i):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("m,i,k", [(1, 176, 64), (8, 14336, 512), (70, 136, 80), (64, 256, 96), (130, 331, 96),
-                                   (300, 1024, 264), (2048, 512, 128), (5, 44, 20)])
+                                   (300, 1024, 264), (2048, 512, 128), (5, 44, 20), (33, 331, 96), (64, 14336, 512),
+                                   (20, 178, 72), (128, 130, 264)])
 def test_linear_with_swiglu_epilogue(dtype, m, i, k):
     """The fused product + activation (tensor cores, both orientations) and its unfused fallback."""
     x = rnd(m, k, dtype=dtype, seed=1)
@@ -398,6 +399,7 @@ def test_sample_same_request_same_draw_in_any_batch():
     (1, 128, 64), (1, 4096, 4096), (8, 6144, 4096), (8, 512, 14336), (16, 130, 264), (17, 256, 128),
     (33, 1000, 72), (64, 4096, 1024), (65, 384, 512), (128, 256, 256), (129, 256, 256), (200, 331, 96),
     (300, 520, 4096), (1024, 768, 512), (5, 40, 8), (2048, 256, 128),
+    (20, 130, 264), (40, 331, 96), (64, 6144, 4096), (48, 4096, 14336), (100, 4096, 4096), (128, 1002, 520),
 ])
 def test_tensor_core_linear(m, n, k):
     from simple_inference_autoresearch_b200.kernels import gemm_tc
