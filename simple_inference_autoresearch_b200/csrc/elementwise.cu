@@ -35,6 +35,42 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const T* __r
   for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)t * H + j] = to_f32(row[j]);
 }
 
+// The same for a bfloat16 table whose rows are whole 16-byte pieces: eight values per thread and
+// load, every load of a thread asked for before the first is used.
+__global__ void embed_gather_bf16x8_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                                           float* __restrict__ out, int H, int V, int* __restrict__ status) {
+  pdl_launch_dependents();
+  SIAR_TRACE(1, 0);
+  pdl_wait();
+  SIAR_TRACE(1, 2);
+  const int t = blockIdx.x;
+  const int id = tokens[t];
+  const bool bad = id < 0 || id >= V;
+  if (bad && threadIdx.x == 0) atomicOr(status, kStatusTokenOutOfRange);
+  const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(bad ? 0 : id) * H);
+  float4* dst = reinterpret_cast<float4*>(out + (size_t)t * H);
+  const int pieces = H / 8;
+  for (int j0 = threadIdx.x; j0 < pieces; j0 += 4 * blockDim.x) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * blockDim.x;
+      v[u] = (j < pieces && !bad) ? __ldg(row + j) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * blockDim.x;
+      if (j >= pieces) break;
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].y));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].z));
+      const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].w));
+      dst[2 * j] = make_float4(a.x, a.y, b.x, b.y);
+      dst[2 * j + 1] = make_float4(c.x, c.y, d.x, d.y);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ row gather
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows,
                                    float* __restrict__ dst, int H) {
@@ -385,7 +421,9 @@ extern "C" int siar_embed_gather(int is_bf16, const int* tokens, const void* tab
                                  int V, int* status, void* stream) {
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  if (is_bf16)
+  if (is_bf16 && H % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) % 16) == 0)
+    launch_kernel(embed_gather_bf16x8_kernel, N, 128, 0, s, tokens, (const __nv_bfloat16*)table, out, H, V, status);
+  else if (is_bf16)
     launch_kernel(embed_gather_kernel<__nv_bfloat16>, N, 256, 0, s, tokens, (const __nv_bfloat16*)table, out, H, V, status);
   else
     launch_kernel(embed_gather_kernel<float>, N, 256, 0, s, tokens, (const float*)table, out, H, V, status);

@@ -29,7 +29,7 @@ def tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,h,v", [(1, 64, 256), (7, 80, 331), (33, 4096, 1000)])
+@pytest.mark.parametrize("n,h,v", [(1, 64, 256), (7, 80, 331), (33, 4096, 1000), (3, 44, 50), (2, 5000, 300)])
 def test_embed(dtype, n, h, v):
     table = rnd(v, h, dtype=dtype)
     tokens = torch.randint(0, v, (n,), dtype=torch.int32)
@@ -38,12 +38,14 @@ def test_embed(dtype, n, h, v):
     torch.testing.assert_close(out.cpu(), emu.embed(tokens, table), rtol=0, atol=0)
 
 
-def test_embed_flags_bad_token():
-    table = rnd(16, 32).to(DEV)
-    ops.embed(torch.tensor([3, 16], dtype=torch.int32, device=DEV), table)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_flags_bad_token(dtype):
+    table = rnd(16, 32, dtype=dtype).to(DEV)
+    out = ops.embed(torch.tensor([3, 16, -1], dtype=torch.int32, device=DEV), table)
     with pytest.raises(RuntimeError, match="token id outside"):
         ops.check_status(DEV)
     ops.check_status(DEV)  # cleared
+    assert torch.equal(out[0].cpu(), table[3].float().cpu()) and not out[1:].any()
 
 
 def test_gather_rows():
