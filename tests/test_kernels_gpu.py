@@ -367,6 +367,42 @@ def test_sample_matches_plain_sampler(v, temperature, top_k, top_p):
             assert lo - 1e-5 <= u <= cdf[got[i]] + 1e-5, (got[i], want, u, float(lo), float(cdf[got[i]]))
 
 
+@pytest.mark.parametrize("v,scale,temperature,top_k,top_p", [
+    (5000, 6.0, 1.0, 0, 0.9),       # a peaked row: the nucleus lies within the gathered candidates
+    (5000, 0.1, 1.0, 0, 0.5),       # a flat row: the nucleus is far larger than the candidates (whole-row bisection)
+    (3000, 2.0, 1.0, 600, 1.0),     # top-k beyond what the candidate way takes
+    (3000, 2.0, 0.9, 600, 0.8),
+    (5000, 3.0, 0.7, 512, 0.95),    # the largest top-k of the candidate way
+    (1500, 2.0, 1.0, 1499, 1.0),
+])
+def test_sample_both_ways_to_the_thresholds_match_the_plain_sampler(v, scale, temperature, top_k, top_p):
+    rows = 4
+    logits = rnd(rows, v, seed=21, scale=scale)
+    seeds = [99 + 5 * i for i in range(rows)]
+    idx = [0, 7, 8, 300]
+    got = sample_case(logits, [temperature] * rows, [top_k] * rows, [top_p] * rows, seeds, idx)
+    for i in range(rows):
+        u = plain_llama.counter_uniform(seeds[i], idx[i])
+        probs = plain_llama.kept_probabilities(logits[i], temperature, top_k, top_p)
+        cdf = torch.cumsum(probs, 0)
+        assert probs[got[i]] > 0, "drew a token outside the kept set"
+        lo = cdf[got[i]] - probs[got[i]]
+        assert lo - 1e-5 <= u <= cdf[got[i]] + 1e-5, (got[i], u, float(lo), float(cdf[got[i]]))
+
+
+@pytest.mark.parametrize("v", [300, 6000])
+def test_sample_tokens_of_equal_logit_enter_or_leave_the_nucleus_together(v):
+    logits = torch.full((1, v), -10.0)
+    logits[0, 10] = 5.0
+    logits[0, [20, 30, 40]] = 4.0           # weights 1 and 3 x e^-1: the group's mass before it is 1 of 2.10
+    inside, outside = set(), set()
+    for i in range(150):
+        inside.add(sample_case(logits, [1.0], [0], [0.6], [5], [i])[0])     # limit 1.26 >= 1: the group stays
+        outside.add(sample_case(logits, [1.0], [0], [0.4], [5], [i])[0])    # limit 0.84 < 1: the group leaves
+    assert inside == {10, 20, 30, 40}
+    assert outside == {10}
+
+
 def test_sample_top_k_keeps_exactly_k_and_ties_go_to_lower_ids():
     v = 300
     logits = torch.zeros(1, v)
