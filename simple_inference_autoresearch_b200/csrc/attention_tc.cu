@@ -11,14 +11,18 @@
 // consecutive rows as two query tiles of 128 (the MMA's M) and walks the keys in tiles of 64 (one
 // cache page), so every K / V tile that arrives is used by two query tiles:
 //   TMA thread      Q once (a 3-D box: 64 dims x G heads x 128/G tokens lands as 128 packed rows),
-//                   then K and V of each key tile into a three-stage ring;
+//                   then K and V of each key tile into three-stage rings of their own (a K stage
+//                   is free as soon as the scores that read it are done, a V stage a step later);
 //   MMA thread      for each query tile S = Q K^T (8 MMAs of K = 16 over the two 64-dim halves),
 //                   one key tile ahead of the softmax (S is double-buffered in tensor memory), and,
 //                   once that tile's softmax threads have written P, O += P V (4 MMAs over 16 keys
-//                   each, V read as an MN-major operand: its 64-dim rows are the contiguous index);
+//                   each; P is the A operand read from tensor memory, V an MN-major operand in
+//                   shared memory: its 64-dim rows are the contiguous index);
 //   softmax threads (one group of 128 per query tile) read their row of S from tensor memory, mask,
-//                   exponentiate in the base-2 domain, write P (bf16) into shared memory in the
-//                   swizzled layout the MMA expects, and keep the row sum.  O stays in tensor memory;
+//                   exponentiate in the base-2 domain, write P (bf16 pairs) over the first 32
+//                   columns of the S they read (shared memory carries only Q, K and V: P through
+//                   shared memory cost a write and a read of 16 KiB per tile and step, measured 11%
+//                   of the kernel's time at 8,192 tokens), and keep the row sum.  O stays in tensor memory;
 //                   it is rescaled there only when a row's maximum has grown by more than 2^8 since
 //                   the last rescale (the final division uses the same reference maximum, so the
 //                   result is exact up to rounding), and read once at the end.
@@ -36,11 +40,10 @@ constexpr int kRows = 128;       // rows per query tile
 constexpr int kQTiles = 2;       // query tiles per block
 constexpr int kKeys = 64;        // keys per tile
 constexpr int kHd = 128;         // head_dim
-constexpr int kStages = 3;       // K / V ring
+constexpr int kStages = 3;       // K and V rings
 constexpr int kQBytes = kRows * kHd * 2;            // 32 KiB, two 64-dim halves of 16 KiB
 constexpr int kTileBytes = kKeys * kHd * 2;         // 16 KiB, two 64-dim halves of 8 KiB
-constexpr int kPBytes = kRows * kKeys * 2;          // 16 KiB
-constexpr int kSmemBytes = kQTiles * kQBytes + kStages * 2 * kTileBytes + kQTiles * 2 * kPBytes;
+constexpr int kSmemBytes = kQTiles * kQBytes + kStages * 2 * kTileBytes;
 constexpr uint32_t kTmemCols = 512;                 // S[q][buf]: 64 columns each from 0; O[q]: 128 each from 256
 constexpr float kRescaleGap = 8.f;                  // log2 of the growth that forces a rescale
 constexpr int kThreads = 128 + kQTiles * 128;   // TMA warp, one MMA warp per query tile, a spare, the softmax warps
@@ -78,7 +81,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t q_full;
   __shared__ __align__(8) uint64_t s_full[kQTiles][2], p_full[kQTiles][2], pv_full[kQTiles][2];
-  __shared__ __align__(8) uint64_t kv_full[kStages], kv_empty[kStages];
+  // keys and values have rings of their own: a key stage is free again as soon as the scores that
+  // read it are done, a value stage only after P.V, a step later, so each is asked for as early as it can be
+  __shared__ __align__(8) uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -114,7 +119,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   unsigned char* q_s = sm;                                   // [q tile][half][128 rows][64 dims]
   unsigned char* k_s = q_s + kQTiles * kQBytes;              // [stage][half][64 keys][64 dims]
   unsigned char* v_s = k_s + kStages * kTileBytes;
-  unsigned char* p_s = v_s + kStages * kTileBytes;           // [q tile][buffer][128 rows][64 keys]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -128,8 +132,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       mbar_init(&pv_full[g][1], 1);
     }
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], n_q);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], n_q);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], n_q);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -163,23 +169,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tma_load_3d(q_s + g * kQBytes + kQBytes / 2, &tmQ, &q_full, 64, kvh * G, tok);
       }
       const int* table = prm.block_table + (size_t)slot * prm.max_pages;
-      int issued = 0;
+      int issued_k = 0, issued_v = 0;
+      int page = table[0];                       // read one tile ahead of its use
       for (int i = 0; i < nt_max; ++i) {
         const int s = i % kStages;
-        if (!mbar_wait(&kv_empty[s], ((i / kStages) & 1) ^ 1) || SIAR_ABORTED()) { SIAR_FAIL(); break; }
+        const uint32_t ph = ((i / kStages) & 1) ^ 1;
         const int j0 = i * kKeys;
-        const int page = table[j0 / prm.page_tokens];
         const int row = (page * prm.Hkv + kvh) * prm.page_tokens + (j0 % prm.page_tokens);
-        mbar_expect_tx(&kv_full[s], 2 * kTileBytes);
-        tma_load_2d(k_s + s * kTileBytes, &tmK, &kv_full[s], 0, row);
-        tma_load_2d(k_s + s * kTileBytes + kTileBytes / 2, &tmK, &kv_full[s], 64, row);
-        tma_load_2d(v_s + s * kTileBytes, &tmV, &kv_full[s], 0, row);
-        tma_load_2d(v_s + s * kTileBytes + kTileBytes / 2, &tmV, &kv_full[s], 64, row);
-        issued = i + 1;
+        if (i + 1 < nt_max) page = table[(j0 + kKeys) / prm.page_tokens];
+        if (!mbar_wait(&k_empty[s], ph) || SIAR_ABORTED()) { SIAR_FAIL(); break; }
+        mbar_expect_tx(&k_full[s], kTileBytes);
+        tma_load_2d(k_s + s * kTileBytes, &tmK, &k_full[s], 0, row);
+        tma_load_2d(k_s + s * kTileBytes + kTileBytes / 2, &tmK, &k_full[s], 64, row);
+        issued_k = i + 1;
+        if (!mbar_wait(&v_empty[s], ph) || SIAR_ABORTED()) { SIAR_FAIL(); break; }
+        mbar_expect_tx(&v_full[s], kTileBytes);
+        tma_load_2d(v_s + s * kTileBytes, &tmV, &v_full[s], 0, row);
+        tma_load_2d(v_s + s * kTileBytes + kTileBytes / 2, &tmV, &v_full[s], 64, row);
+        issued_v = i + 1;
       }
       if (SIAR_ABORTED()) {    // let copies in flight land before the block leaves
         mbar_wait(&q_full, 0);
-        for (int i = max(0, issued - kStages); i < issued; ++i) mbar_wait(&kv_full[i % kStages], (i / kStages) & 1);
+        for (int i = max(0, issued_k - kStages); i < issued_k; ++i) mbar_wait(&k_full[i % kStages], (i / kStages) & 1);
+        for (int i = max(0, issued_v - kStages); i < issued_v; ++i) mbar_wait(&v_full[i % kStages], (i / kStages) & 1);
       }
     }
   } else if (warp == 1 || warp == 2) {
@@ -195,7 +207,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const uint32_t q_lo = (uint32_t)smem_desc_sw128(smem_u32(q_s + g * kQBytes));
       const uint32_t k_lo = (uint32_t)smem_desc_sw128(smem_u32(k_s));
       const uint32_t v_lo = (uint32_t)smem_desc_sw128_mn(smem_u32(v_s), kTileBytes / 2);
-      const uint32_t p_lo = (uint32_t)smem_desc_sw128(smem_u32(p_s + g * 2 * kPBytes));
       const uint32_t tmem_o = tmem_base + 256u + (uint32_t)(g * kHd);
       // S[g][i & 1] = Q_g K_i^T over the two 64-dim halves, 4 steps of 16 dims (32 bytes) in each
       auto issue_qk = [&](int i) {
@@ -206,30 +217,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           umma_f16_words(tmem_s, q_lo + (uint32_t)((kk / 4) * (kQBytes / 2 >> 4) + (kk % 4) * 2), hi_k,
                          ks + (uint32_t)((kk / 4) * (kTileBytes / 2 >> 4) + (kk % 4) * 2), hi_k, idesc_qk, kk > 0 ? 1u : 0u);
         umma_commit(&s_full[g][i & 1]);
+        umma_commit(&k_empty[i % kStages]);       // the key stage is free once these scores are done
       };
-      bool ok = mbar_wait(&q_full, 0) && mbar_wait(&kv_full[0], 0);
+      bool ok = mbar_wait(&q_full, 0) && mbar_wait(&k_full[0], 0);
       if (ok) {
         tc_fence_after();
         issue_qk(0);
       }
       for (int i = 0; i < nt_max && ok; ++i) {
         if (i + 1 < nt_max) {
-          if (!mbar_wait(&kv_full[(i + 1) % kStages], ((i + 1) / kStages) & 1) || SIAR_ABORTED()) { ok = false; break; }
+          if (!mbar_wait(&k_full[(i + 1) % kStages], ((i + 1) / kStages) & 1) || SIAR_ABORTED()) { ok = false; break; }
           tc_fence_after();
           issue_qk(i + 1);
         }
-        if (!mbar_wait(&p_full[g][i & 1], (i >> 1) & 1) || SIAR_ABORTED()) { ok = false; break; }
+        if (!mbar_wait(&p_full[g][i & 1], (i >> 1) & 1) || !mbar_wait(&v_full[i % kStages], (i / kStages) & 1) ||
+            SIAR_ABORTED()) { ok = false; break; }
         tc_fence_after();
         // O_g += P_g V_i: 4 steps of 16 keys; V rows (keys) are 128 bytes of one dim half,
         // 8-row groups 1024 bytes apart, the two dim halves 8 KiB apart
-        const uint32_t ps = p_lo + (uint32_t)((i & 1) * (kPBytes >> 4));
+        // P_i sits in tensor memory, in the first 32 columns of the scores it was made from
+        const uint32_t tmem_p = tmem_base + (uint32_t)((g * 2 + (i & 1)) * kKeys);
         const uint32_t vs = v_lo + (uint32_t)((i % kStages) * (kTileBytes >> 4));
 #pragma unroll
         for (int t = 0; t < kKeys / kUmmaK; ++t)
-          umma_f16_words(tmem_o, ps + (uint32_t)(t * 2), hi_k, vs + (uint32_t)(t * (2048 >> 4)), hi_v, idesc_pv,
-                         (i > 0 || t > 0) ? 1u : 0u);
+          umma_f16_tmem_a(tmem_o, tmem_p + (uint32_t)(t * 8), vs + (uint32_t)(t * (2048 >> 4)), hi_v, idesc_pv,
+                          (i > 0 || t > 0) ? 1u : 0u);
         umma_commit(&pv_full[g][i & 1]);
-        umma_commit(&kv_empty[i % kStages]);
+        umma_commit(&v_empty[i % kStages]);
       }
       if (!ok) SIAR_FAIL();
     }
@@ -244,7 +258,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int kv_end = row < rows_q[g] ? base + rg / G + 1 : 0;
     const float sl2 = prm.scale * 1.4426950408889634f;
     const int n_tiles = nt[g];
-    unsigned char* prow0 = p_s + g * 2 * kPBytes + row * 128;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
@@ -292,27 +305,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       if (need) m_used = m_new;
       const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-      // P's buffer is free once the P.V of two tiles ago has completed
-      if (i >= 2) {
-        if (!mbar_wait(&pv_full[g][i & 1], ((i - 2) >> 1) & 1) || SIAR_ABORTED()) { ok = false; break; }
-      }
-      // P = 2^(s c - m) as bf16, written as this row's 128 bytes with the 16-byte pieces swizzled
-      unsigned char* prow = prow0 + (i & 1) * kPBytes;
+      // P = 2^(s c - m) as bf16 pairs, written over the first 32 columns of the scores in tensor
+      // memory (this thread holds its whole row in registers by now).  The next scores for this
+      // buffer are issued after the P.V that reads P, and the tensor pipe keeps that order.
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pw[32];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float p0 = ex2(fmaf(__uint_as_float(sr[c * 8 + 2 * e]), sl2, neg_m));
           const float p1 = ex2(fmaf(__uint_as_float(sr[c * 8 + 2 * e + 1]), sl2, neg_m));
           sum[e] += p0 + p1;
-          pk[e] = pack_bf16x2(p0, p1);
+          pw[c * 4 + e] = pack_bf16x2(p0, p1);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
+      SIAR_TMEM_ST_32(tmem_s, pw);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-      fence_async_smem();
       tc_fence_before();
       if (g == 0)
         asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -86,6 +86,18 @@ __device__ __forceinline__ void umma_f16_words(uint32_t tmem_d, uint32_t a_lo, u
       ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D (+)= A B with A in tensor memory (row m of A on lane m, the K index along the columns, two
+// bfloat16 to a 32-bit column: 8 columns per step of 16) and B in shared memory.
+__device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // ---- two SMs on one tile (cta_group::2).  The two blocks of a cluster of two each hold half of
 // the tile's A rows and half of its B rows at the same shared-memory offsets; the even block issues
 // the MMAs, which read both blocks' shared memory and write both blocks' tensor memory.
