@@ -144,11 +144,11 @@ def make_cache(n_kv, d, dtype, device, max_tokens=8192, max_slots=12, max_seq_le
 
 
 def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None, qk_scale=1.0,
-                       window=None):
+                       window=None, cache_size=None):
     """Fills two caches (GPU kernel / CPU restatement) with the same history through
     rope_kv_write, then compares rope + attention of a last step."""
     torch.manual_seed(seed)
-    caches = {dev: make_cache(hkv, d, dtype, dev, window=window) for dev in ("cpu", DEV)}
+    caches = {dev: make_cache(hkv, d, dtype, dev, window=window, **(cache_size or {})) for dev in ("cpu", DEV)}
     kw = {} if window is None else {"window": window}
     backends = {"cpu": emu, DEV: ops}
     inv_freq = plain_llama.rope_inv_freq(d, theta, None)
@@ -653,6 +653,26 @@ def test_tc_attention_long_prompt_and_far_key():
     outs = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[900, 0], q_lens=[300, 1100], boost=(0, 200, 8.0))
     v_row = rnd(900, (hq + 2 * hkv) * d, dtype=torch.bfloat16, seed=10)[200, (hq + hkv) * d:(hq + hkv + 1) * d].float()
     torch.testing.assert_close(outs[DEV][0][299, :d], v_row, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_decode_over_tens_of_thousands_of_keys(dtype):
+    """Many chunks per sequence in the decode kernels (the cap on chunks, the join over dozens of
+    partials), beside short sequences in the same batch; the key that matters is the fourth of 20,000."""
+    hq, hkv, d = 8, 2, 128
+    outs = run_attention_case(dtype, hq, hkv, d, lens_before=[20000, 9000, 70], q_lens=[1, 1, 1], boost=(0, 3, 8.0),
+                              cache_size=dict(max_tokens=32768, max_seq_len=20480))
+    v_row = rnd(20000, (hq + 2 * hkv) * d, dtype=dtype, seed=10)[3, (hq + hkv) * d:(hq + hkv + 1) * d].float()
+    torch.testing.assert_close(outs[DEV][0][0, :d], v_row, rtol=5e-2, atol=5e-2)
+
+
+def test_tc_attention_prompt_of_thousands_of_tokens():
+    """Ninety-odd key tiles for the last rows (the barriers' phases turn over dozens of times)."""
+    hq, hkv, d = 2, 1, 128
+    outs = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[100], q_lens=[6000], boost=(0, 10, 8.0),
+                              cache_size=dict(max_tokens=8192, max_seq_len=6144))
+    v_row = rnd(100, (hq + 2 * hkv) * d, dtype=torch.bfloat16, seed=10)[10, (hq + hkv) * d:(hq + hkv + 1) * d].float()
+    torch.testing.assert_close(outs[DEV][0][5999, :d], v_row, rtol=5e-2, atol=5e-2)
 
 
 def test_tc_attention_large_scores_rescale():
