@@ -92,6 +92,7 @@ class ClockSampler:
 
 
 def main() -> int:
+    global PROMPT_TOKENS, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -100,6 +101,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS,
+                    help="tokens of every prompt, also of the timed prefill (other context lengths than the default run's)")
+    ap.add_argument("--context", type=int, default=0,
+                    help="cache tokens per sequence (default: 4,096, or the prompt and the decoded tokens rounded up to 1,024)")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels in plain stream order (no programmatic dependent launch)")
     ap.add_argument("--cuda-profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                     help="bracket the timed decode replays (or the timed prefill steps) with cudaProfilerStart/Stop, "
@@ -116,6 +121,12 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    PROMPT_TOKENS = args.prompt_tokens
+    need = PROMPT_TOKENS + args.warmup + args.steps + 64
+    CONTEXT = args.context or max(CONTEXT, (need + 1023) // 1024 * 1024)
+    if CONTEXT < need:
+        print(f"bench.py: --context {CONTEXT} holds no prompt of {PROMPT_TOKENS} tokens plus {args.warmup + args.steps} steps")
+        return 2
 
     import dataclasses
 
@@ -136,12 +147,17 @@ def main() -> int:
 
     loaded = siar.init_random(siar.build_model(cfg, torch.bfloat16, dev), seed=0)
     model = loaded.model
+    kv_token_bytes = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * (cfg.head_dim or cfg.hidden_size // cfg.num_attention_heads) * 2
+    if not args.no_points and 64 * CONTEXT * kv_token_bytes > 100e9:
+        print(f"bench.py: the batch 1 / 64 points are left out: 64 sequences of {CONTEXT:,} tokens would hold "
+              f"{64 * CONTEXT * kv_token_bytes / 1e9:.0f} GB of keys and values", file=sys.stderr)
+        args.no_points = True
     max_b = max(args.batch, 1 if args.no_points else 64)
     engine = siar.Engine(model, max_batch=max_b, max_seq_len=CONTEXT, use_cuda_graph=True)
     gen = torch.Generator().manual_seed(0)
     rand_tokens = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()  # noqa: E731
 
-    # ---------------------------------------------------------------- prefill, one prompt of 2,048 tokens
+    # ---------------------------------------------------------------- prefill, one prompt
     def prefill_once():
         s = engine.open()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -261,7 +277,8 @@ def main() -> int:
 
     achieved = head["bytes"] / (head["ms"] * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s @ batch 8 (Llama-3.1-8B shape, bf16, 2,048-token prompts, 4,096-token cache)",
+        "metric": f"decode tok/s @ batch {args.batch} (Llama-3.1-8B shape, bf16, {PROMPT_TOKENS:,}-token prompts, "
+                  f"{CONTEXT:,}-token cache)",
         "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
