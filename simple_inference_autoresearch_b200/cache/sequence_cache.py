@@ -283,12 +283,13 @@ class SequenceCache:
     def _upload_cells(self, g: "KVGroup", cells) -> None:
         if not cells:
             return
-        idx = torch.tensor([[c[0], c[1]] for c in cells], dtype=torch.int64)
-        val = torch.tensor([c[2] for c in cells], dtype=torch.int32)
         if torch.device(self.device).type == "cuda":
-            idx = idx.pin_memory().to(self.device, non_blocking=True)
-            val = val.pin_memory().to(self.device, non_blocking=True)
-        g.block_table[idx[:, 0], idx[:, 1]] = val
+            from ..kernels import ops
+            triples = torch.tensor([[c[0], c[1], c[2]] for c in cells], dtype=torch.int32)
+            ops.set_table_cells(g.block_table, triples.pin_memory().to(self.device, non_blocking=True))
+            return
+        idx = torch.tensor([[c[0], c[1]] for c in cells], dtype=torch.int64)
+        g.block_table[idx[:, 0], idx[:, 1]] = torch.tensor([c[2] for c in cells], dtype=torch.int32)
 
     def commit(self, slots: Sequence[int], new_tokens: Sequence[int]) -> None:
         """The step ran: lengths advance, and groups that keep a window of keys give back the

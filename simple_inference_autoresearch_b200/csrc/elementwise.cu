@@ -409,6 +409,18 @@ __global__ void advance_lengths_kernel(int* __restrict__ base_len, const int* __
   if (b < B) base_len[b] += q_start[b + 1] - q_start[b];
 }
 
+// table[row][col] = value for n (row, col, value) triples: the pages a step gave to or took from
+// sequences, written into the block table of a group of layers.
+__global__ void set_table_cells_kernel(int* __restrict__ table, const int* __restrict__ cells, int n, int rows,
+                                       int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int r = cells[3 * i], c = cells[3 * i + 1];
+  if (r >= 0 && r < rows && c >= 0 && c < cols) table[(size_t)r * cols + c] = cells[3 * i + 2];
+}
+
 }  // namespace siar
 
 using namespace siar;
@@ -517,6 +529,12 @@ extern "C" int siar_swiglu(int is_bf16, const void* gu, void* out, int N, int I,
     launch_kernel(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, interleaved);
   else
     launch_kernel(swiglu_kernel<float>, grid, 256, 0, s, (const float*)gu, (float*)out, I, interleaved);
+  LAUNCH_END();
+}
+
+extern "C" int siar_set_table_cells(int* table, const int* cells, int n, int rows, int cols, void* stream) {
+  if (n == 0) return 0;
+  launch_kernel(set_table_cells_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, table, cells, n, rows, cols);
   LAUNCH_END();
 }
 

@@ -34,6 +34,7 @@ _signatures = {
                                c_void_p, c_void_p],
         "siar_swiglu": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "siar_advance_lengths": [c_void_p, c_void_p, c_int, c_void_p],
+        "siar_set_table_cells": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "gemm_simt": {
         "siar_gemm_nt_simt": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -486,6 +487,15 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
 def advance_lengths(base_len: torch.Tensor, q_start: torch.Tensor, n_seqs: int) -> None:
     _need_cuda(base_len, q_start)
     _launch("elementwise", "siar_advance_lengths", _ptr(base_len), _ptr(q_start), n_seqs, _stream())
+
+
+def set_table_cells(table: torch.Tensor, cells: torch.Tensor) -> None:
+    """``table[r, c] = v`` for every (r, c, v) row of the int32 tensor ``cells`` [n, 3] (both on the GPU)."""
+    _need_cuda(table, cells)
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    assert cells.dtype == torch.int32 and cells.dim() == 2 and cells.shape[1] == 3 and cells.is_contiguous()
+    _launch("elementwise", "siar_set_table_cells", _ptr(table), _ptr(cells), cells.shape[0], table.shape[0],
+            table.shape[1], _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

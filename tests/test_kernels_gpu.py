@@ -48,6 +48,22 @@ def test_embed_flags_bad_token(dtype):
     assert torch.equal(out[0].cpu(), table[3].float().cpu()) and not out[1:].any()
 
 
+def test_set_table_cells():
+    table = torch.full((7, 40), -1, dtype=torch.int32, device=DEV)
+    cells = torch.tensor([[0, 0, 5], [6, 39, 17], [3, 12, 0], [3, 13, -1]], dtype=torch.int32)
+    ops.set_table_cells(table, cells.to(DEV))
+    want = torch.full((7, 40), -1, dtype=torch.int32)
+    for r, c, v in cells.tolist():
+        want[r, c] = v
+    assert torch.equal(table.cpu(), want)
+    n = torch.arange(280)                        # every cell once, more than one block of threads
+    big = torch.stack([n % 7, n // 7, n + 100], 1).to(torch.int32)
+    ops.set_table_cells(table, big.to(DEV))
+    for r, c, v in big.tolist():
+        want[r, c] = v
+    assert torch.equal(table.cpu(), want)
+
+
 def test_gather_rows():
     src = rnd(9, 331)
     rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32)
