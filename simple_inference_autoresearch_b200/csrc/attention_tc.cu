@@ -1,16 +1,18 @@
 // Causal grouped-query attention for prompts (any mix of new-token counts per sequence) on the
 // 5th-generation tensor cores: S = Q K^T and O += P V are tcgen05.mma instructions with S and O in
 // tensor memory, Q / K / V tiles come by TMA (K and V straight from the pages of the cache), and
-// the softmax runs on 256 threads, each owning one row.  bfloat16, head_dim 128, a group size G
-// that divides 128; other sizes use the warp-level kernel of attention_mma.cu.  The rules are those
+// the softmax runs on 256 threads, each owning one row.  bfloat16, head_dim 64 or 128, up to 128
+// query heads per kv head; other sizes use the warp-level kernel of attention_mma.cu.  The rules are those
 // of attention.cu (bottom-right causal, scale after the dot, running maximum, division at the end),
 // cited there; as in the reference's flash kernel P is rounded to bfloat16 before P.V
 // (kernels/attention_kernel.py:221).
 //
-// Rows of one (sequence, kv head) are (query position, head in group) pairs; a block takes 256
-// consecutive rows as two query tiles of 128 (the MMA's M) and walks the keys in tiles of 64 (one
-// cache page), so every K / V tile that arrives is used by two query tiles:
-//   TMA thread      Q once (a 3-D box: 64 dims x G heads x 128/G tokens lands as 128 packed rows),
+// Rows of one (sequence, kv head) are (query position, head in group) pairs; a block takes two
+// query tiles of 128 rows (the MMA's M), each holding floor(128 / G) whole tokens (a group size
+// that does not divide 128 leaves the tile's last rows unused: they are masked like the rows past
+// the end of a prompt), and walks the keys in tiles of 64 (one cache page), so every K / V tile
+// that arrives is used by two query tiles:
+//   TMA thread      Q once (a 3-D box: 64 dims x G heads x floor(128/G) tokens lands as packed rows),
 //                   then K and V of each key tile into three-stage rings of their own (a K stage
 //                   is free as soon as the scores that read it are done, a V stage a step later);
 //   MMA thread      for each query tile S = Q K^T (8 MMAs of K = 16 over the two 64-dim halves),
@@ -26,7 +28,7 @@
 //                   it is rescaled there only when a row's maximum has grown by more than 2^8 since
 //                   the last rescale (the final division uses the same reference maximum, so the
 //                   result is exact up to rounding), and read once at the end.
-// Tensor memory: 2 x 2 x 64 columns of S and 2 x 128 columns of O = 512 columns, one block per SM.
+// Tensor memory: 2 x 2 x 64 columns of S and 2 x head_dim columns of O (512 columns allocated), one block per SM.
 // Every mbarrier wait is bounded and reports through the status word.
 #include "tcgen05.cuh"
 
@@ -39,11 +41,8 @@ namespace siar {
 constexpr int kRows = 128;       // rows per query tile
 constexpr int kQTiles = 2;       // query tiles per block
 constexpr int kKeys = 64;        // keys per tile
-constexpr int kHd = 128;         // head_dim
 constexpr int kStages = 3;       // K and V rings
-constexpr int kQBytes = kRows * kHd * 2;            // 32 KiB, two 64-dim halves of 16 KiB
-constexpr int kTileBytes = kKeys * kHd * 2;         // 16 KiB, two 64-dim halves of 8 KiB
-constexpr int kSmemBytes = kQTiles * kQBytes + kStages * 2 * kTileBytes;
+constexpr int smem_bytes(int hd) { return kQTiles * kRows * hd * 2 + kStages * 2 * kKeys * hd * 2; }
 constexpr uint32_t kTmemCols = 512;                 // S[q][buf]: 64 columns each from 0; O[q]: 128 each from 256
 constexpr float kRescaleGap = 8.f;                  // log2 of the growth that forces a rescale
 constexpr int kThreads = 128 + kQTiles * 128;   // TMA warp, one MMA warp per query tile, a spare, the softmax warps
@@ -75,6 +74,7 @@ __device__ __forceinline__ float ex2(float x) {
       "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)                           \
       : "memory")
 
+template <int kHd>
 __global__ void __launch_bounds__(kThreads)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const AttnTcParams prm) {
@@ -87,14 +87,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  constexpr int kHalves = kHd / 64;                  // 64-dim (128-byte) column blocks of a row
+  constexpr int kQBytes = kRows * kHd * 2;           // 16 KiB per half
+  constexpr int kTileBytes = kKeys * kHd * 2;        // 8 KiB per half
   pdl_launch_dependents();
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = prm.Hq / prm.Hkv;
+  const int tile_rows = (kRows / G) * G;             // rows of a query tile in use: whole tokens only
   const int t0 = prm.q_start[b];                 // batch description: written by no kernel of this step
   const int q_len = prm.q_start[b + 1] - t0;
   const int rows_total = q_len * G;
   // blocks with the most keys (the last rows) start first: the tail of the grid is made of short blocks
-  const int row0 = (gridDim.x - 1 - blockIdx.x) * (kQTiles * kRows);
+  const int row0 = (gridDim.x - 1 - blockIdx.x) * (kQTiles * tile_rows);
   if (row0 >= rows_total) return;
   const int base = prm.base_len[b];
   const int slot = prm.slot_ids[b];
@@ -103,8 +107,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   int n_q = 0;
 #pragma unroll
   for (int g = 0; g < kQTiles; ++g) {
-    rows_q[g] = max(0, min(kRows, rows_total - row0 - g * kRows));
-    nt[g] = rows_q[g] > 0 ? (base + (row0 + g * kRows + rows_q[g] - 1) / G + 1 + kKeys - 1) / kKeys : 0;
+    rows_q[g] = max(0, min(tile_rows, rows_total - row0 - g * tile_rows));
+    nt[g] = rows_q[g] > 0 ? (base + (row0 + g * tile_rows + rows_q[g] - 1) / G + 1 + kKeys - 1) / kKeys : 0;
     if (rows_q[g] > 0) n_q = g + 1;
   }
   // Both query tiles walk all the key tiles of the block (the first tile's last one may be masked
@@ -162,11 +166,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmK) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmV) : "memory");
-      mbar_expect_tx(&q_full, n_q * kQBytes);
+      mbar_expect_tx(&q_full, n_q * tile_rows * kHd * 2);      // a box is tile_rows packed rows (the rest of the tile stays as it was: masked rows)
       for (int g = 0; g < n_q; ++g) {
-        const int tok = t0 + (row0 + g * kRows) / G;
-        tma_load_3d(q_s + g * kQBytes, &tmQ, &q_full, 0, kvh * G, tok);
-        tma_load_3d(q_s + g * kQBytes + kQBytes / 2, &tmQ, &q_full, 64, kvh * G, tok);
+        const int tok = t0 + (row0 + g * tile_rows) / G;
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_3d(q_s + g * kQBytes + h * (kQBytes / kHalves), &tmQ, &q_full, 64 * h, kvh * G, tok);
       }
       const int* table = prm.block_table + (size_t)slot * prm.max_pages;
       int issued_k = 0, issued_v = 0;
@@ -179,13 +184,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (i + 1 < nt_max) page = table[(j0 + kKeys) / prm.page_tokens];
         if (!mbar_wait(&k_empty[s], ph) || SIAR_ABORTED()) { SIAR_FAIL(); break; }
         mbar_expect_tx(&k_full[s], kTileBytes);
-        tma_load_2d(k_s + s * kTileBytes, &tmK, &k_full[s], 0, row);
-        tma_load_2d(k_s + s * kTileBytes + kTileBytes / 2, &tmK, &k_full[s], 64, row);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_2d(k_s + s * kTileBytes + h * (kTileBytes / kHalves), &tmK, &k_full[s], 64 * h, row);
         issued_k = i + 1;
         if (!mbar_wait(&v_empty[s], ph) || SIAR_ABORTED()) { SIAR_FAIL(); break; }
         mbar_expect_tx(&v_full[s], kTileBytes);
-        tma_load_2d(v_s + s * kTileBytes, &tmV, &v_full[s], 0, row);
-        tma_load_2d(v_s + s * kTileBytes + kTileBytes / 2, &tmV, &v_full[s], 64, row);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_2d(v_s + s * kTileBytes + h * (kTileBytes / kHalves), &tmV, &v_full[s], 64 * h, row);
         issued_v = i + 1;
       }
       if (SIAR_ABORTED()) {    // let copies in flight land before the block leaves
@@ -203,10 +210,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       constexpr uint32_t idesc_pv = instr_desc_bf16(kHd, true);
       // descriptors differ in their low word only (the address field, in units of 16 bytes)
       const uint32_t hi_k = (uint32_t)(smem_desc_sw128(0) >> 32);
-      const uint32_t hi_v = (uint32_t)(smem_desc_sw128_mn(0, kTileBytes / 2) >> 32);
+      const uint32_t hi_v = (uint32_t)(smem_desc_sw128_mn(0, kTileBytes / kHalves) >> 32);
       const uint32_t q_lo = (uint32_t)smem_desc_sw128(smem_u32(q_s + g * kQBytes));
       const uint32_t k_lo = (uint32_t)smem_desc_sw128(smem_u32(k_s));
-      const uint32_t v_lo = (uint32_t)smem_desc_sw128_mn(smem_u32(v_s), kTileBytes / 2);
+      const uint32_t v_lo = (uint32_t)smem_desc_sw128_mn(smem_u32(v_s), kTileBytes / kHalves);
       const uint32_t tmem_o = tmem_base + 256u + (uint32_t)(g * kHd);
       // S[g][i & 1] = Q_g K_i^T over the two 64-dim halves, 4 steps of 16 dims (32 bytes) in each
       auto issue_qk = [&](int i) {
@@ -214,8 +221,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const uint32_t tmem_s = tmem_base + (uint32_t)((g * 2 + (i & 1)) * kKeys);
 #pragma unroll
         for (int kk = 0; kk < kHd / kUmmaK; ++kk)
-          umma_f16_words(tmem_s, q_lo + (uint32_t)((kk / 4) * (kQBytes / 2 >> 4) + (kk % 4) * 2), hi_k,
-                         ks + (uint32_t)((kk / 4) * (kTileBytes / 2 >> 4) + (kk % 4) * 2), hi_k, idesc_qk, kk > 0 ? 1u : 0u);
+          umma_f16_words(tmem_s, q_lo + (uint32_t)((kk / 4) * (kQBytes / kHalves >> 4) + (kk % 4) * 2), hi_k,
+                         ks + (uint32_t)((kk / 4) * (kTileBytes / kHalves >> 4) + (kk % 4) * 2), hi_k, idesc_qk, kk > 0 ? 1u : 0u);
         umma_commit(&s_full[g][i & 1]);
         umma_commit(&k_empty[i % kStages]);       // the key stage is free once these scores are done
       };
@@ -254,7 +261,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int row = quad * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const uint32_t tmem_o = tmem_base + 256u + (uint32_t)(g * kHd) + lane_base;
-    const int rg = row0 + g * kRows + row;
+    const int rg = row0 + g * tile_rows + row;
     const int kv_end = row < rows_q[g] ? base + rg / G + 1 : 0;
     const float sl2 = prm.scale * 1.4426950408889634f;
     const int n_tiles = nt[g];
@@ -370,18 +377,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 struct PoolKey {
   const void* ptr;
   long long rows;
-  bool operator==(const PoolKey& o) const { return ptr == o.ptr && rows == o.rows; }
+  int hd;
+  bool operator==(const PoolKey& o) const { return ptr == o.ptr && rows == o.rows && hd == o.hd; }
 };
 struct PoolKeyHash {
-  size_t operator()(const PoolKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows; }
+  size_t operator()(const PoolKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows ^ ((size_t)k.hd << 48); }
 };
 
-// The pool of one cache entry as a [rows, 128] matrix seen in boxes of 64 rows x 64 dims.
-static bool pool_map(const void* ptr, long long rows, CUtensorMap* out) {
+// The pool of one cache entry as a [rows, head_dim] matrix seen in boxes of 64 rows x 64 dims.
+static bool pool_map(const void* ptr, long long rows, int kHd, CUtensorMap* out) {
   static std::unordered_map<PoolKey, CUtensorMap, PoolKeyHash> cache;
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
-  PoolKey key{ptr, rows};
+  PoolKey key{ptr, rows, kHd};
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return true; }
   EncodeTiledFn fn = encode_fn();
@@ -399,9 +407,10 @@ static bool pool_map(const void* ptr, long long rows, CUtensorMap* out) {
   return true;
 }
 
-// The query part of the fused qkv rows as [tokens, Hq heads, 128 dims], seen in boxes of
-// 128/G tokens x G heads x 64 dims: one box is 128 packed rows of a kv head's group.
-static bool query_map(const void* qkv, int n_tokens, int Hq, int Hkv, CUtensorMap* out) {
+// The query part of the fused qkv rows as [tokens, Hq heads, head_dim], seen in boxes of
+// floor(128/G) tokens x G heads x 64 dims: one box is the packed rows of a kv head's group that a
+// query tile uses (all 128 when G divides 128).
+static bool query_map(const void* qkv, int n_tokens, int Hq, int Hkv, int kHd, CUtensorMap* out) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const int G = Hq / Hkv;
@@ -420,16 +429,29 @@ using namespace siar;
 
 SIAR_DEFINE_PDL_SWITCH()
 
-// 1 when this unit takes the sizes: head_dim 128, a group size that divides 128, pages of 64 tokens
-// (or a multiple), at most 256 tokens' worth of heads in a TMA box.
+// 1 when this unit takes the sizes: head_dim 64 or 128, at most 128 query heads per kv head, pages
+// of 64 tokens (or a multiple).
 extern "C" int siar_attn_tc_supported(int Hq, int Hkv, int D, int page_tokens) {
   if (Hkv <= 0 || Hq % Hkv != 0) return 0;
   const int G = Hq / Hkv;
-  return D == kHd && G <= 128 && kRows % G == 0 && page_tokens % kKeys == 0;
+  return (D == 64 || D == 128) && G <= 128 && page_tokens % kKeys == 0;
 }
 
-// qkv [N, (Hq + 2 Hkv) * 128] bf16 with q already rotated and the new keys and values already in
-// the cache; k_pool / v_pool [n_pages, Hkv, page_tokens, 128]; out [N, Hq * 128] bf16.
+template <int HD>
+static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnTcParams& prm,
+                          dim3 grid, cudaStream_t s) {
+  constexpr size_t smem = smem_bytes(HD) + 1024;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  return (int)launch_kernel(attn_prefill_tc_kernel<HD>, grid, dim3(kThreads), smem, s, tmQ, tmK, tmV, prm);
+}
+
+// qkv [N, (Hq + 2 Hkv) * D] bf16 with q already rotated and the new keys and values already in
+// the cache; k_pool / v_pool [n_pages, Hkv, page_tokens, D]; out [N, Hq * D] bf16.
 extern "C" int siar_attn_tc_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                                     const int* slot_ids, const int* q_start, const int* base_len, void* out, int N,
                                     int B, int Hq, int Hkv, int D, int page_tokens, int max_pages, int n_pages,
@@ -439,7 +461,7 @@ extern "C" int siar_attn_tc_prefill(const void* qkv, const void* k_pool, const v
   if (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return (int)cudaErrorInvalidValue;
   CUtensorMap tmQ, tmK, tmV;
   const long long rows = (long long)n_pages * Hkv * page_tokens;
-  if (!query_map(qkv, N, Hq, Hkv, &tmQ) || !pool_map(k_pool, rows, &tmK) || !pool_map(v_pool, rows, &tmV))
+  if (!query_map(qkv, N, Hq, Hkv, D, &tmQ) || !pool_map(k_pool, rows, D, &tmK) || !pool_map(v_pool, rows, D, &tmV))
     return (int)cudaErrorInvalidValue;
   AttnTcParams prm;
   prm.out = (__nv_bfloat16*)out;
@@ -450,14 +472,9 @@ extern "C" int siar_attn_tc_prefill(const void* qkv, const void* k_pool, const v
   prm.status = status;
   prm.Hq = Hq; prm.Hkv = Hkv; prm.page_tokens = page_tokens; prm.max_pages = max_pages;
   prm.scale = scale;
-  const size_t smem = kSmemBytes + 1024;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    attr = true;
-  }
   const int G = Hq / Hkv;
-  dim3 grid((max_q_len * G + kQTiles * kRows - 1) / (kQTiles * kRows), Hkv, B);
-  return (int)launch_kernel(attn_prefill_tc_kernel, grid, dim3(kThreads), smem, (cudaStream_t)stream, tmQ, tmK, tmV, prm);
+  const int tile_rows = (kRows / G) * G;
+  dim3 grid((max_q_len * G + kQTiles * tile_rows - 1) / (kQTiles * tile_rows), Hkv, B);
+  return D == 64 ? launch_prefill<64>(tmQ, tmK, tmV, prm, grid, (cudaStream_t)stream)
+                 : launch_prefill<128>(tmQ, tmK, tmV, prm, grid, (cudaStream_t)stream);
 }

@@ -271,11 +271,11 @@ use_tc_attention = True
 
 
 def tc_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
-    """True when the tcgen05 kernel for prompts takes these sizes (bfloat16, head_dim 128, a
-    group size that divides 128, pages of 64 tokens or a multiple)."""
+    """True when the tcgen05 kernel for prompts takes these sizes (bfloat16, head_dim 64 or 128, at
+    most 128 query heads per kv head, pages of 64 tokens or a multiple)."""
     if dtype != torch.bfloat16 or not (use_tc_attention and use_mma_attention):
         return False
-    if head_dim != 128 or n_kv_heads <= 0 or n_heads % n_kv_heads:      # the unit is not even compiled for these
+    if head_dim not in (64, 128) or n_kv_heads <= 0 or n_heads % n_kv_heads:      # the unit is not even compiled for these
         return False
     return bool(_fn("attention_tc", "siar_attn_tc_supported")(n_heads, n_kv_heads, head_dim, page_tokens))
 

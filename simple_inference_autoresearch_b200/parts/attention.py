@@ -63,7 +63,7 @@ class GroupedQueryAttention(Mixer):
 
     def extension_units(self):
         units = ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
-        if self.head_dim == 128 and 128 % (self.n_heads // self.n_kv_heads) == 0:
+        if self.head_dim in (64, 128) and self.n_heads // self.n_kv_heads <= 128:
             units += ("attention_tc",)        # prompts of bfloat16 models with these sizes
         return units
 

@@ -656,12 +656,21 @@ def test_mma_attention_far_key_and_rows_do_not_depend_on_batch():
 
 
 # ----------------------------------------------------------------------------- tcgen05 attention for prompts
-@pytest.mark.parametrize("hq,hkv", [(8, 2), (4, 4), (32, 8), (16, 1), (2, 1), (64, 2)])
-def test_tc_attention_prefill_groups_and_lengths(hq, hkv):
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (4, 4), (32, 8), (16, 1), (2, 1), (64, 2), (6, 2), (24, 8), (5, 1), (7, 7)])
+def test_tc_attention_prefill_groups_and_lengths(hq, hkv, d):
     """Query tiles that are full, half empty and absent; prompts that start at 0 and that continue a
-    cache whose length is no multiple of the key tile; one token among prompts."""
-    assert ops.tc_attention_takes(torch.bfloat16, hq, hkv, 128, 64)
-    run_attention_case(torch.bfloat16, hq, hkv, 128, lens_before=[0, 0, 300, 63, 64], q_lens=[1, 200, 150, 66, 129])
+    cache whose length is no multiple of the key tile; one token among prompts.  Groups of 3 and 5
+    heads leave the last rows of a 128-row tile unused (42 tokens x 3, 25 x 5)."""
+    assert ops.tc_attention_takes(torch.bfloat16, hq, hkv, d, 64)
+    run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0, 300, 63, 64], q_lens=[1, 200, 150, 66, 129])
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(24, 8, 128), (32, 8, 64)])
+def test_tc_attention_far_key_at_the_sizes_of_the_smaller_models(hq, hkv, d):
+    outs = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[900, 0], q_lens=[300, 1100], boost=(0, 200, 8.0))
+    v_row = rnd(900, (hq + 2 * hkv) * d, dtype=torch.bfloat16, seed=10)[200, (hq + hkv) * d:(hq + hkv + 1) * d].float()
+    torch.testing.assert_close(outs[DEV][0][299, :d], v_row, rtol=5e-2, atol=5e-2)
 
 
 def test_tc_attention_long_prompt_and_far_key():
@@ -717,8 +726,9 @@ def test_tc_and_mma_attention_agree_and_rows_do_not_depend_on_batch():
 
 def test_tc_attention_is_refused_where_it_does_not_apply():
     assert not ops.tc_attention_takes(torch.float32, 8, 2, 128, 64)
-    assert not ops.tc_attention_takes(torch.bfloat16, 8, 2, 64, 64)        # head_dim other than 128
-    assert not ops.tc_attention_takes(torch.bfloat16, 6, 2, 128, 64)       # a group of 3 does not divide 128
+    assert not ops.tc_attention_takes(torch.bfloat16, 8, 2, 32, 64)        # head_dim other than 64 and 128
+    assert not ops.tc_attention_takes(torch.bfloat16, 8, 2, 96, 64)
+    assert not ops.tc_attention_takes(torch.bfloat16, 7, 2, 128, 64)       # heads that do not fall into equal groups
     assert not ops.tc_attention_takes(torch.bfloat16, 8, 2, 128, 32)       # pages smaller than a key tile
 
 
