@@ -101,6 +101,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--model", default="llama-3.1-8b", choices=["llama-3.1-8b", "llama-3.2-1b", "llama-3.2-3b"],
+                    help="the preset whose layer sizes run (the default run's is llama-3.1-8b)")
     ap.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS,
                     help="tokens of every prompt, also of the timed prefill (other context lengths than the default run's)")
     ap.add_argument("--context", type=int, default=0,
@@ -139,7 +141,7 @@ def main() -> int:
 
     if args.no_pdl:
         ops.set_programmatic_launch(False)
-    full = LlamaConfig.from_json(preset_path("llama-3.1-8b"))
+    full = LlamaConfig.from_json(preset_path(args.model))
     cfg = dataclasses.replace(full, num_hidden_layers=args.layers) if args.layers else full
     pk, pk_src = peaks()
     dev = torch.device("cuda:0")
@@ -277,14 +279,14 @@ def main() -> int:
 
     achieved = head["bytes"] / (head["ms"] * 1e-3) / 1e9
     line = {
-        "metric": f"decode tok/s @ batch {args.batch} (Llama-3.1-8B shape, bf16, {PROMPT_TOKENS:,}-token prompts, "
+        "metric": f"decode tok/s @ batch {args.batch} ({args.model.replace('llama', 'Llama').upper().replace('LLAMA', 'Llama')} shape, bf16, {PROMPT_TOKENS:,}-token prompts, "
                   f"{CONTEXT:,}-token cache)",
         "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
         "impl": "ours",
         "config": {
-            "model": "llama-3.1-8b shape", "global_batch": args.batch, "seq_len": CONTEXT,
+            "model": f"{args.model} shape", "global_batch": args.batch, "seq_len": CONTEXT,
             "prompt_tokens": PROMPT_TOKENS, "parallelism": "single GPU", "layers": L,
             "layers_of_full_model": full.num_hidden_layers, "hidden_size": h, "intermediate_size": i,
             "vocab_size": v, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
