@@ -25,7 +25,10 @@ namespace siar {
 
 constexpr int kPad = 8;             // bf16 elements of padding per shared-memory row (16 bytes)
 constexpr int kMmaDecodeChunk = 128;   // granularity of a decode block's key range
-constexpr int kDecodeWarpKeys = 16;    // keys per warp and pipeline step in the decode kernel
+// keys per warp and pipeline step in the decode kernel: 16 rows of 256 bytes at head_dim 128, 32 rows
+// of 128 bytes at head_dim 64 (the same bytes on their way per warp; with 16 the smaller head streamed
+// at little more than half the rate)
+__host__ __device__ constexpr int decode_warp_keys(int d) { return d <= 64 ? 32 : 16; }
 constexpr int kDecodeStages = 3;       // pipeline depth per warp
 constexpr int kDecodeBlocksPerSM = 2;  // what shared memory allows with that depth
 constexpr int kJoinPad = 8;            // floats of padding per row of the warps' join buffer (decode)
@@ -72,7 +75,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   SIAR_TRACE(20, 2);
   constexpr int RS = D + kPad;                 // row stride in elements
   constexpr int CPR = D / 8;                   // 16-byte pieces per row
-  constexpr int WK = kDecodeWarpKeys;          // keys per warp and step
+  constexpr int WK = decode_warp_keys(D);      // keys per warp and step
   constexpr int kStageElems = 2 * 4 * WK * RS; // K and V tiles of the four warps
   __shared__ int is_last;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -617,7 +620,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   const int max_chunks = (max_kv_len + chunk_keys - 1) / chunk_keys;
   float* part_ml = scratch;
   float* part_acc = scratch + (size_t)B * Hq * max_chunks * 2;
-  size_t smem = (size_t)kDecodeStages * 2 * 4 * kDecodeWarpKeys * (D + kPad) * 2;       // stages of K and V tiles
+  size_t smem = (size_t)kDecodeStages * 2 * 4 * decode_warp_keys(D) * (D + kPad) * 2;   // stages of K and V tiles
   const size_t merge = sizeof(float) * (4 * 16 * (D + kJoinPad) + 2 * 4 * 16);
   if (merge > smem) smem = merge;
   auto kern = attn_decode_mma_kernel<D>;
