@@ -14,6 +14,11 @@ the decode step with the bytes it has to read (each weight it uses once, plus th
 keys and values of the live sequences).  Weights are seeded random values of the
 real shape (there is no checkpoint offline); inputs exceed L2, so nothing stays
 cached between steps.
+
+Other workloads than the default run's: ``--model llama-3.2-1b|llama-3.2-3b`` takes
+another preset's layer sizes, ``--prompt-tokens N`` (with ``--context C``) other prompt
+and cache lengths, ``--batch B`` another batch; the line then names them in ``metric``
+and ``config``.
 """
 
 import argparse
