@@ -17,6 +17,7 @@ the whole batch and sampling outside the graph).
 
 from __future__ import annotations
 
+import gc
 import time
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
@@ -256,8 +257,18 @@ class _DecodeGraph:
         torch.cuda.current_stream().synchronize()
         before = ops.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._body(advance=True)
+        # An engine and its graphs refer to each other, so a dropped engine waits for the cycle
+        # collector; destroying its graphs while this stream captures would make the capture invalid.
+        # Collect now and keep the collector off until the capture has ended.
+        gc.collect()
+        collector_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self._body(advance=True)
+        finally:
+            if collector_on:
+                gc.enable()
         self.kernels = ops.launch_count - before
         ops.launch_count = before
 
