@@ -149,19 +149,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       int issued = 0;
       // Weights do not depend on earlier kernels: when X is the weight, the first STAGES
       // tiles of it are requested before this grid waits for its predecessors.
+      // x_is_weight: 1 the X operand is the weight, 2 the Y operand is (the many-row orientation)
       const int pre = prm.x_is_weight ? min(STAGES, num_kb) : 0;
+      const bool y_first = prm.x_is_weight == 2;
       const uint32_t tx_bytes = make_y ? kXBytes : kStageBytes;
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], tx_bytes);
-        tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
+        if (y_first)
+          tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
+        else
+          tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
       }
       SIAR_STAMP(1);
       pdl_wait();
       SIAR_TRACE(10, 2);
       SIAR_STAMP(2);
-      if (!make_y)
+      if (y_first) {
+        for (int i = 0; i < pre; ++i)
+          tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
+      } else if (!make_y) {
         for (int i = 0; i < pre; ++i)
           tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
+      }
       issued = pre;
       for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
@@ -353,17 +362,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         const int tr = quad * 32 + lane;
         int push_owner = 0, push_gl = 0;
 #pragma unroll 1
-        for (int ch = 0; ch < kChunks; ++ch) {
-          uint32_t r[16];
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          uint32_t r[32];
           if (num_kb > 0 && acc_ok) {
-            SIAR_TMEM_LD_16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 16), r);
+            SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ch * 32), r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = 0u;
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
 #pragma unroll
-          for (int g4 = 0; g4 < 4; ++g4) {
+          for (int g4 = 0; g4 < 8; ++g4) {
             const uint32_t local = recv + (uint32_t)(((rank * NLg + push_gl) * 128 + tr) * 16);
             uint32_t remote;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(push_owner));
@@ -437,7 +446,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const float4 v = mine4[(z * NLg + gl) * 128 + et];
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
           }
-          if (pp < prm.P) {
+          if (pp < prm.P && !prm.transpose_out) {
+            // rows of A on the tile's rows (prompts of a few hundred tokens): the group is four
+            // consecutive outputs of row pp; `accumulate` adds them into the float32 residual
+            const int q = q0 + 4 * gq;
+            TOut* dst = C + (long long)pp * prm.ldc + q;
+            const bool whole = q + 3 < prm.Q && prm.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(C) % 16) == 0;
+            if constexpr (sizeof(TOut) == 4) {
+              if (prm.accumulate) {
+                if (whole) {
+                  const float4 o = *reinterpret_cast<const float4*>(dst);
+                  acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+                } else {
+                  acc.x += reinterpret_cast<const float*>(dst)[0];
+                  if (q + 1 < prm.Q) acc.y += reinterpret_cast<const float*>(dst)[1];
+                  if (q + 2 < prm.Q) acc.z += reinterpret_cast<const float*>(dst)[2];
+                  if (q + 3 < prm.Q) acc.w += reinterpret_cast<const float*>(dst)[3];
+                }
+              }
+              if (whole) *reinterpret_cast<float4*>(dst) = acc;
+            } else {
+              if (whole) {
+                uint2 pk;
+                pk.x = pack_bf16x2(acc.x, acc.y);
+                pk.y = pack_bf16x2(acc.z, acc.w);
+                *reinterpret_cast<uint2*>(dst) = pk;
+              }
+            }
+            if (!whole) {
+              store_out<TOut>(dst, acc.x);
+              if (q + 1 < prm.Q) store_out<TOut>(dst + 1, acc.y);
+              if (q + 2 < prm.Q) store_out<TOut>(dst + 2, acc.z);
+              if (q + 3 < prm.Q) store_out<TOut>(dst + 3, acc.w);
+            }
+          } else if (pp < prm.P) {
             const int q = q0 + 4 * gq;
             TOut* dst = C + (long long)q * prm.ldc + pp;
             store_out<TOut>(dst, acc.x);
@@ -1166,6 +1208,26 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
   prm.stamps = g_stamps;
 #endif
 
+  // Prompts of a few hundred tokens give the many-row orientation fewer tiles than there are SMs,
+  // and a tile's block then streams its weight rows alone, at a single SM's share of the bandwidth.
+  // Those products run on the small-batch kernel in this orientation instead: a cluster of blocks
+  // per 128 x 256 tile, each with a slice of K, partial sums joined through distributed shared memory.
+  if (!swap && BN == 256 && epilogue != 1 && tiles < sm_count) {
+    int sp = sm_count / tiles;              // one block to an SM (192 KB of pipeline stages): one wave
+    sp = sp >= 8 ? 8 : sp >= 4 ? 4 : sp >= 2 ? 2 : 1;      // clusters of 3, 5, 6 or 7 do not all find room at once
+    if (sp > max_splits) sp = max_splits;
+    if (sp > num_kb / 4) sp = num_kb / 4;
+    if (sp >= 2) {
+      const int per = (num_kb + sp - 1) / sp;
+      sp = (num_kb + per - 1) / per;
+      prm.kb_per_split = per;
+      prm.x_is_weight = 2;
+      if (sp >= 2)
+        return out_f32 ? launch<256, 4, float>(tmX, tmY, prm, sp, s) : launch<256, 4, __nv_bfloat16>(tmX, tmY, prm, sp, s);
+      prm.kb_per_split = kbps;
+      prm.x_is_weight = 0;
+    }
+  }
   if (!swap && BN == 256 && sm_count >= 2 && (g_pairs == 2 || (g_pairs == 1 && P >= kPairRows))) {
     CUtensorMap tmY2;
     if (tensor_map(Y, Q, K, 128, &tmY2))

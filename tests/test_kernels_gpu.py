@@ -454,6 +454,7 @@ def test_sample_same_request_same_draw_in_any_batch():
     (33, 1000, 72), (64, 4096, 1024), (65, 384, 512), (128, 256, 256), (129, 256, 256), (200, 331, 96),
     (300, 520, 4096), (1024, 768, 512), (5, 40, 8), (2048, 256, 128),
     (20, 130, 264), (40, 331, 96), (64, 6144, 4096), (48, 4096, 14336), (100, 4096, 4096), (128, 1002, 520),
+    (256, 6144, 4096), (192, 4096, 8192), (500, 1000, 2048), (200, 330, 2048), (130, 257, 1024),
 ])
 def test_tensor_core_linear(m, n, k):
     from simple_inference_autoresearch_b200.kernels import gemm_tc
@@ -582,9 +583,12 @@ def test_product_makes_its_own_normed_input(m, n, k, pieces, swiglu):
     assert (got.float() - ref.float()).abs().max().item() <= 4e-3 * scale + 1e-4, (m, n, k)
 
 
-@pytest.mark.parametrize("m,n,k", [(129, 256, 256), (300, 520, 136), (2048, 4096, 512), (1000, 331 * 4, 264)])
+@pytest.mark.parametrize("m,n,k", [(129, 256, 256), (300, 520, 136), (2048, 4096, 512), (1000, 331 * 4, 264),
+                                   (300, 520, 4096), (256, 4096, 4096), (192, 1000, 14336), (500, 331 * 4, 1024),
+                                   (200, 330, 2048)])
 def test_product_of_many_rows_adds_into_the_residual(m, n, k):
-    """The persistent kernel's epilogue: residual += x @ w^T (no sums of squares), whole and ragged tiles."""
+    """residual += x @ w^T (no sums of squares), whole and ragged tiles: the persistent kernel's epilogue,
+    and for few tiles over a long K the cluster of blocks that shares a tile's K."""
     x = rnd(m, k, dtype=torch.bfloat16, seed=1).to(DEV)
     w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
     res0 = rnd(m, n, seed=3)
