@@ -38,7 +38,9 @@ template <typename T>
 __device__ __forceinline__ const T* key_row(const T* __restrict__ pool, const int* __restrict__ block_table,
                                             int slot, int max_pages, int page_tokens, int Hkv, int kvh, int D,
                                             int key) {
-  const int page = block_table[(size_t)slot * max_pages + key / page_tokens];
+  // a cell below zero is a page the sequence does not hold (the kernel that wrote this step's keys
+  // has reported it through the status word): read page 0, an address that exists
+  const int page = max(block_table[(size_t)slot * max_pages + key / page_tokens], 0);
   return pool + (((size_t)page * Hkv + kvh) * page_tokens + (key % page_tokens)) * D;
 }
 

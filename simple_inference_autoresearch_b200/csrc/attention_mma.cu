@@ -64,7 +64,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        const int* __restrict__ base_len, float* __restrict__ part_ml, float* __restrict__ part_acc,
                        int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int page_tokens,
                        int max_pages, int max_chunks, int chunk_keys, float scale, const float* __restrict__ inv_freq,
-                       int fuse_rope, int write_kv) {
+                       int fuse_rope, int write_kv, int* __restrict__ status) {
   // fuse_rope: the fused qkv rows are as the product left them; this kernel rotates q (in
   // registers) and the new token's k by the token's position, writes that k and v to the cache
   // (write_kv) and uses them from shared memory, so no separate rotate-and-write kernel runs.
@@ -98,9 +98,15 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   const int* table = block_table + (size_t)slot * max_pages;
   // The page of a tile is read from the block table one step before the tile is requested, so
   // that the (dependent) table read never sits in front of the loads it feeds.
+  // A block-table cell below zero is a page the sequence does not hold: its keys are read from
+  // page 0 (an address that exists), the new token's key and value are not stored, and the status
+  // word says so, so that the host raises instead of using the result.
+  bool absent_page = false;
   auto page_of = [&](int it) {
     const int w0 = c0 + it * 4 * WK + warp * WK;
-    return w0 < c_end ? __ldg(table + w0 / page_tokens) : 0;
+    int page = w0 < c_end ? __ldg(table + w0 / page_tokens) : 0;
+    if (page < 0) { absent_page = true; page = 0; }
+    return page;
   };
   auto load_tile = [&](int it, int stage, int page) {
     const int w0 = c0 + it * 4 * WK + warp * WK;
@@ -201,7 +207,9 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       __nv_bfloat16* ks = tiles + stage * kStageElems + warp * WK * RS + (pos - w0) * RS;
       __nv_bfloat16* vs = ks + 4 * WK * RS;
       const int page = __ldg(table + pos / page_tokens);
-      const size_t grow = (((size_t)page * Hkv + kvh) * page_tokens + (pos % page_tokens)) * D;
+      const bool held = page >= 0;
+      if (!held) absent_page = true;
+      const size_t grow = (((size_t)(held ? page : 0) * Hkv + kvh) * page_tokens + (pos % page_tokens)) * D;
       __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(k_pool) + grow;
       __nv_bfloat16* vdst = const_cast<__nv_bfloat16*>(v_pool) + grow;
       for (int i = lane; i < D / 2; i += 32) {
@@ -209,12 +217,12 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
         const __nv_bfloat16 oa = __float2bfloat16_rn(a * cs_s[i] - c2 * cs_s[D / 2 + i]);
         const __nv_bfloat16 oc = __float2bfloat16_rn(c2 * cs_s[i] + a * cs_s[D / 2 + i]);
         ks[i] = oa; ks[i + D / 2] = oc;
-        kdst[i] = oa; kdst[i + D / 2] = oc;
+        if (held) { kdst[i] = oa; kdst[i + D / 2] = oc; }
       }
       for (int d = lane; d < D; d += 32) {
         const __nv_bfloat16 v = vrow[d];
         vs[d] = v;
-        vdst[d] = v;
+        if (held) vdst[d] = v;
       }
       __syncwarp();
     }
@@ -292,6 +300,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   }
   cp_async_wait<0>();
 
+  if (absent_page && status != nullptr && lane == 0) atomicOr(status, kStatusBadPage);
   // join the four warps: reuse the tile memory as float buffers
   SIAR_STAMP(3);
   __syncthreads();
@@ -441,7 +450,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     cp_async_16(smem_u32_generic(q_s + r * RS + ch * 8), src, ok);
   }
   const int* table = block_table + (size_t)slot * max_pages;
-  auto page_of = [&](int tile) { return tile < n_tiles ? __ldg(table + tile * kMmaKeyTile / page_tokens) : 0; };
+  // a cell below zero (a page the sequence does not hold; the kernel that wrote this step's keys has
+  // reported it through the status word) is read as page 0, an address that exists
+  auto page_of = [&](int tile) { return tile < n_tiles ? max(__ldg(table + tile * kMmaKeyTile / page_tokens), 0) : 0; };
   auto load_tile = [&](int tile, int stage, int page) {
     const int j0 = tile * kMmaKeyTile;
     const int valid = min(kMmaKeyTile, block_kv_end - j0);
@@ -615,7 +626,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
                          const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
                          int* counters, int B, int Hq, int Hkv, int page_tokens, int max_pages, int max_kv_len,
                          int sm_count, float scale, cudaStream_t s, const float* inv_freq = nullptr,
-                         int fuse_rope = 0, int write_kv = 1) {
+                         int fuse_rope = 0, int write_kv = 1, int* status = nullptr) {
   const int chunk_keys = decode_chunk_keys(B, Hkv, max_kv_len, sm_count);
   const int max_chunks = (max_kv_len + chunk_keys - 1) / chunk_keys;
   float* part_ml = scratch;
@@ -634,7 +645,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, part_ml, part_acc,
                             counters, (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, max_chunks, chunk_keys,
-                            scale, inv_freq, fuse_rope, write_kv);
+                            scale, inv_freq, fuse_rope, write_kv, status);
 }
 
 template <int D>
@@ -686,16 +697,17 @@ extern "C" long long siar_attn_mma_decode_scratch_floats(int B, int Hq, int Hkv,
 extern "C" int siar_attn_mma_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                                     const int* slot_ids, const int* q_start, const int* base_len, void* out,
                                     float* scratch, int* counters, int B, int Hq, int Hkv, int D, int page_tokens,
-                                    int max_pages, int max_kv_len, int sm_count, float scale, void* stream) {
+                                    int max_pages, int max_kv_len, int sm_count, float scale, void* stream,
+                                    int* status) {
   if (B == 0) return 0;
   if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64)
     return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters,
-                             B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
+                             B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, nullptr, 0, 1, status);
   return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters, B,
-                            Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s);
+                            Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, nullptr, 0, 1, status);
 }
 
 // The same with the rotary encoding and the cache write of the new token fused in: qkv holds the
@@ -705,7 +717,7 @@ extern "C" int siar_attn_mma_decode_rope(const void* qkv, void* k_pool, void* v_
                                          const int* slot_ids, const int* q_start, const int* base_len, void* out,
                                          float* scratch, int* counters, const float* inv_freq, int write_kv, int B,
                                          int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_kv_len,
-                                         int sm_count, float scale, void* stream) {
+                                         int sm_count, float scale, void* stream, int* status) {
   if (B == 0) return 0;
   if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
     return (int)cudaErrorInvalidValue;
@@ -713,9 +725,10 @@ extern "C" int siar_attn_mma_decode_rope(const void* qkv, void* k_pool, void* v_
   if (D == 64)
     return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters,
                              B, Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, inv_freq, 1,
-                             write_kv);
+                             write_kv, status);
   return launch_decode<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters, B,
-                            Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, inv_freq, 1, write_kv);
+                            Hq, Hkv, page_tokens, max_pages, max_kv_len, sm_count, scale, s, inv_freq, 1, write_kv,
+                            status);
 }
 
 extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,

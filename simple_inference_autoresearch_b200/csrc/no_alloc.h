@@ -44,6 +44,11 @@
  * same call).  Two calls whose work overlaps on the GPU (different streams, or one
  * stream with programmatic overlap and no dependency) would race on the array: run
  * calls that share a device one after the other.
+ *
+ * Pages.  Every key position up to base_len[b] must have a page in the block table.
+ * A cell below zero (a page the sequence does not hold) is read as page 0, so the
+ * call touches no address outside the pools, but its result is then meaningless and,
+ * unlike the ordinary entry point, this one has no status word to say so.
  */
 #ifndef SIAR_NO_ALLOC_H
 #define SIAR_NO_ALLOC_H

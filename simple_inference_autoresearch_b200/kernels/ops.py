@@ -53,10 +53,10 @@ _signatures = {
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
         "siar_attn_mma_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_float, c_void_p],
+                                 c_float, c_void_p, c_void_p],
         "siar_attn_mma_decode_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_int, c_float, c_void_p],
+                                      c_int, c_int, c_int, c_float, c_void_p, c_void_p],
         "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
         "siar_attn_mma_decode_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
@@ -126,7 +126,7 @@ _status = {}
 STATUS_MESSAGES = {
     1: "a token id outside [0, vocab_size) was fed",
     2: "a bounded device-side wait expired",
-    4: "a cache write met a position without a page",
+    4: "a key or a cache write met a position without a page",
 }
 
 
@@ -403,7 +403,7 @@ def rope_and_attention(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, 
             _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len), _ptr(out), _ptr(scratch),
             _ptr(_decode_counters(qkv.device, meta.n_seqs * n_kv_heads)), _ptr(inv_freq), int(write_kv), meta.n_seqs,
             n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1], meta.max_kv_len, sms, float(scale),
-            _stream())
+            _stream(), _ptr(status_word(qkv.device)))
     return out
 
 
@@ -432,7 +432,7 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
                                   dtype=torch.float32, device=qkv.device)
             _launch("attention_mma", "siar_attn_mma_decode", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
                     _ptr(scratch), _ptr(_decode_counters(qkv.device, meta.n_seqs * n_kv_heads)), *sizes,
-                    meta.max_kv_len, sms, float(scale), _stream())
+                    meta.max_kv_len, sms, float(scale), _stream(), _ptr(status_word(qkv.device)))
         else:
             chunk = attention_limits()["decode_chunk"]
             scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len, chunk),

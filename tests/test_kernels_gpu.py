@@ -772,3 +772,47 @@ def test_fused_rope_decode_attention_equals_the_two_kernels(hq, hkv, d, write_kv
     torch.testing.assert_close(results[0][1], results[1][1], rtol=0, atol=0)     # cached keys: same rounding, same bits
     torch.testing.assert_close(results[0][2], results[1][2], rtol=0, atol=0)
     torch.testing.assert_close(results[0][0], results[1][0], rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype,path", [(torch.bfloat16, "fused"), (torch.bfloat16, "mma"), (torch.bfloat16, "mma_prefill"),
+                                        (torch.bfloat16, "cuda_core"), (torch.float32, "cuda_core")])
+def test_a_page_the_sequence_does_not_hold_is_reported_and_no_other_memory_is_touched(dtype, path):
+    """A block-table cell of -1 inside the keys a step reads and writes (a replay of a captured step
+    without the pages reserved first would meet one): the kernels read page 0 instead of an address
+    in front of the pool, store nothing for the token without a page, and the status word says so."""
+    hq, hkv, d = 8, 2, 128
+    width = (hq + 2 * hkv) * d
+    n_before, q_len = 300, (70 if path == "mma_prefill" else 1)
+    c = make_cache(hkv, d, dtype, DEV, max_tokens=4096, max_slots=4)
+    decoy, slot = c.alloc(), c.alloc()
+    c.reserve([decoy], [64]); c.commit([decoy], [64])           # page 0 belongs to another sequence
+    hist = rnd(n_before, width, dtype=dtype, seed=3).to(DEV)
+    c.reserve([slot], [n_before])
+    ops.rope_kv_write(hist, None, c.entry(0), BatchMeta.build([StepEntry(slot, [0] * n_before)], [0], DEV), hq, hkv, d)
+    c.commit([slot], [n_before])
+    c.reserve([slot], [q_len])
+    ops.check_status(DEV)
+    table = c.entry(0).block_table
+    table[slot, 2] = -1                                          # keys 128..191 of the history
+    table[slot, (n_before + q_len - 1) // 64] = -1               # and the page of the newest token
+    k_before, v_before = c.entry(0).k.clone(), c.entry(0).v.clone()
+    new = rnd(q_len, width, dtype=dtype, seed=4).to(DEV)
+    meta = BatchMeta.build([StepEntry(slot, [0] * q_len)], [n_before], DEV)
+    saved = ops.fuse_decode_rope, ops.use_mma_attention, ops.use_tc_attention
+    ops.fuse_decode_rope = path == "fused"
+    ops.use_mma_attention = path != "cuda_core"
+    ops.use_tc_attention = False
+    try:
+        out = ops.rope_and_attention(new, None, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d))
+        torch.cuda.synchronize()
+    finally:
+        ops.fuse_decode_rope, ops.use_mma_attention, ops.use_tc_attention = saved
+    assert out.shape == (q_len, hq * d)
+    with pytest.raises(RuntimeError, match="without a page"):
+        ops.check_status(DEV)
+    ops.check_status(DEV)                                        # the word is cleared once it has been read
+    # tokens whose page exists were stored (a prompt's first tokens), the one without a page nowhere
+    first_new_page = table[slot, n_before // 64].item()
+    changed_k = (c.entry(0).k != k_before).flatten(1).any(1).nonzero().flatten().tolist()
+    assert set(changed_k) <= {first_new_page} - {-1}
+    assert torch.equal(c.entry(0).v[0], v_before[0]) and torch.equal(c.entry(0).k[0], k_before[0])
