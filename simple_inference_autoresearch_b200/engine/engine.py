@@ -32,6 +32,10 @@ from .batch import BatchMeta, StepEntry
 from .model import DecoderModel
 
 
+#: captured decode steps an engine keeps (one per batch size and 512-key length bucket met)
+MAX_CAPTURED_STEPS = 64
+
+
 class Engine:
     def __init__(self, model: DecoderModel, max_batch: int = 8, max_seq_len: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_slots: Optional[int] = None, page_tokens: int = 64,
@@ -50,8 +54,9 @@ class Engine:
                                    max_seq_len, model.dtype, self.device, page_tokens)
         self.max_seq_len = self.cache.max_seq_len
         self.use_cuda_graph = bool(use_cuda_graph)
-        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}      # in order of last use
         self._graph_state: Optional[_GraphBuffers] = None
+        self._graph_pool = None      # one memory pool for all captured steps: they never run at the same time
 
     # ------------------------------------------------------------------ slots
     def open(self) -> int:
@@ -140,9 +145,12 @@ class Engine:
             st.host_in[j] = t[0]
         st.tokens[:b].copy_(st.host_in[:b], non_blocking=True)
         key = (b, bucket)
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
-            g = self._graphs[key] = _DecodeGraph(self, st, b, bucket)
+            while len(self._graphs) >= MAX_CAPTURED_STEPS:            # drop the step that was used longest ago
+                del self._graphs[next(iter(self._graphs))]
+            g = _DecodeGraph(self, st, b, bucket)
+        self._graphs[key] = g
         g.replay()
         # one synchronisation for both read-backs: the sampled tokens and the kernels' status word
         st.host_tokens[:b].copy_(st.tokens[:b], non_blocking=True)
@@ -263,8 +271,10 @@ class _DecodeGraph:
         gc.collect()
         collector_on = gc.isenabled()
         gc.disable()
+        if engine._graph_pool is None:
+            engine._graph_pool = torch.cuda.graph_pool_handle()
         try:
-            with torch.cuda.graph(self.graph):
+            with torch.cuda.graph(self.graph, pool=engine._graph_pool):
                 self._body(advance=True)
         finally:
             if collector_on:

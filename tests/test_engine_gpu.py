@@ -198,6 +198,29 @@ def test_greedy_generation_through_the_entry_point(folders, name, graph):
     assert one == outs[0] and st["prompt_tokens"] == len(reqs[0])
 
 
+def test_captured_steps_share_one_pool_and_the_oldest_are_dropped(folders, monkeypatch):
+    """Requests that end at different times give a captured step per batch size; with room for two
+    of them the engine drops the one used longest ago and captures it again when it is needed, all
+    in one memory pool.  The tokens are those of the engine without graphs."""
+    from simple_inference_autoresearch_b200.engine import engine as engine_module
+    monkeypatch.setattr(engine_module, "MAX_CAPTURED_STEPS", 2)
+    name = "A"
+    vocab = tiny_configs.CONFIGS[name]["vocab_size"]
+    reqs = prompts(vocab, [9, 4, 21, 2], seed=12)
+    new = [3, 14, 7, 10]                                 # batch sizes 4, 3, 2, 1 in turn
+    loaded = siar.load_model(folders[name], device="cuda", dtype=torch.bfloat16)
+    outs = {}
+    for graph in (True, False):
+        eng = siar.build_engine(loaded, max_batch=4, max_seq_len=128, use_cuda_graph=graph)
+        for _ in range(2):                               # the second round captures the dropped steps again
+            outs.setdefault(graph, []).append(eng.generate(reqs, SamplingParams(temperature=0.0),
+                                                           max_new_tokens=new, ignore_eos=True))
+        if graph:
+            assert len(eng._graphs) == 2 and eng._graph_pool is not None
+    assert outs[True] == outs[False]
+    assert [len(o) for o in outs[True][0]] == new
+
+
 def test_generation_stops_at_stop_tokens_and_samples_reproducibly(folders):
     name = "B"
     vocab = tiny_configs.CONFIGS[name]["vocab_size"]
