@@ -120,3 +120,26 @@ def test_resolve_path(tmp_path):
     assert arch.name == "LlamaForCausalLM" and cfg.num_hidden_layers == 3
     with pytest.raises(FileNotFoundError):
         registry.resolve_path(tmp_path / "missing")
+
+
+def test_shipped_configurations_include_the_two_tiny_ones():
+    a = LlamaConfig.from_json(preset_path("tiny-a"))
+    b = LlamaConfig.from_json(preset_path("tiny-b"))
+    assert (a.num_hidden_layers, a.hidden_size, a.num_attention_heads, a.num_key_value_heads, a.head_dim,
+            a.intermediate_size, a.vocab_size, a.tie_word_embeddings, a.rope_scaling) == (2, 64, 4, 2, 16, 176, 256, True, None)
+    assert (b.num_hidden_layers, b.hidden_size, b.num_attention_heads, b.num_key_value_heads, b.head_dim,
+            b.intermediate_size, b.vocab_size, b.tie_word_embeddings) == (3, 96, 3, 1, 32, 256, 384, False)
+    assert b.rope_scaling.rope_type == "llama3" and b.rope_scaling.original_max_position_embeddings == 32
+    assert b.rms_norm_eps == 1e-6 and a.rms_norm_eps == 1e-5
+
+
+def test_command_line_refusals(capsys):
+    from simple_inference_autoresearch_b200 import inference
+    for argv, words in (
+        (["--model", "no-such-model", "--prompt-len", "4"], "no such folder"),
+        (["--model", "no-such-model", "--random-weights", "--prompt-len", "4"], "no preset"),
+        (["--model", "tiny-a", "--random-weights", "--prompt-len", "4", "--batch", "0"], "--batch must be at least 1"),
+    ):
+        with pytest.raises(SystemExit) as e:
+            inference.main(argv)
+        assert e.value.code == 2 and words in capsys.readouterr().err

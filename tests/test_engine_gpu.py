@@ -302,3 +302,27 @@ def test_command_line(folders, capsys):
     first = [int(t) for t in out.splitlines()[0].split()]
     assert first == plain_greedy(folders["A"], [5, 17, 3], 6)
     assert "decode_tok_s" in out and "ttft_ms" in out and "prompt_tokens" in out
+
+
+def test_command_line_with_random_weights_a_batch_and_stop_ids(capsys):
+    """A shipped configuration with seeded random weights, several random prompts of unequal lengths
+    at once, and a further stop token: the same seed gives the same lines, and no line holds the stop token."""
+    from simple_inference_autoresearch_b200 import inference
+    base = ["--model", "tiny-b", "--random-weights", "--seed", "3", "--prompt-len", "12", "--batch", "3",
+            "--max-new-tokens", "10", "--temperature", "0", "--dtype", "float32", "--ignore-eos"]
+    assert inference.main(base) == 0
+    first = capsys.readouterr().out
+    lines = [ln for ln in first.splitlines() if ln.startswith("[")]
+    assert [ln.split()[1] for ln in lines] == ["12", "9", "6"]                 # prompt lengths from N down to N/2
+    tokens = [[int(t) for t in ln.split("->")[1].split()] for ln in lines]
+    assert all(len(t) == 10 for t in tokens)
+    assert inference.main(base) == 0
+    assert [ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("[")] == lines
+    stop = tokens[1][4]
+    assert inference.main(base + ["--stop-id", str(stop)]) == 0
+    cut = [[int(t) for t in ln.split("->")[1].split()] for ln in capsys.readouterr().out.splitlines() if ln.startswith("[")]
+    for full, c in zip(tokens, cut):
+        assert c == (full[:full.index(stop)] if stop in full else full)
+    assert inference.main(["--model", "tiny-a", "--random-weights", "--prompt-len", "5", "--max-new-tokens", "4",
+                           "--temperature", "0.8", "--top-k", "0", "--top-p", "1.0"]) == 0
+    assert "decode_tok_s" in capsys.readouterr().out
