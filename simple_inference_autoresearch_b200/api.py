@@ -81,10 +81,10 @@ def build_engine(loaded: LoadedModel, *, max_batch: int = 1, max_seq_len: Option
 def generate(prompt_ids: Sequence[int], engine: Engine, max_new_tokens: int = 256, temperature: float = 1.0,
              top_k: int = 50, top_p: float = 0.9, seed: int = 0, stop_token_ids=None,
              ignore_eos: bool = False) -> Iterator[int]:
-    """Yields the new token ids of one prompt (defaults as generate.py:50-59)."""
-    out, _ = generate_with_stats(prompt_ids, engine, max_new_tokens, temperature, top_k, top_p, seed=seed,
-                                 stop_token_ids=stop_token_ids, ignore_eos=ignore_eos)
-    yield from out
+    """Yields the new token ids of one prompt, each as soon as it is drawn (defaults as generate.py:50-59)."""
+    for _index, tok in engine.stream([list(prompt_ids)], SamplingParams(temperature, top_k, top_p, seed),
+                                     max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos):
+        yield tok
 
 
 def generate_with_stats(prompt_ids: Sequence[int], engine: Engine, max_new_tokens: int = 256,

@@ -163,15 +163,24 @@ class Engine:
         return out
 
     # ------------------------------------------------------------------ generation
+    def _stop_set(self, stop_token_ids, ignore_eos: bool) -> set:
+        stop = set() if ignore_eos else set(self.model.spec.stop_token_ids)
+        if stop_token_ids is not None:
+            stop |= {int(t) for t in stop_token_ids}
+        return stop
+
+    def stream(self, prompts: Sequence[Sequence[int]], params=SamplingParams(), max_new_tokens=128,
+               stop_token_ids: Optional[Iterable[int]] = None, ignore_eos: bool = False):
+        """``generate`` as a generator: yields ``(prompt index, token id)`` as soon as each token is drawn."""
+        return generation.stream(self, prompts, params, max_new_tokens, self._stop_set(stop_token_ids, ignore_eos))
+
     def generate(self, prompts: Sequence[Sequence[int]], params=SamplingParams(), max_new_tokens=128,
                  stop_token_ids: Optional[Iterable[int]] = None, ignore_eos: bool = False,
                  on_token: Optional[Callable[[int, int], None]] = None, return_stats: bool = False):
         """Generates for every prompt (lists of token ids); returns the new tokens
         of each, and with ``return_stats`` also a dict with the keys of the
         reference's stats (generate.py:227-237)."""
-        stop = set() if ignore_eos else set(self.model.spec.stop_token_ids)
-        if stop_token_ids is not None:
-            stop |= {int(t) for t in stop_token_ids}
+        stop = self._stop_set(stop_token_ids, ignore_eos)
         timings: dict = {}
         if self._cuda:
             torch.cuda.reset_peak_memory_stats(self.device)

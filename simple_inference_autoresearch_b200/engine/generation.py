@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
-from typing import Callable, Iterable, List, Optional, Protocol, Sequence, Tuple
+from typing import Callable, Iterable, Iterator, List, Optional, Protocol, Sequence, Tuple
 
 from ..sampling.params import SamplingParams
 
@@ -73,6 +73,15 @@ def plan_batches(requests: Sequence[Request], backend: Backend) -> List[List[Req
 
 def run_batch(batch: List[Request], backend: Backend, stop_ids: frozenset,
               on_token: Optional[Callable[[int, int], None]] = None, timings: Optional[dict] = None) -> None:
+    for index, tok in iter_batch(batch, backend, stop_ids, timings):
+        if on_token is not None:
+            on_token(index, tok)
+
+
+def iter_batch(batch: List[Request], backend: Backend, stop_ids: frozenset,
+               timings: Optional[dict] = None) -> Iterator[Tuple[int, int]]:
+    """Runs one batch and yields ``(request index, token)`` as each token is drawn.  When the
+    consumer stops early (the generator is closed), the slots still held are given back."""
     live = list(batch)
     for r in live:
         r.slot = backend.open()
@@ -93,8 +102,7 @@ def run_batch(batch: List[Request], backend: Backend, stop_ids: frozenset,
                     r.finish_reason = "stop"
                 else:
                     r.output.append(tok)
-                    if on_token is not None:
-                        on_token(r.index, tok)
+                    yield r.index, tok
                     if len(r.output) >= r.max_new_tokens:
                         r.finish_reason = "length"
                     elif len(r.prompt) + len(r.output) >= backend.max_seq_len:
@@ -118,6 +126,24 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], params, max_new
     """Runs all requests, batch after batch; returns them with ``output`` and
     ``finish_reason`` filled.  ``params`` and ``max_new_tokens`` are one value for
     all requests or one per request."""
+    requests = make_requests(prompts, params, max_new_tokens)
+    stop = frozenset(int(t) for t in stop_token_ids)
+    for batch in plan_batches([r for r in requests if r.finish_reason is None], backend):
+        run_batch(batch, backend, stop, on_token, timings)
+    return requests
+
+
+def stream(backend: Backend, prompts: Sequence[Sequence[int]], params, max_new_tokens,
+           stop_token_ids: Iterable[int] = (), timings: Optional[dict] = None) -> Iterator[Tuple[int, int]]:
+    """The same loop as a generator: yields ``(request index, token)`` the moment a token exists
+    (the reference streams its single request the same way, generate.py:50-119)."""
+    requests = make_requests(prompts, params, max_new_tokens)
+    stop = frozenset(int(t) for t in stop_token_ids)
+    for batch in plan_batches([r for r in requests if r.finish_reason is None], backend):
+        yield from iter_batch(batch, backend, stop, timings)
+
+
+def make_requests(prompts: Sequence[Sequence[int]], params, max_new_tokens) -> List[Request]:
     n = len(prompts)
     plist = list(params) if isinstance(params, (list, tuple)) else [params] * n
     mlist = list(max_new_tokens) if isinstance(max_new_tokens, (list, tuple)) else [max_new_tokens] * n
@@ -127,8 +153,4 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], params, max_new
     for r in requests:
         if r.max_new_tokens <= 0:
             r.finish_reason = "length"
-    todo = [r for r in requests if r.finish_reason is None]
-    stop = frozenset(int(t) for t in stop_token_ids)
-    for batch in plan_batches(todo, backend):
-        run_batch(batch, backend, stop, on_token, timings)
     return requests

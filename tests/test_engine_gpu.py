@@ -196,6 +196,12 @@ def test_greedy_generation_through_the_entry_point(folders, name, graph):
     assert stats["new_tokens"] == 8 * len(reqs) and stats["finish_reasons"] == ["length"] * len(reqs)
     one, st = siar.generate_with_stats(reqs[0], eng, max_new_tokens=8, temperature=0.0, ignore_eos=True)
     assert one == outs[0] and st["prompt_tokens"] == len(reqs[0])
+    # the streaming forms: one prompt's tokens one by one, and (prompt index, token) pairs of a batch
+    assert list(siar.generate(reqs[0], eng, max_new_tokens=8, temperature=0.0, ignore_eos=True)) == outs[0]
+    streamed = [[] for _ in reqs]
+    for index, tok in eng.stream(reqs, SamplingParams(temperature=0.0), max_new_tokens=8, ignore_eos=True):
+        streamed[index].append(tok)
+    assert streamed == outs
 
 
 def test_captured_steps_share_one_pool_and_the_oldest_are_dropped(folders, monkeypatch):

@@ -134,3 +134,23 @@ def test_slots_are_freed_when_a_step_raises():
     with pytest.raises(RuntimeError, match="boom"):
         generation.generate(be, [[9], [9]], GREEDY, 2)
     assert not be.held
+
+
+def test_stream_yields_each_token_when_it_is_drawn_and_gives_slots_back_when_abandoned():
+    script = {0: [10, 11, 12], 1: [20, 99, 22], 2: [30, 31, 32]}
+    be = ScriptedBackend(script)
+    seen = []
+    for index, tok in generation.stream(be, [[1, 2, 3], [4], [5, 6]], GREEDY, 3, stop_token_ids=[99]):
+        seen.append((index, tok, len(runs(be))))          # how many steps had run when the token came out
+    assert seen == [(0, 10, 1), (1, 20, 1), (0, 11, 2), (0, 12, 3), (2, 30, 4), (2, 31, 5), (2, 32, 6)]
+    assert not be.held
+    # the same tokens as the loop that returns everything at the end
+    be2 = ScriptedBackend(script)
+    reqs = generation.generate(be2, [[1, 2, 3], [4], [5, 6]], GREEDY, 3, stop_token_ids=[99])
+    assert [r.output for r in reqs] == [[10, 11, 12], [20], [30, 31, 32]] and be2.log == be.log
+    # a consumer that stops after the first token: the batch's slots are closed with the generator
+    be3 = ScriptedBackend(script)
+    it = generation.stream(be3, [[1, 2, 3], [4]], GREEDY, 3)
+    assert next(it) == (0, 10) and be3.held
+    it.close()
+    assert not be3.held
