@@ -438,9 +438,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
       if constexpr (BN >= 32) {
         const float4* mine4 = reinterpret_cast<const float4*>(tiles);
+        // Adding into the residual in the plain orientation: the old values of four groups are asked
+        // for at once (one trip to L2 for four groups instead of one trip each, in a row of them).
+        bool batched = false;
+        if constexpr (sizeof(TOut) == 4) {
+          if (prm.accumulate && !prm.transpose_out && pp < prm.P && prm.ldc % 4 == 0 &&
+              (reinterpret_cast<uintptr_t>(C) % 16) == 0) {
+            batched = true;
+            float* crow = reinterpret_cast<float*>(C) + (long long)pp * prm.ldc + q0;
+            for (int gl0 = 0; gl0 < NLg; gl0 += 4) {
+              float4 old[4];
+              bool ok[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int gq = (gl0 + u) * splits + rank;
+                ok[u] = gl0 + u < NLg && gq < kGroups && q0 + 4 * gq + 3 < prm.Q;
+                if (ok[u]) old[u] = *reinterpret_cast<const float4*>(crow + 4 * gq);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (!ok[u]) continue;
+                const int gl = gl0 + u, gq = gl * splits + rank;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int z = 0; z < splits; ++z) {
+                  const float4 v = mine4[(z * NLg + gl) * 128 + et];
+                  acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+                acc.x += old[u].x; acc.y += old[u].y; acc.z += old[u].z; acc.w += old[u].w;
+                *reinterpret_cast<float4*>(crow + 4 * gq) = acc;
+              }
+            }
+          }
+        }
         for (int gl = 0; gl < NLg; ++gl) {
           const int gq = gl * splits + rank;
           if (gq >= kGroups || q0 + 4 * gq >= prm.Q) break;
+          if (batched && q0 + 4 * gq + 3 < prm.Q) continue;      // done above
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int z = 0; z < splits; ++z) {
             const float4 v = mine4[(z * NLg + gl) * 128 + et];
