@@ -72,6 +72,27 @@ def test_generate_greedy_and_sampled(tmp_path):
     assert eng.cache.slots.held == 0
 
 
+def test_stream_and_the_one_prompt_generator_give_generates_tokens(tmp_path):
+    eng, raw, _ = build(tmp_path, "B", max_batch=2)
+    reqs = [toks(raw["vocab_size"], n, 20 + i) for i, n in enumerate((4, 13, 7))]
+    p = SamplingParams(temperature=0.8, top_k=0, top_p=1.0, seed=9)
+    new = [5, 2, 6]
+    outs = eng.generate(reqs, p, max_new_tokens=new, ignore_eos=True)
+    assert [len(o) for o in outs] == new
+    got = [[] for _ in reqs]
+    for index, tok in eng.stream(reqs, p, max_new_tokens=new, ignore_eos=True):
+        got[index].append(tok)
+    assert got == outs
+    # the first request alone draws the same tokens (request index 0, the same seed stream)
+    assert list(siar.generate(reqs[0], eng, max_new_tokens=5, temperature=0.8, top_k=0, top_p=1.0, seed=9,
+                              ignore_eos=True)) == outs[0]
+    it = eng.stream(reqs, p, max_new_tokens=new, ignore_eos=True)
+    next(it)
+    assert eng.cache.slots.held == 2
+    it.close()                                   # an abandoned stream gives its slots and pages back
+    assert eng.cache.slots.held == 0 and eng.cache.held_tokens() == 0
+
+
 def test_step_errors_come_before_any_launch(tmp_path):
     eng, raw, _ = build(tmp_path, "A", max_batch=2, max_tokens=128)
     s = eng.open()
