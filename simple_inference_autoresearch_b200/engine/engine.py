@@ -141,8 +141,7 @@ class Engine:
         if st.slots != slots or st.bucket != bucket:
             st.upload(requests, bucket)
         # the step's input tokens come from the host every step, as the caller gives them
-        for j, t in enumerate(new_tokens):
-            st.host_in[j] = t[0]
+        st.host_in_np[:b] = [t[0] for t in new_tokens]
         st.tokens[:b].copy_(st.host_in[:b], non_blocking=True)
         key = (b, bucket)
         g = self._graphs.pop(key, None)
@@ -234,6 +233,7 @@ class _GraphBuffers:
         self.seeds = z(capacity, torch.int64)
         self.host_tokens = torch.zeros(capacity, dtype=torch.int32).pin_memory()
         self.host_in = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.host_in_np = self.host_in.numpy()       # the same pinned memory, written without a torch call per token
         self.host_status = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.engine = engine
         self.slots: Optional[List[int]] = None
