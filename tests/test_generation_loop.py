@@ -154,3 +154,45 @@ def test_stream_yields_each_token_when_it_is_drawn_and_gives_slots_back_when_aba
     assert next(it) == (0, 10) and be3.held
     it.close()
     assert not be3.held
+
+
+def test_random_traffic_keeps_the_loops_promises():
+    """Random prompts, budgets and stop tokens: every request gets its script's tokens up to the first stop
+    token, its budget or the cache's capacity; a prompt is fed once and whole; every later step feeds each live
+    request the token it drew last; no step holds more requests than the backend allows; every slot comes back."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=80, deadline=None)
+    @given(st.lists(st.tuples(st.integers(1, 20), st.integers(0, 9)), min_size=1, max_size=9),
+           st.integers(1, 4), st.randoms(use_true_random=False))
+    def check(shape, max_batch, rnd):
+        n = len(shape)
+        prompts = [[rnd.randrange(3, 50) for _ in range(p)] for p, _ in shape]
+        budgets = [m for _, m in shape]
+        script = {i: [rnd.choice([1, 2, 60, 61, 62, 63]) for _ in range(12)] for i in range(n)}
+        stop = {1, 2}
+        max_seq_len = 24
+        be = ScriptedBackend(script, max_batch=max_batch, max_seq_len=max_seq_len, page=8, pages=3 * max_batch)
+        reqs = generation.generate(be, prompts, GREEDY, budgets, stop_token_ids=stop)
+        assert not be.held and sorted(be.free) == list(range(max_batch))
+        drawn = {i: 0 for i in range(n)}              # tokens request i has drawn so far
+        for _, indices, feeds in runs(be):
+            assert 1 <= len(indices) <= max_batch and len(set(indices)) == len(indices)
+            for i, f in zip(indices, feeds):
+                assert f == (prompts[i] if drawn[i] == 0 else [script[i][drawn[i] - 1]])
+                drawn[i] += 1
+        for i, r in enumerate(reqs):
+            want, reason = [], "length"
+            for tok in script[i]:
+                if len(want) >= budgets[i]:
+                    break
+                if tok in stop:
+                    reason = "stop"
+                    break
+                want.append(tok)
+                if len(want) < budgets[i] and len(prompts[i]) + len(want) >= max_seq_len:
+                    reason = "capacity"
+                    break
+            assert (r.output, r.finish_reason) == (want, reason), (i, prompts[i], budgets[i], script[i])
+            assert drawn[i] == (0 if budgets[i] == 0 else len(want) + (reason == "stop"))
+    check()
