@@ -212,9 +212,7 @@ def main() -> int:
             feed = [[t] for t in out]
         # device-timed: K replays of the captured step (tokens, lengths and sampling stay on the device)
         graph = engine._graphs[(batch, engine._graph_state.bucket)]
-        for r in slots_reqs:   # pages for the replays below
-            pass
-        engine.cache.reserve([r.slot for r in slots_reqs], [steps] * batch)
+        engine.cache.reserve([r.slot for r in slots_reqs], [steps] * batch)    # pages for the replays below
         sampler = ClockSampler()
         sampler.start()
         before = ops.launch_count
