@@ -106,8 +106,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
-    ap.add_argument("--model", default="llama-3.1-8b", choices=["llama-3.1-8b", "llama-3.2-1b", "llama-3.2-3b"],
-                    help="the preset whose layer sizes run (the default run's is llama-3.1-8b)")
+    ap.add_argument("--model", default="llama-3.1-8b",
+                    help="the shipped or registered configuration whose layer sizes run (the default run's is llama-3.1-8b)")
     ap.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS,
                     help="tokens of every prompt, also of the timed prefill (other context lengths than the default run's)")
     ap.add_argument("--context", type=int, default=0,
@@ -140,13 +140,18 @@ def main() -> int:
     import torch
 
     import simple_inference_autoresearch_b200 as siar
-    from simple_inference_autoresearch_b200.config import LlamaConfig, preset_path
+    from simple_inference_autoresearch_b200 import registry
+    from simple_inference_autoresearch_b200.config import preset_path
     from simple_inference_autoresearch_b200.engine import generation
     from simple_inference_autoresearch_b200.kernels import ops
 
     if args.no_pdl:
         ops.set_programmatic_launch(False)
-    full = LlamaConfig.from_json(preset_path(args.model))
+    try:
+        _arch, full = registry.resolve_path(preset_path(args.model))      # the class the preset's architecture names
+    except FileNotFoundError as e:
+        print(f"bench.py: {e}")
+        return 2
     cfg = dataclasses.replace(full, num_hidden_layers=args.layers) if args.layers else full
     pk, pk_src = peaks()
     dev = torch.device("cuda:0")

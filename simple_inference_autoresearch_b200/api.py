@@ -18,6 +18,7 @@ from . import registry
 from .engine.engine import Engine
 from .engine.model import DecoderModel
 from .kernels import build
+from .kernels.options import DEFAULT as DEFAULT_OPTIONS, KernelOptions
 from .sampling.params import SamplingParams
 from .weights.loader import load_checkpoint
 from .weights.random_init import random_tensors
@@ -72,28 +73,32 @@ def init_random(loaded: LoadedModel, seed: int) -> LoadedModel:
 
 
 def build_engine(loaded: LoadedModel, *, max_batch: int = 1, max_seq_len: Optional[int] = None,
-                 max_tokens: Optional[int] = None, use_cuda_graph: bool = True) -> Engine:
-    """The counterpart of the reference's ``build_cache``: cache and step function for a loaded model."""
+                 max_tokens: Optional[int] = None, use_cuda_graph: bool = True,
+                 options: KernelOptions = DEFAULT_OPTIONS) -> Engine:
+    """The counterpart of the reference's ``build_cache``: cache and step function for a loaded model.
+    ``options`` chooses kernels where there is a choice (``KernelOptions``)."""
     return Engine(loaded.model, max_batch=max_batch, max_seq_len=max_seq_len, max_tokens=max_tokens,
-                  use_cuda_graph=use_cuda_graph)
+                  use_cuda_graph=use_cuda_graph, options=options)
 
 
 def generate(prompt_ids: Sequence[int], engine: Engine, max_new_tokens: int = 256, temperature: float = 1.0,
              top_k: int = 50, top_p: float = 0.9, seed: int = 0, stop_token_ids=None,
-             ignore_eos: bool = False) -> Iterator[int]:
-    """Yields the new token ids of one prompt, each as soon as it is drawn (defaults as generate.py:50-59)."""
+             ignore_eos: bool = False, request_id: int = 0) -> Iterator[int]:
+    """Yields the new token ids of one prompt, each as soon as it is drawn (defaults as generate.py:50-59).
+    ``request_id`` keys the random stream together with ``seed`` (see ``Engine.generate``)."""
     for _index, tok in engine.stream([list(prompt_ids)], SamplingParams(temperature, top_k, top_p, seed),
-                                     max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos):
+                                     max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos,
+                                     request_ids=[request_id]):
         yield tok
 
 
 def generate_with_stats(prompt_ids: Sequence[int], engine: Engine, max_new_tokens: int = 256,
                         temperature: float = 1.0, top_k: int = 50, top_p: float = 0.9,
                         on_token: Optional[Callable[[int], None]] = None, seed: int = 0, stop_token_ids=None,
-                        ignore_eos: bool = False) -> Tuple[list, dict]:
+                        ignore_eos: bool = False, request_id: int = 0) -> Tuple[list, dict]:
     """(new token ids, stats) for one prompt; stats has the reference's keys (generate.py:227-237)."""
     cb = (lambda _i, tok: on_token(tok)) if on_token is not None else None
     outs, stats = engine.generate([list(prompt_ids)], SamplingParams(temperature, top_k, top_p, seed),
                                   max_new_tokens, stop_token_ids=stop_token_ids, ignore_eos=ignore_eos,
-                                  on_token=cb, return_stats=True)
+                                  on_token=cb, return_stats=True, request_ids=[request_id])
     return outs[0], stats

@@ -15,11 +15,15 @@ from ..engine.model import ModelSpec
 from ..parts.base import PartSpec
 
 
-def llama_model_spec(cfg: LlamaConfig, norm_weight_init: str = "ones") -> ModelSpec:
-    """``norm_weight_init`` only matters to the random-weights writer."""
+def llama_model_spec(cfg: LlamaConfig, norm_weight_init: str = None) -> ModelSpec:
+    """``norm_weight_init`` (default: the configuration's) and the configuration's
+    ``initializer_range`` only matter to the random-weights writer."""
     scaling = cfg.rope_scaling.to_dict() if cfg.rope_scaling is not None else None
+    std = cfg.initializer_range
+    norm_weight_init = norm_weight_init or cfg.norm_weight_init
     norm = lambda prefix: PartSpec("rmsnorm", {"prefix": prefix, "hidden_size": cfg.hidden_size,  # noqa: E731
-                                               "eps": cfg.rms_norm_eps, "weight_init": norm_weight_init})
+                                               "eps": cfg.rms_norm_eps, "weight_init": norm_weight_init,
+                                               "weight_std": std})
     layers = []
     for i in range(cfg.num_hidden_layers):
         layers.append(PartSpec("prenorm", {
@@ -27,10 +31,11 @@ def llama_model_spec(cfg: LlamaConfig, norm_weight_init: str = "ones") -> ModelS
             "mixer_norm": norm("input_layernorm."),
             "mixer": PartSpec("gqa_attention", {
                 "prefix": "self_attn.", "hidden_size": cfg.hidden_size, "n_heads": cfg.num_attention_heads,
-                "n_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim}),
+                "n_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "init_std": std}),
             "ffn_norm": norm("post_attention_layernorm."),
             "feed_forward": PartSpec("swiglu", {
-                "prefix": "mlp.", "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}),
+                "prefix": "mlp.", "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+                "init_std": std}),
         }))
     return ModelSpec(
         architecture=cfg.architecture,
@@ -43,4 +48,5 @@ def llama_model_spec(cfg: LlamaConfig, norm_weight_init: str = "ones") -> ModelS
         layers=tuple(layers),
         final_norm=norm("model.norm."),
         stop_token_ids=cfg.stop_token_ids,
+        embedding_std=std,
     )

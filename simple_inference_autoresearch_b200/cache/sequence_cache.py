@@ -31,6 +31,10 @@ import torch
 from ..parts.base import KVNeed, StateNeed
 
 
+#: positions per page of keys and values: the key tile of the tensor-core attention kernels
+DEFAULT_PAGE_TOKENS = 64
+
+
 class CacheError(RuntimeError):
     """Misuse or exhaustion of the cache (raised before anything is launched)."""
 
@@ -99,9 +103,9 @@ class KVGroup:
         self.page_tokens = page_tokens
         self.max_pages_per_seq = max_pages_per_seq
         self.pages = FreeList(n_pages, "cache page")
-        shape = (n_entries, n_pages, need.n_kv_heads, page_tokens, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (n_entries, n_pages, need.n_kv_heads, page_tokens)
+        self.k = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
         # -1 marks "no page"; the cache-write kernel flags a write through it.
         self.block_table = torch.full((n_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
         # per slot: the page of every page index so far; None once a windowed group gave it back
@@ -150,13 +154,18 @@ class KVGroup:
     def held_pages(self, slot: int) -> int:
         return sum(p is not None for p in self.slot_pages[slot])
 
-    def close_slot(self, slot: int) -> None:
-        for p in self.slot_pages.pop(slot):
+    def close_slot(self, slot: int) -> List[Tuple[int, int, int]]:
+        """Gives the slot's pages back; returns (slot, page index, -1) rows for the block table, so
+        that the next sequence in this slot finds no page number of this one beyond its own length
+        (a read past the reserved pages then meets -1 and is reported)."""
+        pages = self.slot_pages.pop(slot)
+        for p in pages:
             if p is not None:
                 self.pages.give(p)
+        return [(slot, idx, -1) for idx, p in enumerate(pages) if p is not None]
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class StateGroup:
@@ -189,13 +198,14 @@ class SequenceCache:
     """
 
     def __init__(self, needs: Sequence[object], max_tokens: int, max_slots: int, max_seq_len: int,
-                 dtype: torch.dtype, device, page_tokens: int = 64):
+                 dtype: torch.dtype, device, page_tokens: int = DEFAULT_PAGE_TOKENS):
         if max_tokens <= 0 or max_slots <= 0 or max_seq_len <= 0:
             raise CacheError("max_tokens, max_slots and max_seq_len must be positive")
         self.page_tokens = page_tokens
         self.n_pages = -(-max_tokens // page_tokens)
         self.n_slots = min(max_slots, self.n_pages)
-        self.max_seq_len = min(round_up(max_seq_len, page_tokens), self.n_pages * page_tokens)
+        # the caller's limit stands as given (only the page count is rounded up)
+        self.max_seq_len = min(int(max_seq_len), self.n_pages * page_tokens)
         self.dtype, self.device = dtype, device
         self.slots = FreeList(self.n_slots, "cache slot")
         self.lengths: Dict[int, int] = {}
@@ -209,7 +219,7 @@ class SequenceCache:
         for need, entries in by_need.items():
             if isinstance(need, KVNeed):
                 g = KVGroup(need, len(entries), self.n_slots, self.n_pages,
-                            self.max_seq_len // page_tokens, page_tokens, dtype, device)
+                            -(-self.max_seq_len // page_tokens), page_tokens, dtype, device)
             elif isinstance(need, StateNeed):
                 g = StateGroup(need, len(entries), self.n_slots, device)
             else:
@@ -239,7 +249,7 @@ class SequenceCache:
             raise CacheError(f"cache slot {slot} is not held (freed twice?)")
         for g in self.groups:
             if isinstance(g, KVGroup):
-                g.close_slot(slot)
+                self._upload_cells(g, g.close_slot(slot))
         del self.lengths[slot]
         self.slots.give(slot)
 

@@ -13,6 +13,10 @@ Key names, required/optional status and defaults follow the reference's
 * Options the kernels do not implement (biases, an activation other than SiLU,
   an unknown rope_type) are refused here with a clear error instead of being
   silently ignored.
+* Two keys only the random-weights mode reads (the reference has no such mode):
+  ``initializer_range`` (the checkpoint format's own key: the standard deviation of
+  matrices and embeddings, default 0.02) and ``norm_weight_init`` (this library's:
+  ``"ones"`` or ``"ones_plus_normal"``, norm weights 1 or 1 + N(0, initializer_range)).
 """
 
 from __future__ import annotations
@@ -95,6 +99,8 @@ class LlamaConfig:
     tie_word_embeddings: bool = True
     torch_dtype: str = "bfloat16"
     architecture: str = field(default="LlamaForCausalLM")
+    initializer_range: float = 0.02
+    norm_weight_init: str = "ones"
 
     def __post_init__(self):
         def bad(msg):
@@ -121,6 +127,10 @@ class LlamaConfig:
             bad(f"rope_theta must be > 0, got {self.rope_theta!r}")
         if self.torch_dtype not in _DTYPES:
             bad(f"torch_dtype must be one of {_DTYPES}, got {self.torch_dtype!r}")
+        if not (self.initializer_range > 0):
+            bad(f"initializer_range must be > 0, got {self.initializer_range!r}")
+        if self.norm_weight_init not in ("ones", "ones_plus_normal"):
+            bad(f"norm_weight_init must be 'ones' or 'ones_plus_normal', got {self.norm_weight_init!r}")
         if isinstance(self.eos_token_id, int):
             object.__setattr__(self, "eos_token_id", (int(self.eos_token_id),))
         else:
@@ -179,6 +189,8 @@ class LlamaConfig:
             tie_word_embeddings=bool(d.get("tie_word_embeddings", True)),
             torch_dtype=d.get("torch_dtype", d.get("dtype", "bfloat16")),
             architecture=str(archs[0]),
+            initializer_range=float(d.get("initializer_range", 0.02)),
+            norm_weight_init=str(d.get("norm_weight_init", "ones")),
         )
 
     @classmethod
@@ -191,7 +203,10 @@ class LlamaConfig:
 
     def to_dict(self) -> dict:
         eos = list(self.eos_token_id)
+        extra = {} if self.norm_weight_init == "ones" else {"norm_weight_init": self.norm_weight_init}
         return {
+            **extra,
+            "initializer_range": self.initializer_range,
             "architectures": [self.architecture],
             "model_type": "llama",
             "hidden_size": self.hidden_size,

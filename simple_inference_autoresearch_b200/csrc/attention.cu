@@ -37,10 +37,14 @@ constexpr int kDecodeRound = kDecodeWarps * kTile;  // keys staged in shared mem
 template <typename T>
 __device__ __forceinline__ const T* key_row(const T* __restrict__ pool, const int* __restrict__ block_table,
                                             int slot, int max_pages, int page_tokens, int Hkv, int kvh, int D,
-                                            int key) {
-  // a cell below zero is a page the sequence does not hold (the kernel that wrote this step's keys
-  // has reported it through the status word): read page 0, an address that exists
-  const int page = max(block_table[(size_t)slot * max_pages + key / page_tokens], 0);
+                                            int key, int* __restrict__ status) {
+  // a cell below zero is a page the sequence does not hold: read page 0, an address that
+  // exists, and say so through the status word, so that the host raises instead of using the result
+  int page = block_table[(size_t)slot * max_pages + key / page_tokens];
+  if (page < 0) {
+    if (status != nullptr) atomicOr(status, kStatusBadPage);
+    page = 0;
+  }
   return pool + (((size_t)page * Hkv + kvh) * page_tokens + (key % page_tokens)) * D;
 }
 
@@ -52,7 +56,8 @@ __global__ void __launch_bounds__(kPrefillWarps * 32)
 attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                     const int* __restrict__ block_table, const int* __restrict__ slot_ids,
                     const int* __restrict__ q_start, const int* __restrict__ base_len, T* __restrict__ out,
-                    int Hq, int Hkv, int D, int page_tokens, int max_pages, float scale, int window) {
+                    int Hq, int Hkv, int D, int page_tokens, int max_pages, float scale, int window,
+                    int* __restrict__ status) {
   // window > 0: a query at position p sees keys p - window + 1 .. p only (0 = all keys up to p);
   // keys in front of a block's first window are never touched (their pages may be gone).
   pdl_launch_dependents();
@@ -108,8 +113,8 @@ attn_prefill_kernel(const T* __restrict__ qkv, const T* __restrict__ k_pool, con
       const int key = j0 + j;
       float kval = 0.f, vval = 0.f;
       if (key < block_kv_end && key >= block_kv_begin) {
-        kval = to_f32(key_row(k_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d]);
-        vval = to_f32(key_row(v_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d]);
+        kval = to_f32(key_row(k_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key, status)[d]);
+        vval = to_f32(key_row(v_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key, status)[d]);
       }
       k_s[j * (D + 1) + d] = kval;
       v_s[j * D + d] = vval;
@@ -168,13 +173,20 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
                            const int* __restrict__ block_table, const int* __restrict__ slot_ids,
                            const int* __restrict__ q_start, const int* __restrict__ base_len,
                            float* __restrict__ part_ml, float* __restrict__ part_acc, int Hq, int Hkv, int D,
-                           int page_tokens, int max_pages, int max_chunks, float scale, int window) {
+                           int page_tokens, int max_pages, int max_chunks, float scale, int window,
+                           int* __restrict__ status) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = Hq / Hkv;
-  const int kv_len = base_len[b] + 1;
+  int kv_len = base_len[b] + 1;
+  if (kv_len > max_chunks * kDecodeChunk) {
+    // the sequence is longer than the launch was sized for (a captured step replayed past its
+    // length bucket): the keys beyond the grid are not read, and the status word says so
+    if (status != nullptr && threadIdx.x == 0) atomicOr(status, kStatusLengthPastGrid);
+    kv_len = max_chunks * kDecodeChunk;
+  }
   const int c0 = c * kDecodeChunk;
   if (c0 >= kv_len) return;
   const int c_end = min(kv_len, c0 + kDecodeChunk);
@@ -221,8 +233,8 @@ attn_decode_partial_kernel(const T* __restrict__ qkv, const T* __restrict__ k_po
       const int key = r0 + j;
       T kval = from_f32<T>(0.f), vval = from_f32<T>(0.f);
       if (key < c_end && key >= kv_begin) {
-        kval = key_row(k_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d];
-        vval = key_row(v_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key)[d];
+        kval = key_row(k_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key, status)[d];
+        vval = key_row(v_pool, block_table, slot, max_pages, page_tokens, Hkv, kvh, D, key, status)[d];
       }
       k_s[j * ks + d] = kval;
       v_s[j * D + d] = vval;
@@ -299,7 +311,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_ml, co
   pdl_wait();
   const int hq = blockIdx.x, b = blockIdx.y;
   const int kv_len = base_len[b] + 1;
-  const int n_chunks = (kv_len + kDecodeChunk - 1) / kDecodeChunk;
+  const int n_chunks = min((kv_len + kDecodeChunk - 1) / kDecodeChunk, max_chunks);   // the partial kernel reports a longer sequence
   const size_t p0 = ((size_t)b * Hq + hq) * max_chunks;
   float mx = -INFINITY;
   for (int c = 0; c < n_chunks; ++c) mx = fmaxf(mx, part_ml[(p0 + c) * 2]);
@@ -326,7 +338,7 @@ template <typename T, int NDIM>
 static int launch_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                           const int* slot_ids, const int* q_start, const int* base_len, void* out, int B, int Hq,
                           int Hkv, int D, int page_tokens, int max_pages, int max_q_len, float scale, int window,
-                          cudaStream_t s) {
+                          cudaStream_t s, int* status) {
   const int G = Hq / Hkv;
   const size_t smem = sizeof(float) * ((size_t)kPrefillRows * D + kTile * (D + 1) + kTile * D);
   auto kern = attn_prefill_kernel<T, NDIM>;
@@ -337,7 +349,7 @@ static int launch_prefill(const void* qkv, const void* k_pool, const void* v_poo
   dim3 grid((max_q_len * G + kPrefillRows - 1) / kPrefillRows, Hkv, B);
   launch_kernel(kern, grid, kPrefillWarps * 32, smem, s, (const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
                                               slot_ids, q_start, base_len, (T*)out, Hq, Hkv, D, page_tokens,
-                                              max_pages, scale, window);
+                                              max_pages, scale, window, status);
   return (int)cudaGetLastError();
 }
 
@@ -355,14 +367,14 @@ extern "C" int siar_attn_max_head_dim() { return 256; }
 extern "C" int siar_attn_prefill(int is_bf16, const void* qkv, const void* k_pool, const void* v_pool,
                                  const int* block_table, const int* slot_ids, const int* q_start,
                                  const int* base_len, void* out, int B, int Hq, int Hkv, int D, int page_tokens,
-                                 int max_pages, int max_q_len, int window, float scale, void* stream) {
+                                 int max_pages, int max_q_len, int window, float scale, void* stream, int* status) {
   if (B == 0 || max_q_len == 0) return 0;
   if (D % 16 != 0 || D > 256 || D <= 0 || Hq % Hkv != 0 || Hkv > 65535 || B > 65535 || window < 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
 #define SIAR_PREFILL(T, ND)                                                                                   \
   return launch_prefill<T, ND>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv, \
-                               D, page_tokens, max_pages, max_q_len, scale, window, s)
+                               D, page_tokens, max_pages, max_q_len, scale, window, s, status)
   const int nd = (D + 31) / 32;
   if (is_bf16) {
     if (nd <= 1) SIAR_PREFILL(__nv_bfloat16, 1);
@@ -388,7 +400,7 @@ template <typename T>
 static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                          const int* slot_ids, const int* q_start, const int* base_len, void* out, float* scratch,
                          int B, int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_kv_len,
-                         float scale, int window, cudaStream_t s) {
+                         float scale, int window, cudaStream_t s, int* status) {
   const int G = Hq / Hkv;
   const int max_chunks = (max_kv_len + kDecodeChunk - 1) / kDecodeChunk;
   float* part_ml = scratch;
@@ -403,7 +415,7 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   dim3 grid(max_chunks, Hkv, B);
   launch_kernel(kern, grid, kDecodeWarps * 32, smem, s, (const T*)qkv, (const T*)k_pool, (const T*)v_pool, block_table,
                                              slot_ids, q_start, base_len, part_ml, part_acc, Hq, Hkv, D,
-                                             page_tokens, max_pages, max_chunks, scale, window);
+                                             page_tokens, max_pages, max_chunks, scale, window, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   dim3 grid2(Hq, B);
@@ -419,14 +431,14 @@ extern "C" int siar_attn_decode(int is_bf16, const void* qkv, const void* k_pool
                                 const int* block_table, const int* slot_ids, const int* q_start,
                                 const int* base_len, void* out, float* scratch, int B, int Hq, int Hkv, int D,
                                 int page_tokens, int max_pages, int max_kv_len, int window, float scale,
-                                void* stream) {
+                                void* stream, int* status) {
   if (B == 0) return 0;
   if (D % 16 != 0 || D > 256 || D <= 0 || Hq % Hkv != 0 || Hkv > 65535 || B > 65535 || max_kv_len <= 0 || window < 0)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (is_bf16)
     return launch_decode<__nv_bfloat16>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out,
-                                        scratch, B, Hq, Hkv, D, page_tokens, max_pages, max_kv_len, scale, window, s);
+                                        scratch, B, Hq, Hkv, D, page_tokens, max_pages, max_kv_len, scale, window, s, status);
   return launch_decode<float>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, B, Hq,
-                              Hkv, D, page_tokens, max_pages, max_kv_len, scale, window, s);
+                              Hkv, D, page_tokens, max_pages, max_kv_len, scale, window, s, status);
 }

@@ -86,7 +86,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   // The prologue is a chain of dependent reads (lengths -> table -> tiles; row -> query), each a
   // trip to L2: everything that has its address is asked for before anything is used.
   const int base_b = base_len[b], slot = slot_ids[b], row_b = q_start[b];
-  const int kv_len = base_b + 1;
+  // A sequence longer than the launch was sized for (a captured step replayed past its length
+  // bucket): the keys beyond the grid are not read, the chunk count stays within the grid (so the
+  // counters end at zero and the row is written), and the status word says so.
+  const bool past_grid = base_b + 1 > max_chunks * chunk_keys;
+  const int kv_len = past_grid ? max_chunks * chunk_keys : base_b + 1;
   const float sl2 = scale * 1.4426950408889634f;     // scores, maxima and the partials' maxima are in the base-2 domain
   const int c0 = c * chunk_keys;
   if (c0 >= kv_len) return;
@@ -138,7 +142,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   SIAR_STAMP(7);
   int page_ahead = pages[kDecodeStages - 1];      // page of tile it + kDecodeStages - 1 at step it
   static_assert(D / 2 <= 128, "one thread per rotation frequency");
-  const int pos = kv_len - 1;                      // position of the new token
+  const int pos = base_b;                          // position of the new token
   if (fuse_rope) {
     if (threadIdx.x < D / 2) {
       float sn = 0.f, cs = 1.f;
@@ -301,6 +305,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   cp_async_wait<0>();
 
   if (absent_page && status != nullptr && lane == 0) atomicOr(status, kStatusBadPage);
+  if (past_grid && status != nullptr && threadIdx.x == 0) atomicOr(status, kStatusLengthPastGrid);
   // join the four warps: reuse the tile memory as float buffers
   SIAR_STAMP(3);
   __syncthreads();
@@ -413,7 +418,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_table,
                         const int* __restrict__ slot_ids, const int* __restrict__ q_start,
                         const int* __restrict__ base_len, __nv_bfloat16* __restrict__ out, int Hq, int Hkv,
-                        int page_tokens, int max_pages, float scale) {
+                        int page_tokens, int max_pages, float scale, int* __restrict__ status) {
   pdl_launch_dependents();
   SIAR_TRACE(21, 0);
   pdl_wait();
@@ -450,9 +455,14 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     cp_async_16(smem_u32_generic(q_s + r * RS + ch * 8), src, ok);
   }
   const int* table = block_table + (size_t)slot * max_pages;
-  // a cell below zero (a page the sequence does not hold; the kernel that wrote this step's keys has
-  // reported it through the status word) is read as page 0, an address that exists
-  auto page_of = [&](int tile) { return tile < n_tiles ? max(__ldg(table + tile * kMmaKeyTile / page_tokens), 0) : 0; };
+  // a cell below zero (a page the sequence does not hold) is read as page 0, an address that
+  // exists, and reported through the status word
+  bool absent_page = false;
+  auto page_of = [&](int tile) {
+    int page = tile < n_tiles ? __ldg(table + tile * kMmaKeyTile / page_tokens) : 0;
+    if (page < 0) { absent_page = true; page = 0; }
+    return page;
+  };
   auto load_tile = [&](int tile, int stage, int page) {
     const int j0 = tile * kMmaKeyTile;
     const int valid = min(kMmaKeyTile, block_kv_end - j0);
@@ -584,6 +594,7 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     __syncthreads();   // everyone is done with this stage before it is refilled
   }
 
+  if (absent_page && status != nullptr && threadIdx.x == 0) atomicOr(status, kStatusBadPage);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + g + 8 * h;
@@ -635,11 +646,14 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
   const size_t merge = sizeof(float) * (4 * 16 * (D + kJoinPad) + 2 * 4 * 16);
   if (merge > smem) smem = merge;
   auto kern = attn_decode_mma_kernel<D>;
-  static bool attr = false;
-  if (!attr && smem > 48 * 1024) {
+  // the shared-memory limit of a kernel is a property of the device's copy of it: set once per device
+  static bool attr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (!attr[dev] && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr = true;
+    attr[dev] = true;
   }
   dim3 grid(max_chunks, Hkv, B);
   return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
@@ -651,7 +665,8 @@ static int launch_decode(const void* qkv, const void* k_pool, const void* v_pool
 template <int D>
 static int launch_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                           const int* slot_ids, const int* q_start, const int* base_len, void* out, int B, int Hq,
-                          int Hkv, int page_tokens, int max_pages, int max_q_len, float scale, cudaStream_t s) {
+                          int Hkv, int page_tokens, int max_pages, int max_q_len, float scale, cudaStream_t s,
+                          int* status) {
   const int G = Hq / Hkv;
   const size_t smem = (size_t)(kMmaPrefillRows + 4 * kMmaKeyTile) * (D + kPad) * 2;
   auto kern = attn_prefill_mma_kernel<D>;
@@ -664,7 +679,7 @@ static int launch_prefill(const void* qkv, const void* k_pool, const void* v_poo
   dim3 grid((max_q_len * G + kMmaPrefillRows - 1) / kMmaPrefillRows, Hkv, B);
   return (int)launch_kernel(kern, grid, dim3(128), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len,
-                            (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, scale);
+                            (__nv_bfloat16*)out, Hq, Hkv, page_tokens, max_pages, scale, status);
 }
 
 }  // namespace siar
@@ -712,15 +727,19 @@ extern "C" int siar_attn_mma_decode(const void* qkv, const void* k_pool, const v
 
 // The same with the rotary encoding and the cache write of the new token fused in: qkv holds the
 // product's output (q and k not rotated), inv_freq the rotary frequencies (nullptr: no rotation),
-// write_kv == 0 leaves the cache alone (a layer that reads another layer's cache).
+// write_kv == 0 leaves the cache alone (a layer that reads another layer's cache).  The kernel
+// rotates the whole head in pairs (i, i + D/2); any other rotary layout (rotary_dim != D, interleaved
+// pairs) is refused with cudaErrorInvalidValue, and the caller runs the separate rotary kernel.
 extern "C" int siar_attn_mma_decode_rope(const void* qkv, void* k_pool, void* v_pool, const int* block_table,
                                          const int* slot_ids, const int* q_start, const int* base_len, void* out,
                                          float* scratch, int* counters, const float* inv_freq, int write_kv, int B,
                                          int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_kv_len,
-                                         int sm_count, float scale, void* stream, int* status) {
+                                         int sm_count, float scale, void* stream, int* status, int rotary_dim,
+                                         int interleaved) {
   if (B == 0) return 0;
   if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535 || max_kv_len <= 0)
     return (int)cudaErrorInvalidValue;
+  if (inv_freq != nullptr && (rotary_dim != D || interleaved)) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64)
     return launch_decode<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, scratch, counters,
@@ -734,16 +753,16 @@ extern "C" int siar_attn_mma_decode_rope(const void* qkv, void* k_pool, void* v_
 extern "C" int siar_attn_mma_prefill(const void* qkv, const void* k_pool, const void* v_pool, const int* block_table,
                                      const int* slot_ids, const int* q_start, const int* base_len, void* out, int B,
                                      int Hq, int Hkv, int D, int page_tokens, int max_pages, int max_q_len,
-                                     float scale, void* stream) {
+                                     float scale, void* stream, int* status) {
   if (B == 0 || max_q_len == 0) return 0;
   if (!siar_attn_mma_supported(Hq, Hkv, D, page_tokens) || Hkv > 65535 || B > 65535)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64)
     return launch_prefill<64>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv,
-                              page_tokens, max_pages, max_q_len, scale, s);
+                              page_tokens, max_pages, max_q_len, scale, s, status);
   return launch_prefill<128>(qkv, k_pool, v_pool, block_table, slot_ids, q_start, base_len, out, B, Hq, Hkv,
-                             page_tokens, max_pages, max_q_len, scale, s);
+                             page_tokens, max_pages, max_q_len, scale, s, status);
 }
 
 // ------------------------------------------------------------------ decode without allocation

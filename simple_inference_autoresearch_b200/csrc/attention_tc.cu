@@ -175,13 +175,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       const int* table = prm.block_table + (size_t)slot * prm.max_pages;
       int issued_k = 0, issued_v = 0;
+      // A cell below zero means "no page": the sequence does not hold these positions.  It is read
+      // as page 0 (never as a row in front of the pool) and reported through the status word.
+      bool bad_page = false;
       int page = table[0];                       // read one tile ahead of its use
+      if (page < 0) { bad_page = true; page = 0; }
       for (int i = 0; i < nt_max; ++i) {
         const int s = i % kStages;
         const uint32_t ph = ((i / kStages) & 1) ^ 1;
         const int j0 = i * kKeys;
         const int row = (page * prm.Hkv + kvh) * prm.page_tokens + (j0 % prm.page_tokens);
-        if (i + 1 < nt_max) page = table[(j0 + kKeys) / prm.page_tokens];
+        if (i + 1 < nt_max) {
+          page = table[(j0 + kKeys) / prm.page_tokens];
+          if (page < 0) { bad_page = true; page = 0; }
+        }
         if (!mbar_wait(&k_empty[s], ph) || SIAR_ABORTED()) { SIAR_FAIL(); break; }
         mbar_expect_tx(&k_full[s], kTileBytes);
 #pragma unroll
@@ -195,6 +202,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           tma_load_2d(v_s + s * kTileBytes + h * (kTileBytes / kHalves), &tmV, &v_full[s], 64 * h, row);
         issued_v = i + 1;
       }
+      if (bad_page) atomicOr(prm.status, kStatusBadPage);
       if (SIAR_ABORTED()) {    // let copies in flight land before the block leaves
         mbar_wait(&q_full, 0);
         for (int i = max(0, issued_k - kStages); i < issued_k; ++i) mbar_wait(&k_full[i % kStages], (i / kStages) & 1);

@@ -26,6 +26,7 @@ enum StatusBits : int {
   kStatusTokenOutOfRange = 1,
   kStatusWaitExpired = 2,
   kStatusBadPage = 4,
+  kStatusLengthPastGrid = 8,
 };
 
 __device__ __forceinline__ float to_f32(float x) { return x; }

@@ -189,18 +189,22 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
 // One block per token.  The token's sin/cos (one pair per rotary frequency, shared by all
 // heads) are formed once in shared memory; then q heads are rotated in place, k heads are
 // rotated into the cache and v heads are copied into the cache.  inv_freq == nullptr means
-// "no rotation".
+// "no rotation".  This kernel takes every rotary layout: the first `rotary_dim` dims of a head are
+// rotated (the rest pass through), in pairs (i, i + rotary_dim/2) or, `interleaved`, (2i, 2i+1);
+// inv_freq holds rotary_dim/2 frequencies.  (The reference's kernel has the same two pairings,
+// kernels/rope_kernel.py:139-152, and always rotates the whole head.)
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ inv_freq,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const int* __restrict__ block_table, const int* __restrict__ slot_ids,
                                      const int* __restrict__ q_start, const int* __restrict__ base_len,
                                      int B, int Hq, int Hkv, int D, int page_tokens, int max_pages,
-                                     int n_pages, int write_kv, int* __restrict__ status) {
+                                     int n_pages, int write_kv, int* __restrict__ status, int rotary_dim,
+                                     int interleaved) {
   pdl_launch_dependents();
   SIAR_TRACE(3, 0);
   extern __shared__ float cs[];   // cos[half], sin[half]
-  const int half = D >> 1;
+  const int half = rotary_dim >> 1;
   const int flat = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
   for (int i = flat; i < half; i += nthreads) cs[i] = inv_freq != nullptr ? inv_freq[i] : 0.f;
   pdl_wait();
@@ -237,11 +241,14 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
   for (int head = blockIdx.y * blockDim.y + threadIdx.y; head < n_rot; head += hstep) {
     T* dst = head < Hq ? row + head * D : kdst + (size_t)(head - Hq) * head_stride;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const float a = to_f32(row[head * D + i]), c = to_f32(row[head * D + i + half]);
+      const int i0 = interleaved ? 2 * i : i, i1 = interleaved ? 2 * i + 1 : i + half;
+      const float a = to_f32(row[head * D + i0]), c = to_f32(row[head * D + i1]);
       const float cosv = cs[i], sinv = cs[half + i];
-      dst[i] = from_f32<T>(a * cosv - c * sinv);
-      dst[i + half] = from_f32<T>(c * cosv + a * sinv);
+      dst[i0] = from_f32<T>(a * cosv - c * sinv);
+      dst[i1] = from_f32<T>(c * cosv + a * sinv);
     }
+    if (head >= Hq)      // the dims of a key past the rotary part go to the cache as they are
+      for (int i = rotary_dim + threadIdx.x; i < D; i += blockDim.x) dst[i] = row[head * D + i];
   }
   if (vdst != nullptr) {
     const T* vrow = row + (size_t)(Hq + Hkv) * D;
@@ -490,16 +497,19 @@ extern "C" int siar_add_rmsnorm(int out_bf16, int weight_bf16, float* residual, 
 extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq, void* k_pool, void* v_pool,
                                   const int* block_table, const int* slot_ids, const int* q_start,
                                   const int* base_len, int N, int B, int Hq, int Hkv, int D, int page_tokens,
-                                  int max_pages, int n_pages, int write_kv, int* status, void* stream) {
+                                  int max_pages, int n_pages, int write_kv, int* status, void* stream,
+                                  int rotary_dim, int interleaved) {
   if (N == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  if (D % 2 != 0) return (int)cudaErrorInvalidValue;
+  if (D % 2 != 0 || rotary_dim < 0 || rotary_dim > D || rotary_dim % 2 != 0) return (int)cudaErrorInvalidValue;
+  if (inv_freq == nullptr) rotary_dim = D;      // no rotation: every dim passes through the pair loop with angle 0
+  const bool whole_split_half = rotary_dim == D && !interleaved;
   // many tokens: one block per token walks all heads; few tokens: several blocks share a token
   const int ysplit = N >= 256 ? 1 : (Hq + Hkv < 16 ? Hq + Hkv : 16);
   const int tx = D / 2 > 64 ? 128 : D / 2 > 32 ? 64 : 32;   // one pass over the D/2 pairs of a head
   const dim3 threads(tx, ysplit == 1 ? 256 / tx : 1);        // many tokens: several heads at a time per block
   const size_t smem = sizeof(float) * D;
-  if (is_bf16 && N >= 256 && D % 16 == 0 && D <= 256 && (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) == 0) {
+  if (whole_split_half && is_bf16 && N >= 256 && D % 16 == 0 && D <= 256 && (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) % 16) == 0) {
     launch_kernel(rope_kv_write_bf16x8_kernel, dim3(N), dim3(128), smem, s, (__nv_bfloat16*)qkv, inv_freq,
                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv,
                   D, page_tokens, max_pages, n_pages, write_kv, status);
@@ -508,11 +518,11 @@ extern "C" int siar_rope_kv_write(int is_bf16, void* qkv, const float* inv_freq,
   if (is_bf16)
     launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(N, ysplit), dim3(threads), smem, s, (__nv_bfloat16*)qkv, inv_freq,
                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv,
-                  D, page_tokens, max_pages, n_pages, write_kv, status);
+                  D, page_tokens, max_pages, n_pages, write_kv, status, rotary_dim, interleaved);
   else
     launch_kernel(rope_kv_write_kernel<float>, dim3(N, ysplit), dim3(threads), smem, s, (float*)qkv, inv_freq, (float*)k_pool,
                   (float*)v_pool, block_table, slot_ids, q_start, base_len, B, Hq, Hkv, D, page_tokens, max_pages,
-                  n_pages, write_kv, status);
+                  n_pages, write_kv, status, rotary_dim, interleaved);
   LAUNCH_END();
 }
 

@@ -1159,16 +1159,14 @@ extern "C" void siar_gemm_tc_set_stamps(unsigned long long* p) { g_stamps = p; }
 #endif
 
 // Products of many rows with at least 256 output columns: two SMs per 256 x 256 tile or one SM per
-// 128 x 256 tile.  0 = never pairs, 2 = always, 1 = pairs from kPairRows rows on (measured on B200 with
-// the Llama-3.1-8B products: at 8,192 rows pairs are 2% faster, at 2,048 rows 1.5% slower; both run
-// near the clocks the power cap allows, so the third less traffic from L2 buys little).
-static int g_pairs = 1;
+// 128 x 256 tile.  pair_mode 0 = never pairs, 2 = always, 1 = pairs from kPairRows rows on (measured on
+// B200 with the Llama-3.1-8B products: at 8,192 rows pairs are 2% faster, at 2,048 rows 1.5% slower; both
+// run near the clocks the power cap allows, so the third less traffic from L2 buys little).
 constexpr int kPairRows = 4096;
-extern "C" void siar_gemm_tc_set_pairs(int mode) { g_pairs = mode < 0 ? 0 : mode > 2 ? 2 : mode; }
 
-// Products with fewer output tiles than this many per SM are split along K.
-static int g_split_target = 1;
-extern "C" void siar_gemm_tc_set_split_target(int blocks_per_sm) { g_split_target = blocks_per_sm < 1 ? 1 : blocks_per_sm; }
+// Products with fewer output tiles than this many per SM are split along K (two or three blocks'
+// worth of splits per SM made a decode step 4-6% slower).
+constexpr int kSplitTarget = 1;
 
 // Returns 0 on launch, a cudaError_t on failure, and -1 when the shape is one this
 // unit does not take (the caller then uses the CUDA-core kernel).
@@ -1183,7 +1181,7 @@ extern "C" void siar_gemm_tc_set_split_target(int blocks_per_sm) { g_split_targe
 //   norm_w with eps, the sums of squares of the rows given in pieces as ss_in [M, ss_tiles].
 static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, int out_f32, int max_splits,
                     int epilogue, int* status, int sm_count, void* stream, const float* resid, const float* ss_in,
-                    int ss_tiles, const void* norm_w, float eps, float* ss_out) {
+                    int ss_tiles, const void* norm_w, float eps, float* ss_out, int pair_mode) {
   if (M <= 0 || N <= 0) return 0;
   if (epilogue < 0 || epilogue > 2) return -1;
   if (epilogue == 1 && (out_f32 || (N & 1))) return -1;
@@ -1210,8 +1208,8 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
   const int tiles = ((P + kBM - 1) / kBM) * ((Q + BN - 1) / BN);
   const int num_kb = (K + kBK - 1) / kBK;
   int splits = 1;
-  if (swap && tiles < g_split_target * sm_count) {
-    splits = (g_split_target * sm_count + tiles - 1) / tiles;
+  if (swap && tiles < kSplitTarget * sm_count) {
+    splits = (kSplitTarget * sm_count + tiles - 1) / tiles;
     if (splits > 8) splits = 8;
     if (splits > max_splits) splits = max_splits;
     if (splits > num_kb / 4) splits = num_kb / 4;
@@ -1261,7 +1259,7 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
       prm.x_is_weight = 0;
     }
   }
-  if (!swap && BN == 256 && sm_count >= 2 && (g_pairs == 2 || (g_pairs == 1 && P >= kPairRows))) {
+  if (!swap && BN == 256 && sm_count >= 2 && (pair_mode >= 2 || (pair_mode == 1 && P >= kPairRows))) {
     CUtensorMap tmY2;
     if (tensor_map(Y, Q, K, 128, &tmY2))
       return out_f32 ? launch_pair<6, float>(tmX, tmY2, prm, sm_count, s)
@@ -1288,17 +1286,18 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
 }
 
 extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
-                                 int max_splits, int epilogue, int* status, int sm_count, void* stream) {
+                                 int max_splits, int epilogue, int* status, int sm_count, void* stream,
+                                 int pair_mode) {
   if (epilogue == 2) return -1;
   return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, nullptr, nullptr, 0,
-                  nullptr, 0.f, nullptr);
+                  nullptr, 0.f, nullptr, pair_mode);
 }
 
 // The same product inside a float32 residual stream, for at most 16 rows (see run_gemm).
 extern "C" int siar_gemm_tc_bf16_fused(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
                                        int max_splits, int epilogue, int* status, int sm_count, void* stream,
                                        const float* resid, const float* ss_in, int ss_tiles, const void* norm_w,
-                                       float eps, float* ss_out) {
+                                       float eps, float* ss_out, int pair_mode) {
   return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, resid, ss_in, ss_tiles,
-                  norm_w, eps, ss_out);
+                  norm_w, eps, ss_out, pair_mode);
 }

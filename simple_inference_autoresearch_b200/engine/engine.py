@@ -24,8 +24,9 @@ from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.sequence_cache import SequenceCache, round_up
+from ..cache.sequence_cache import DEFAULT_PAGE_TOKENS, SequenceCache, round_up
 from ..kernels import ops
+from ..kernels.options import DEFAULT, KernelOptions
 from ..sampling.params import SamplingParams, request_seed
 from . import generation
 from .batch import BatchMeta, StepEntry
@@ -38,9 +39,10 @@ MAX_CAPTURED_STEPS = 64
 
 class Engine:
     def __init__(self, model: DecoderModel, max_batch: int = 8, max_seq_len: Optional[int] = None,
-                 max_tokens: Optional[int] = None, max_slots: Optional[int] = None, page_tokens: int = 64,
-                 use_cuda_graph: bool = True):
+                 max_tokens: Optional[int] = None, max_slots: Optional[int] = None, page_tokens: int = DEFAULT_PAGE_TOKENS,
+                 use_cuda_graph: bool = True, options: KernelOptions = DEFAULT):
         self.model = model
+        self.options = options        # which kernel runs where there is a choice (this engine's steps only)
         self.device = model.device
         self._cuda = self.device.type == "cuda"   # kernels refuse anything else at their first launch
         max_seq_len = int(max_seq_len or model.spec.max_position)
@@ -57,6 +59,7 @@ class Engine:
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}      # in order of last use
         self._graph_state: Optional[_GraphBuffers] = None
         self._graph_pool = None      # one memory pool for all captured steps: they never run at the same time
+        self._last_logits: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ slots
     def open(self) -> int:
@@ -84,7 +87,7 @@ class Engine:
         self.cache.reserve(slots, q_lens)
         base = [self.cache.length(s) for s in slots]
         meta = BatchMeta.build(entries, base, self.device)
-        logits = self.model.forward(meta, self.cache)
+        logits = self.model.forward(meta, self.cache, self.options)
         self.cache.commit(slots, q_lens)
         if self._graph_state is not None:
             self._graph_state.invalidate()
@@ -99,7 +102,7 @@ class Engine:
         for j, r in enumerate(requests):
             f[j], f[n + j] = r.params.temperature, r.params.top_p
             i[j], i[n + j] = r.params.top_k, len(r.output)
-            s[j] = request_seed(r.params.seed, r.index)
+            s[j] = request_seed(r.params.seed, r.index if r.request_id is None else r.request_id)
         return f, i, s
 
     def _upload(self, array: np.ndarray) -> torch.Tensor:
@@ -119,6 +122,7 @@ class Engine:
             return self._run_graph(requests, new_tokens)
         entries = [StepEntry(r.slot, t, [len(t) - 1]) for r, t in zip(requests, new_tokens)]
         logits = self.step(entries)
+        self._last_logits = logits
         toks = self.sample(logits, requests)
         out = toks.cpu().tolist()
         ops.check_status(self.device)
@@ -132,6 +136,9 @@ class Engine:
             self._graph_state = _GraphBuffers(self, max(self.max_batch, b))
         st = self._graph_state
         if st.capacity < b:
+            # the captured steps read the old buffers: they go with them
+            self._graphs.clear()
+            self._last_logits = None
             self._graph_state = st = _GraphBuffers(self, b)
         # A captured step serves lengths up to `bucket`; the attention grid and its chunking
         # are fixed by it, so buckets are kept fine (512 keys) and a new graph is captured
@@ -151,6 +158,7 @@ class Engine:
             g = _DecodeGraph(self, st, b, bucket)
         self._graphs[key] = g
         g.replay()
+        self._last_logits = g.logits
         # one synchronisation for both read-backs: the sampled tokens and the kernels' status word
         st.host_tokens[:b].copy_(st.tokens[:b], non_blocking=True)
         st.host_status.copy_(ops.status_word(self.device), non_blocking=True)
@@ -161,6 +169,13 @@ class Engine:
             ops.check_status(self.device)      # raises with the kernels' message and clears the word
         return out
 
+    def last_logits(self) -> Optional[torch.Tensor]:
+        """float32 logits ``[sequences, vocab]`` that the last ``run`` drew its tokens from, in the
+        order of its requests (None before the first ``run``).  After a captured step this is the
+        step's own output buffer, which any later captured step overwrites; the reference's graph
+        runner hands out its static logits the same way (model/cuda_graph_decode.py:134-143)."""
+        return self._last_logits
+
     # ------------------------------------------------------------------ generation
     def _stop_set(self, stop_token_ids, ignore_eos: bool) -> set:
         stop = set() if ignore_eos else set(self.model.spec.stop_token_ids)
@@ -169,22 +184,28 @@ class Engine:
         return stop
 
     def stream(self, prompts: Sequence[Sequence[int]], params=SamplingParams(), max_new_tokens=128,
-               stop_token_ids: Optional[Iterable[int]] = None, ignore_eos: bool = False):
+               stop_token_ids: Optional[Iterable[int]] = None, ignore_eos: bool = False,
+               request_ids: Optional[Sequence[int]] = None):
         """``generate`` as a generator: yields ``(prompt index, token id)`` as soon as each token is drawn."""
-        return generation.stream(self, prompts, params, max_new_tokens, self._stop_set(stop_token_ids, ignore_eos))
+        return generation.stream(self, prompts, params, max_new_tokens, self._stop_set(stop_token_ids, ignore_eos),
+                                 request_ids=request_ids)
 
     def generate(self, prompts: Sequence[Sequence[int]], params=SamplingParams(), max_new_tokens=128,
                  stop_token_ids: Optional[Iterable[int]] = None, ignore_eos: bool = False,
-                 on_token: Optional[Callable[[int, int], None]] = None, return_stats: bool = False):
+                 on_token: Optional[Callable[[int, int], None]] = None, return_stats: bool = False,
+                 request_ids: Optional[Sequence[int]] = None):
         """Generates for every prompt (lists of token ids); returns the new tokens
         of each, and with ``return_stats`` also a dict with the keys of the
-        reference's stats (generate.py:227-237)."""
+        reference's stats (generate.py:227-237).  ``request_ids``: one integer per prompt that keys
+        its random stream together with the seed (default: the prompt's index in this call), so
+        that a request can be repeated alone, or at another place of another call, and draw the same tokens."""
         stop = self._stop_set(stop_token_ids, ignore_eos)
         timings: dict = {}
         if self._cuda:
             torch.cuda.reset_peak_memory_stats(self.device)
         t0 = time.perf_counter()
-        reqs = generation.generate(self, prompts, params, max_new_tokens, stop, on_token, timings)
+        reqs = generation.generate(self, prompts, params, max_new_tokens, stop, on_token, timings,
+                                   request_ids=request_ids)
         if self._cuda:
             torch.cuda.synchronize(self.device)
         wall = time.perf_counter() - t0
@@ -293,7 +314,9 @@ class _DecodeGraph:
 
     def _body(self, advance: bool) -> None:
         eng, st, b = self.engine, self.st, self.b
-        logits = eng.model.forward(self.meta, eng.cache)
+        logits = eng.model.forward(self.meta, eng.cache, eng.options)
+        if advance:
+            self.logits = logits
         ops.sample(logits, st.temperature[:b], st.top_k[:b], st.top_p[:b], st.seeds[:b], st.draw_index[:b],
                    advance_index=advance, out=st.tokens[:b] if advance else None)
         if advance:

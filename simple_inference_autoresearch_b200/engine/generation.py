@@ -31,6 +31,7 @@ class Request:
     max_new_tokens: int
     params: SamplingParams
     index: int = 0
+    request_id: Optional[int] = None      # keys the request's random stream with its seed; None: the index
     # filled by the loop
     output: List[int] = field(default_factory=list)
     finish_reason: Optional[str] = None   # "stop" | "length" | "capacity"
@@ -122,11 +123,12 @@ def iter_batch(batch: List[Request], backend: Backend, stop_ids: frozenset,
 
 
 def generate(backend: Backend, prompts: Sequence[Sequence[int]], params, max_new_tokens, stop_token_ids: Iterable[int] = (),
-             on_token: Optional[Callable[[int, int], None]] = None, timings: Optional[dict] = None) -> List[Request]:
+             on_token: Optional[Callable[[int, int], None]] = None, timings: Optional[dict] = None,
+             request_ids: Optional[Sequence[int]] = None) -> List[Request]:
     """Runs all requests, batch after batch; returns them with ``output`` and
     ``finish_reason`` filled.  ``params`` and ``max_new_tokens`` are one value for
     all requests or one per request."""
-    requests = make_requests(prompts, params, max_new_tokens)
+    requests = make_requests(prompts, params, max_new_tokens, request_ids)
     stop = frozenset(int(t) for t in stop_token_ids)
     for batch in plan_batches([r for r in requests if r.finish_reason is None], backend):
         run_batch(batch, backend, stop, on_token, timings)
@@ -134,22 +136,27 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], params, max_new
 
 
 def stream(backend: Backend, prompts: Sequence[Sequence[int]], params, max_new_tokens,
-           stop_token_ids: Iterable[int] = (), timings: Optional[dict] = None) -> Iterator[Tuple[int, int]]:
+           stop_token_ids: Iterable[int] = (), timings: Optional[dict] = None,
+           request_ids: Optional[Sequence[int]] = None) -> Iterator[Tuple[int, int]]:
     """The same loop as a generator: yields ``(request index, token)`` the moment a token exists
     (the reference streams its single request the same way, generate.py:50-119)."""
-    requests = make_requests(prompts, params, max_new_tokens)
+    requests = make_requests(prompts, params, max_new_tokens, request_ids)
     stop = frozenset(int(t) for t in stop_token_ids)
     for batch in plan_batches([r for r in requests if r.finish_reason is None], backend):
         yield from iter_batch(batch, backend, stop, timings)
 
 
-def make_requests(prompts: Sequence[Sequence[int]], params, max_new_tokens) -> List[Request]:
+def make_requests(prompts: Sequence[Sequence[int]], params, max_new_tokens,
+                  request_ids: Optional[Sequence[int]] = None) -> List[Request]:
     n = len(prompts)
+    if request_ids is not None and len(request_ids) != n:
+        raise ValueError("request_ids must hold one id per prompt")
     plist = list(params) if isinstance(params, (list, tuple)) else [params] * n
     mlist = list(max_new_tokens) if isinstance(max_new_tokens, (list, tuple)) else [max_new_tokens] * n
     if len(plist) != n or len(mlist) != n:
         raise ValueError("params / max_new_tokens must be one value or one per prompt")
-    requests = [Request(list(p), int(m), sp, index=i) for i, (p, m, sp) in enumerate(zip(prompts, mlist, plist))]
+    requests = [Request(list(p), int(m), sp, index=i, request_id=None if request_ids is None else int(request_ids[i]))
+                for i, (p, m, sp) in enumerate(zip(prompts, mlist, plist))]
     for r in requests:
         if r.max_new_tokens <= 0:
             r.finish_reason = "length"

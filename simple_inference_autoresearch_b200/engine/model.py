@@ -20,6 +20,7 @@ from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 import torch
 
 from ..kernels import ops
+from ..kernels.options import DEFAULT, KernelOptions
 from ..parts.base import BLOCKS, NORMS, POSITION_ENCODINGS, PartSpec, TensorSpec
 
 
@@ -56,12 +57,14 @@ class ModelSpec:
 
 
 class StepContext:
-    """What parts see of a step: the compute dtype and the batch description."""
+    """What parts see of a step: the compute dtype, the batch description and the kernel
+    options of the engine that runs it (parts hand ``options`` on to the functions of ``ops``)."""
 
-    def __init__(self, dtype: torch.dtype, meta, cache):
+    def __init__(self, dtype: torch.dtype, meta, cache, options: KernelOptions = DEFAULT):
         self.dtype = dtype
         self.meta = meta
         self.cache = cache
+        self.options = options
         self.residual = None      # set by a block: the stream a sublayer's last product may add into
 
 
@@ -129,13 +132,16 @@ class DecoderModel:
         self._weight_bytes = total
 
     def extension_units(self) -> List[str]:
+        """The CUDA units a step of this model launches from: the model's own (embedding, head
+        product, sampling) and what each part names for the compute dtype."""
         units = ["elementwise", "gemm_simt", "sampling"]
         if self.dtype == torch.bfloat16:
-            units.append("gemm_tc")
-        for layer in self.layers:
-            units += list(layer.extension_units())
-        if self.dtype != torch.bfloat16:   # the tensor-core units are bfloat16 only
-            units = [u for u in units if u not in ("gemm_tc", "attention_mma", "attention_tc")]
+            units.append("gemm_tc")        # the head product
+        for part in [self.position, self.final_norm] + self.layers:
+            try:
+                units += list(part.extension_units(self.dtype))
+            except TypeError:              # a part written before the argument existed
+                units += list(part.extension_units())
         return sorted(set(units))
 
     def weight_bytes(self) -> int:
@@ -143,10 +149,10 @@ class DecoderModel:
         return self._weight_bytes
 
     # ---- forward
-    def forward(self, meta, cache) -> torch.Tensor:
+    def forward(self, meta, cache, options: KernelOptions = DEFAULT) -> torch.Tensor:
         """Runs the step's tokens through the schedule; returns float32 logits
         ``[len(want_rows), vocab]`` for the rows ``meta.want_rows`` names."""
-        ctx = StepContext(self.dtype, meta, cache)
+        ctx = StepContext(self.dtype, meta, cache, options)
         residual = ops.embed(meta.tokens, self.embedding)
         self.position.at_embedding(ctx, residual)
         pending = None
@@ -165,4 +171,4 @@ class DecoderModel:
             h = self.final_norm.norm(ctx, residual)
         else:
             h = self.final_norm.add_norm(ctx, residual, pending)
-        return ops.linear(h, self.head, torch.float32)
+        return ops.linear(h, self.head, torch.float32, options=options)

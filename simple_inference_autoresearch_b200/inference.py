@@ -12,8 +12,9 @@ needs a ``tokenizer.json`` in that folder (read with the ``tokenizers`` package)
 always works.  ``--dtype float32`` runs the true 32-bit path.
 
 Beyond the reference: ``--model NAME --random-weights`` takes one of the configurations shipped
-with the library (``tiny-a``, ``tiny-b``, ``llama-3.2-1b``, ``llama-3.2-3b``, ``llama-3.1-8b``) with
-seeded random weights made on the GPU (``--seed``); ``--prompt-len N`` feeds N seeded random
+with the library (``tiny-a``, ``tiny-b``, ``llama-3.2-1b``, ``llama-3.2-3b``, ``llama-3.1-8b``) or
+added with ``config.register_preset``, of whatever registered architecture its config.json names, with
+seeded random weights made on the GPU (``--seed``; ``--norm-init`` overrides the configuration's rule for norm weights); ``--prompt-len N`` feeds N seeded random
 token ids; ``--batch N`` generates for N prompts at once (``--prompt-len`` draws N different
 ones, their lengths spread between N/2 and N tokens; a given prompt is repeated) and prints the token
 lists instead of streaming; ``--stop-id ID`` (repeatable) adds stop tokens to the model's own.
@@ -44,6 +45,8 @@ def main(argv=None) -> int:
                          "shipped configuration")
     ap.add_argument("--random-weights", action="store_true",
                     help="seeded random weights for the configuration --model names (a shipped name or a folder's config.json)")
+    ap.add_argument("--norm-init", choices=["ones", "ones_plus_normal"],
+                    help="with --random-weights: norm weights 1 or 1 + N(0, initializer_range) (default: the configuration's)")
     ap.add_argument("--prompt", help="prompt text (needs tokenizer.json in the model folder)")
     ap.add_argument("--prompt-ids", help="prompt as comma- or space-separated token ids")
     ap.add_argument("--prompt-len", type=int, help="a prompt of this many seeded random token ids")
@@ -66,12 +69,15 @@ def main(argv=None) -> int:
     model_dir = Path(args.model)
     tok = _tokenizer(model_dir) if model_dir.is_dir() else None
     if args.random_weights:
-        from .config import LlamaConfig, preset_path
+        from . import registry
+        from .config import preset_path
         try:
             config_file = model_dir / "config.json" if model_dir.is_dir() else preset_path(args.model)
         except FileNotFoundError as e:
             ap.error(str(e))
-        loaded = siar.init_random(siar.build_model(LlamaConfig.from_json(config_file), args.dtype, "cuda"), args.seed)
+        _arch, config = registry.resolve_path(config_file)      # the class config.json's architecture names
+        options = {"norm_weight_init": args.norm_init} if args.norm_init else {}
+        loaded = siar.init_random(siar.build_model(config, args.dtype, "cuda", **options), args.seed)
     elif not model_dir.is_dir():
         ap.error(f"--model {args.model}: no such folder (a shipped configuration needs --random-weights)")
     else:

@@ -13,12 +13,11 @@ import torch
 
 from . import build
 
+from .options import DEFAULT, KernelOptions
+
 _state = {}
-#: cap of the split along K for products with few output tiles (1 disables it)
-max_splits = 8
 _fn = None
 _fn_fused = None
-enabled = True
 
 
 def _bind():
@@ -28,7 +27,7 @@ def _bind():
         f = lib.siar_gemm_tc_bf16
         c = ctypes
         f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
-                      c.c_void_p, c.c_int, c.c_void_p]
+                      c.c_void_p, c.c_int, c.c_void_p, c.c_int]
         f.restype = c.c_int
         _fn = f
     return _fn
@@ -41,16 +40,10 @@ def _bind_fused():
         c = ctypes
         f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                       c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_float,
-                      c.c_void_p]
+                      c.c_void_p, c.c_int]
         f.restype = c.c_int
         _fn_fused = f
     return _fn_fused
-
-
-def set_pairs(mode: int) -> None:
-    """Products of many rows: two SMs on one 256 x 256 tile (cta_group::2) or one SM per 128 x 256
-    tile.  0 = never pairs, 1 = pairs from 4,096 rows on (the default), 2 = always pairs."""
-    build.load_unit("gemm_tc").siar_gemm_tc_set_pairs(int(mode))
 
 
 def _device_state(device: torch.device):
@@ -62,15 +55,17 @@ def _device_state(device: torch.device):
     return st
 
 
-def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=None, ss_out=None) -> bool:
+def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=None, ss_out=None,
+               options: KernelOptions = DEFAULT) -> bool:
     """out[M, N] = x[M, K] @ w[N, K]^T; False when the shape is refused (nothing launched).
     ``epilogue=1``: w's rows alternate (gate, up) and out[M, N/2] = silu(gate) * up.
     ``epilogue=2``: out (float32) += the product; for at most 16 rows ``ss_out`` [M, ceil(N/128)]
     also receives partial sums of squares of the new rows of out (more than 128 rows: no sums;
     17..128 rows are refused).
     ``normed`` (an ``ops.NormedResidual`` of at most 16 rows; x is None): the kernel makes the
-    activations rmsnorm(residual) * weight itself."""
-    if not enabled:
+    activations rmsnorm(residual) * weight itself.
+    ``options``: ``use_tc_gemm`` False refuses everything; ``max_splits`` and ``pair_mode`` as in ``KernelOptions``."""
+    if not options.use_tc_gemm:
         return False
     from . import ops
 
@@ -90,13 +85,13 @@ def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=
             m, k = x.shape
             extra = (None, None, 0, None, 0.0)
             xp = x.data_ptr()
-        err = _bind_fused()(xp, w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32), max_splits,
-                            int(epilogue), status, st["sms"], stream, *extra,
-                            None if ss_out is None else ss_out.data_ptr())
+        err = _bind_fused()(xp, w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
+                            options.max_splits, int(epilogue), status, st["sms"], stream, *extra,
+                            None if ss_out is None else ss_out.data_ptr(), options.pair_mode)
     else:
         m, k = x.shape
         err = _bind()(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
-                      max_splits, int(epilogue), status, st["sms"], stream)
+                      options.max_splits, int(epilogue), status, st["sms"], stream, options.pair_mode)
     if err == -1:
         return False
     if err != 0:

@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 
 from . import build
+from .options import DEFAULT, KernelOptions
 
 c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
@@ -31,7 +32,7 @@ _signatures = {
         "siar_add_rmsnorm": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
         "siar_rope_kv_write": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p, c_void_p],
+                               c_void_p, c_void_p, c_int, c_int],
         "siar_swiglu": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "siar_advance_lengths": [c_void_p, c_void_p, c_int, c_void_p],
         "siar_set_table_cells": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -41,22 +42,23 @@ _signatures = {
     },
     "attention": {
         "siar_attn_prefill": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                              c_void_p],
         "siar_attn_decode": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                             c_void_p],
+                             c_void_p, c_void_p],
         "siar_attn_decode_chunk": [],
         "siar_attn_max_head_dim": [],
     },
     "attention_mma": {
         "siar_attn_mma_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
         "siar_attn_mma_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_void_p, c_void_p],
         "siar_attn_mma_decode_rope": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int],
         "siar_attn_mma_supported": [c_int, c_int, c_int, c_int],
         "siar_attn_mma_decode_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
@@ -127,6 +129,7 @@ STATUS_MESSAGES = {
     1: "a token id outside [0, vocab_size) was fed",
     2: "a bounded device-side wait expired",
     4: "a key or a cache write met a position without a page",
+    8: "a sequence is longer than the decode step was sized for (a captured step replayed past its length bucket)",
 }
 
 
@@ -186,10 +189,6 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     return out
 
 
-#: False = the products never take over the residual add and the norm (tests compare both ways)
-fuse_residual_stream = True
-
-
 class Added:
     """Stands for a sublayer output that the product kernel has already added into the residual
     stream.  ``ss_parts`` [rows, pieces] float32 holds, for every row, partial sums of squares of
@@ -222,15 +221,17 @@ class NormedResidual:
         return add_rmsnorm(self.residual, None, self.weight, self.eps, self.dtype)
 
 
-def _fused_input(x: "NormedResidual", w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
-    if not (fuse_residual_stream and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+def _fused_input(x: "NormedResidual", w: torch.Tensor, out: torch.Tensor, epilogue: int,
+                 options: KernelOptions) -> bool:
+    if not (options.fuse_residual_stream and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and x.weight.dtype == torch.bfloat16 and x.residual.shape[0] <= 16):
         return False
     from . import gemm_tc
-    return gemm_tc.try_linear(None, w, out, epilogue=epilogue, normed=x)
+    return gemm_tc.try_linear(None, w, out, epilogue=epilogue, normed=x, options=options)
 
 
-def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Tensor] = None):
+def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Tensor] = None,
+           options: KernelOptions = DEFAULT):
     """y[M, N] = x[M, K] @ w[N, K]^T with 32-bit accumulation.
 
     ``x`` may be a ``NormedResidual``.  With ``add_to`` (the float32 residual [M, N]) the kernel may
@@ -239,7 +240,7 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Te
     if isinstance(x, NormedResidual):
         if add_to is None and out_dtype in (torch.float32, x.dtype):
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=w.device)
-            if _fused_input(x, w, out, 0):
+            if _fused_input(x, w, out, 0, options):
                 return out
         x = x.materialize()
     _need_cuda(x, w)
@@ -251,50 +252,66 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Te
         raise TypeError(f"linear: output dtype {out_dtype} with input dtype {x.dtype}")
     if x.dtype == torch.bfloat16:
         from . import gemm_tc
-        if (add_to is not None and fuse_residual_stream and out_dtype == torch.float32 and (m <= 16 or m > 128)
+        if (add_to is not None and options.fuse_residual_stream and out_dtype == torch.float32 and (m <= 16 or m > 128)
                 and add_to.dtype == torch.float32 and add_to.shape == (m, n) and add_to.is_contiguous()):
             # few rows: with the sums of squares for the norm that follows; many rows: the sum only
             ss = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device) if m <= 16 else None
-            if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss):
+            if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss, options=options):
                 return Added(ss)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     if x.dtype == torch.bfloat16:
-        if gemm_tc.try_linear(x, w, out):
+        if gemm_tc.try_linear(x, w, out, options=options):
             return out
     _launch("gemm_simt", "siar_gemm_nt_simt", _is_bf16(x.dtype), int(out_dtype == torch.float32), _ptr(x),
             _ptr(w), _ptr(out), m, n, k, 1, _stream())
     return out
 
 
-#: set to False to keep prompts' attention on the warp-level tensor-core kernel (tests compare both)
-use_tc_attention = True
-
-
-def tc_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
+def tc_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int,
+                       options: KernelOptions = DEFAULT) -> bool:
     """True when the tcgen05 kernel for prompts takes these sizes (bfloat16, head_dim 64 or 128, at
     most 128 query heads per kv head, pages of 64 tokens or a multiple)."""
-    if dtype != torch.bfloat16 or not (use_tc_attention and use_mma_attention):
+    if dtype != torch.bfloat16 or not (options.use_tc_attention and options.use_mma_attention):
         return False
     if head_dim not in (64, 128) or n_kv_heads <= 0 or n_heads % n_kv_heads:      # the unit is not even compiled for these
         return False
     return bool(_fn("attention_tc", "siar_attn_tc_supported")(n_heads, n_kv_heads, head_dim, page_tokens))
 
 
-def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, meta, n_heads: int, n_kv_heads: int,
+def rotary_layout(rotary, head_dim: int):
+    """(inv_freq, rotary_dim, interleaved) of what a position encoding's ``rotary()`` returned:
+    None (no rotation), a bare float32 tensor of head_dim/2 frequencies (the whole head, pairs
+    (i, i + head_dim/2)), or an object with ``inv_freq`` and optionally ``rotary_dim`` (only the
+    first that many dims of a head are rotated) and ``interleaved`` (pairs (2i, 2i+1))."""
+    if rotary is None:
+        return None, head_dim, False
+    inv_freq = getattr(rotary, "inv_freq", rotary)
+    rotary_dim = int(getattr(rotary, "rotary_dim", None) or 2 * inv_freq.numel())
+    interleaved = bool(getattr(rotary, "interleaved", False))
+    if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+        raise ValueError(f"rotary_dim must be even and within head_dim {head_dim}, got {rotary_dim}")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2:
+        raise ValueError(f"inv_freq must hold rotary_dim / 2 = {rotary_dim // 2} float32 frequencies, "
+                         f"got {inv_freq.numel()} of {inv_freq.dtype}")
+    return inv_freq, rotary_dim, interleaved
+
+
+def rope_kv_write(qkv: torch.Tensor, rotary, kv, meta, n_heads: int, n_kv_heads: int,
                   head_dim: int, write_kv: bool = True) -> None:
     """Rotates the q (in place) and k heads of the fused ``qkv`` rows by their
-    positions and writes k and v into the pages of ``kv`` (a cache entry)."""
+    positions and writes k and v into the pages of ``kv`` (a cache entry).  ``rotary``: see
+    ``rotary_layout``; every layout it describes is taken."""
+    inv_freq, rotary_dim, interleaved = rotary_layout(rotary, head_dim)
     _need_cuda(qkv, inv_freq, kv.k)
     n = qkv.shape[0]
     assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
     assert qkv.dtype == kv.k.dtype and n == meta.n_tokens
-    if inv_freq is not None:
-        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2
-    assert kv.k.shape[1:] == (n_kv_heads, kv.page_tokens, head_dim)
+    assert kv.k.shape[1:] == (n_kv_heads, kv.page_tokens, head_dim) and kv.v.shape == kv.k.shape, \
+        "the attention kernels take keys and values of one width"
     _launch("elementwise", "siar_rope_kv_write", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(inv_freq), _ptr(kv.k),
             _ptr(kv.v), _ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len), n,
             meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1],
-            kv.k.shape[0], int(write_kv), _ptr(status_word(qkv.device)), _stream())
+            kv.k.shape[0], int(write_kv), _ptr(status_word(qkv.device)), _stream(), rotary_dim, int(interleaved))
 
 
 _attn_consts = {}
@@ -353,12 +370,10 @@ def set_programmatic_launch(on: bool) -> None:
 
 _pdl = True
 
-#: set to False to force the CUDA-core attention kernels on the bfloat16 path (tests compare both)
-use_mma_attention = True
 
-
-def mma_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
-    if dtype != torch.bfloat16 or not use_mma_attention:
+def mma_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int,
+                        options: KernelOptions = DEFAULT) -> bool:
+    if dtype != torch.bfloat16 or not options.use_mma_attention:
         return False
     return bool(_fn("attention_mma", "siar_attn_mma_supported")(n_heads, n_kv_heads, head_dim, page_tokens))
 
@@ -368,31 +383,32 @@ def decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: 
     return n_seqs * n_heads * chunks * (head_dim + 2)
 
 
-def decode_fuses_rope(meta, dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int) -> bool:
+def decode_fuses_rope(meta, dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int,
+                      options: KernelOptions = DEFAULT) -> bool:
     """True when ``rope_and_attention`` runs one kernel for this step (one token per sequence
     on the tensor-core path); otherwise it is ``rope_kv_write`` followed by ``attention``."""
-    return bool(meta.is_decode) and fuse_decode_rope and mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim,
-                                                                              page_tokens)
+    return bool(meta.is_decode) and options.fuse_decode_rope and mma_attention_takes(
+        dtype, n_heads, n_kv_heads, head_dim, page_tokens, options)
 
 
-#: set to False to keep the rotary/cache-write kernel separate from decode attention
-fuse_decode_rope = True
-
-
-def rope_and_attention(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, meta, n_heads: int, n_kv_heads: int,
-                       head_dim: int, scale: float, write_kv: bool = True, window: Optional[int] = None) -> torch.Tensor:
+def rope_and_attention(qkv: torch.Tensor, rotary, kv, meta, n_heads: int, n_kv_heads: int,
+                       head_dim: int, scale: float, write_kv: bool = True, window: Optional[int] = None,
+                       options: KernelOptions = DEFAULT) -> torch.Tensor:
     """Rotates q and k by the tokens' positions, writes k and v to the cache entry and attends:
     what a rotary attention mixer does between its two products.  For steps of one token per
     sequence on the tensor-core path this is ONE kernel (q is rotated in registers, the new k and
-    v go to the cache and are used from shared memory); otherwise two.  ``window``: see ``attention``."""
-    if window is not None or not decode_fuses_rope(meta, qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
-        rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
-        return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=window)
+    v go to the cache and are used from shared memory); otherwise two.  The one kernel rotates whole
+    heads in pairs (i, i + head_dim/2) only: any other rotary layout (see ``rotary_layout``) takes the
+    two-kernel way.  ``window``: see ``attention``."""
+    inv_freq, rotary_dim, interleaved = rotary_layout(rotary, head_dim)
+    plain_layout = inv_freq is None or (rotary_dim == head_dim and not interleaved)
+    if window is not None or not plain_layout or not decode_fuses_rope(meta, qkv.dtype, n_heads, n_kv_heads, head_dim,
+                                                                       kv.page_tokens, options):
+        rope_kv_write(qkv, rotary, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
+        return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=window, options=options)
     _need_cuda(qkv, kv.k, inv_freq)
     check_attention_sizes(n_heads, n_kv_heads, head_dim)
     assert qkv.is_contiguous() and qkv.shape == (meta.n_seqs, (n_heads + 2 * n_kv_heads) * head_dim)
-    if inv_freq is not None:
-        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2
     out = torch.empty((meta.n_seqs, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     sms = _sm_count(qkv.device)
     f = _fn("attention_mma", "siar_attn_mma_decode_scratch_floats")
@@ -403,12 +419,12 @@ def rope_and_attention(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], kv, 
             _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len), _ptr(out), _ptr(scratch),
             _ptr(_decode_counters(qkv.device, meta.n_seqs * n_kv_heads)), _ptr(inv_freq), int(write_kv), meta.n_seqs,
             n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1], meta.max_kv_len, sms, float(scale),
-            _stream(), _ptr(status_word(qkv.device)))
+            _stream(), _ptr(status_word(qkv.device)), rotary_dim, int(interleaved))
     return out
 
 
 def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-              window: Optional[int] = None) -> torch.Tensor:
+              window: Optional[int] = None, options: KernelOptions = DEFAULT) -> torch.Tensor:
     """Causal attention of the new tokens' (already rotated) queries over the
     cache entry ``kv``; returns [N, n_heads * head_dim] in qkv's dtype.  bfloat16
     with head_dim 64 or 128 runs on the tensor cores, everything else on the CUDA cores.
@@ -421,7 +437,7 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
     out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     common = (_ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len))
     sizes = (meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1])
-    mma = window is None and mma_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens)
+    mma = window is None and mma_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens, options)
     win = int(window or 0)
     if meta.is_decode:
         if mma:
@@ -438,16 +454,17 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
             scratch = torch.empty(decode_scratch_floats(meta.n_seqs, n_heads, head_dim, meta.max_kv_len, chunk),
                                   dtype=torch.float32, device=qkv.device)
             _launch("attention", "siar_attn_decode", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
-                    _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, win, float(scale), _stream(), kernels=2)
-    elif window is None and tc_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens):
+                    _ptr(out), _ptr(scratch), *sizes, meta.max_kv_len, win, float(scale), _stream(),
+                    _ptr(status_word(qkv.device)), kernels=2)
+    elif window is None and tc_attention_takes(qkv.dtype, n_heads, n_kv_heads, head_dim, kv.page_tokens, options):
         _launch("attention_tc", "siar_attn_tc_prefill", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out), n,
                 *sizes, kv.k.shape[0], meta.max_q_len, float(scale), _ptr(status_word(qkv.device)), _stream())
     elif mma:
         _launch("attention_mma", "siar_attn_mma_prefill", _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common, _ptr(out),
-                *sizes, meta.max_q_len, float(scale), _stream())
+                *sizes, meta.max_q_len, float(scale), _stream(), _ptr(status_word(qkv.device)))
     else:
         _launch("attention", "siar_attn_prefill", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(kv.k), _ptr(kv.v), *common,
-                _ptr(out), *sizes, meta.max_q_len, win, float(scale), _stream())
+                _ptr(out), *sizes, meta.max_q_len, win, float(scale), _stream(), _ptr(status_word(qkv.device)))
     return out
 
 
@@ -463,14 +480,14 @@ def swiglu(gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
     return out
 
 
-def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, options: KernelOptions = DEFAULT) -> torch.Tensor:
     """silu(x @ Wg^T) * (x @ Wu^T) for a weight whose rows alternate (gate_0, up_0, gate_1, ...);
     returns [M, N/2] in x's dtype.  On the bfloat16 path the activation runs in the product's
     epilogue on the float32 accumulators; otherwise it is a product followed by ``swiglu``.
     ``x`` may be a ``NormedResidual``."""
     if isinstance(x, NormedResidual):
         out = torch.empty((x.shape[0], w_interleaved.shape[0] // 2), dtype=x.dtype, device=w_interleaved.device)
-        if w_interleaved.shape[0] % 2 == 0 and _fused_input(x, w_interleaved, out, 1):
+        if w_interleaved.shape[0] % 2 == 0 and _fused_input(x, w_interleaved, out, 1, options):
             return out
         x = x.materialize()
     _need_cuda(x, w_interleaved)
@@ -479,9 +496,9 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
     if x.dtype == torch.bfloat16:
         from . import gemm_tc
         out = torch.empty((x.shape[0], w_interleaved.shape[0] // 2), dtype=x.dtype, device=x.device)
-        if gemm_tc.try_linear(x, w_interleaved, out, epilogue=1):
+        if gemm_tc.try_linear(x, w_interleaved, out, epilogue=1, options=options):
             return out
-    return swiglu(linear(x, w_interleaved, x.dtype), interleaved=True)
+    return swiglu(linear(x, w_interleaved, x.dtype, options=options), interleaved=True)
 
 
 def advance_lengths(base_len: torch.Tensor, q_start: torch.Tensor, n_seqs: int) -> None:

@@ -61,18 +61,20 @@ class GroupedQueryAttention(Mixer):
     def cache_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
 
-    def extension_units(self):
-        units = ("elementwise", "attention", "attention_mma", "gemm_simt", "gemm_tc")
-        if self.head_dim in (64, 128) and self.n_heads // self.n_kv_heads <= 128:
-            units += ("attention_tc",)        # prompts of bfloat16 models with these sizes
+    def extension_units(self, dtype=None):
+        units = ("elementwise", "attention", "gemm_simt")
+        if dtype != torch.float32:            # the tensor-core units are bfloat16 only
+            units += ("attention_mma", "gemm_tc")
+            if self.head_dim in (64, 128) and self.n_heads // self.n_kv_heads <= 128:
+                units += ("attention_tc",)    # prompts of bfloat16 models with these sizes
         return units
 
     takes_deferred_norm = True
 
     def forward(self, ctx, x, cache_entry, writes_cache: bool = True):
-        qkv = ops.linear(x, self.w_qkv, ctx.dtype)
+        qkv = ops.linear(x, self.w_qkv, ctx.dtype, options=ctx.options)
         rotary = self.position.rotary() if self.position is not None else None
-        attn = ops.rope_and_attention(qkv, rotary.inv_freq if rotary is not None else None, cache_entry, ctx.meta,
+        attn = ops.rope_and_attention(qkv, rotary, cache_entry, ctx.meta,
                                       self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
-                                      write_kv=writes_cache, window=self.window)
-        return ops.linear(attn, self.w_o, torch.float32, add_to=ctx.residual)
+                                      write_kv=writes_cache, window=self.window, options=ctx.options)
+        return ops.linear(attn, self.w_o, torch.float32, add_to=ctx.residual, options=ctx.options)

@@ -95,12 +95,15 @@ BLOCKS = PartRegistry("block")
 @dataclass(frozen=True)
 class KVNeed:
     """A mixer that keeps keys and values of earlier tokens.  ``window`` = None
-    keeps all of them; an integer keeps only that many most recent ones.  Layers
+    keeps all of them; an integer keeps only that many most recent ones.  ``v_head_dim``:
+    the width of a value when it differs from a key's (None: the same; the attention kernels of
+    this library take equal widths only, a mixer with its own kernels may differ).  Layers
     whose needs compare equal share one storage group."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -128,8 +131,9 @@ class Part:
         """Take ownership of the tensors named by ``tensor_specs`` (already on the
         device, already in the dtype their role asks for)."""
 
-    def extension_units(self) -> Sequence[str]:
-        """Names of the CUDA source units this part launches kernels from."""
+    def extension_units(self, dtype: Optional[torch.dtype] = None) -> Sequence[str]:
+        """Names of the CUDA source units this part launches kernels from when the model computes
+        in ``dtype`` (None: in any dtype)."""
         return ()
 
 
@@ -151,9 +155,10 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     def rotary(self):
-        """Rotary parameters for a mixer that rotates queries and keys
-        (an object with ``inv_freq``: float32 [rotary_dim/2] on the device), or
-        None when positions enter the model elsewhere."""
+        """Rotary parameters for a mixer that rotates queries and keys: an object with
+        ``inv_freq`` (float32 [rotary_dim/2] on the device), ``rotary_dim`` (how many leading dims
+        of a head are rotated) and ``interleaved`` (pairs (2i, 2i+1) instead of (i, i + rotary_dim/2)),
+        see ``parts.rope.RotaryParams``; or None when positions enter the model elsewhere."""
         return None
 
     def at_embedding(self, ctx, residual: torch.Tensor) -> None:

@@ -18,6 +18,14 @@ from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, PartSpec, TensorSpec
 
 
+def _units_of(part, dtype):
+    """A part's units for ``dtype``; parts written before the argument existed take none."""
+    try:
+        return part.extension_units(dtype)
+    except TypeError:
+        return part.extension_units()
+
+
 @BLOCKS.register("prenorm")
 class PreNormBlock(Block):
     """``mixer``, ``feed_forward``, ``mixer_norm`` and ``ffn_norm`` are PartSpecs whose
@@ -45,8 +53,8 @@ class PreNormBlock(Block):
         for p in self._parts:
             p.load(tensors)
 
-    def extension_units(self):
-        return tuple(u for p in self._parts for u in p.extension_units())
+    def extension_units(self, dtype=None):
+        return tuple(u for p in self._parts for u in _units_of(p, dtype))
 
     def cache_need(self):
         return self.mixer.cache_need()

@@ -44,11 +44,12 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
         self.w_down = tensors[p + "down_proj.weight"].contiguous()
 
-    def extension_units(self):
-        return ("elementwise", "gemm_simt", "gemm_tc")
+    def extension_units(self, dtype=None):
+        # the tcgen05 products are bfloat16 only; the CUDA-core product is the 32-bit path and the fallback
+        return ("elementwise", "gemm_simt") + (() if dtype == torch.float32 else ("gemm_tc",))
 
     takes_deferred_norm = True
 
     def forward(self, ctx, x):
-        f = ops.linear_swiglu(x, self.w_gate_up)
-        return ops.linear(f, self.w_down, torch.float32, add_to=ctx.residual)
+        f = ops.linear_swiglu(x, self.w_gate_up, options=ctx.options)
+        return ops.linear(f, self.w_down, torch.float32, add_to=ctx.residual, options=ctx.options)

@@ -38,7 +38,7 @@ class RMSNorm(Norm):
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.prefix + "weight"].contiguous()
 
-    def extension_units(self):
+    def extension_units(self, dtype=None):
         return ("elementwise",)
 
     def norm(self, ctx, residual: torch.Tensor) -> torch.Tensor:

@@ -32,6 +32,7 @@ from .base import POSITION_ENCODINGS, PositionEncoding
 
 
 def rotary_inv_freq(head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
+    """``head_dim`` here is the width that is rotated (the whole head for Llama)."""
     idx = torch.arange(0, head_dim, 2, dtype=torch.float32)
     freqs = 1.0 / (theta ** (idx / head_dim))
     if scaling and scaling.get("rope_type", "default") == "llama3":
@@ -54,21 +55,32 @@ def rotary_inv_freq(head_dim: int, theta: float, scaling: Optional[dict]) -> tor
 
 
 class RotaryParams:
-    def __init__(self, inv_freq: torch.Tensor):
-        self.inv_freq = inv_freq
+    """What a rotating mixer needs to know: the frequencies (float32 [rotary_dim / 2], on the
+    device), how many leading dims of a head are rotated, and how they pair up: split-half
+    (i, i + rotary_dim/2), the Llama way, or ``interleaved`` (2i, 2i+1)."""
+
+    def __init__(self, inv_freq: torch.Tensor, rotary_dim: int, interleaved: bool = False):
+        self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, int(rotary_dim), bool(interleaved)
 
 
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEncoding(PositionEncoding):
     """``scaling``: None or a dict with rope_type/factor/low_freq_factor/
-    high_freq_factor/original_max_position_embeddings."""
+    high_freq_factor/original_max_position_embeddings.  ``rotary_dim`` (default: the whole head)
+    and ``interleaved`` (default: split-half pairs) are not Llama options (the reference's model
+    always rotates the whole head in split-half pairs, ops/rope.py:188-203; its kernel also knows
+    interleaved pairs, kernels/rope_kernel.py:139-152); they are here so that another architecture's
+    rotary layout is a parameter, not another kernel."""
 
     def __init__(self, prefix: str = "", *, head_dim: int, theta: float, scaling: Optional[dict] = None,
-                 device=None):
+                 rotary_dim: Optional[int] = None, interleaved: bool = False, device=None):
         super().__init__(prefix)
         self.head_dim, self.theta, self.scaling = int(head_dim), float(theta), scaling
-        inv = rotary_inv_freq(self.head_dim, self.theta, self.scaling)
-        self._params = RotaryParams(inv.to(device) if device is not None else inv)
+        self.rotary_dim = int(rotary_dim) if rotary_dim else self.head_dim
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
+            raise ValueError(f"rotary_dim must be even and within head_dim {self.head_dim}, got {rotary_dim}")
+        inv = rotary_inv_freq(self.rotary_dim, self.theta, self.scaling)
+        self._params = RotaryParams(inv.to(device) if device is not None else inv, self.rotary_dim, interleaved)
 
     def rotary(self) -> RotaryParams:
         return self._params

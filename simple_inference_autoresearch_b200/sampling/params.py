@@ -4,7 +4,8 @@ negative one is an error (sampling.py:58-62); ``top_k`` <= 0 or >= vocab disable
 top-k; ``top_p`` >= 1 disables the nucleus and <= 0 keeps only the top token.
 ``seed`` is per request: the reference draws from torch's global generator, so a
 request's tokens depend on what else is in the batch; here the uniform for a
-request's n-th token is a function of (seed, n) alone.
+request's n-th token is a function of (seed, request id, n) alone, the request id being the
+caller's (``Engine.generate(request_ids=...)``) or, by default, the prompt's index in the call.
 """
 
 from __future__ import annotations
@@ -35,10 +36,10 @@ GREEDY = SamplingParams(temperature=0.0)
 _MASK64 = (1 << 64) - 1
 
 
-def request_seed(seed: int, request_index: int) -> int:
+def request_seed(seed: int, request_id: int) -> int:
     """64-bit seed of one request: requests that share a user seed still draw
     different streams.  Returned as a signed 64-bit value (it travels in an int64 tensor)."""
-    z = (int(seed) * 0x9E3779B97F4A7C15 + (int(request_index) + 1) * 0xD1B54A32D192ED03) & _MASK64
+    z = (int(seed) * 0x9E3779B97F4A7C15 + (int(request_id) + 1) * 0xD1B54A32D192ED03) & _MASK64
     z ^= z >> 32
     z = (z * 0xD6E8FEB86659FD93) & _MASK64
     z ^= z >> 32

@@ -2,8 +2,9 @@
 into a model folder (``config.json`` + ``model.safetensors``).
 
 The reference has no such mode (its benches load the real checkpoint).  Every
-tensor is drawn on its own from ``(seed, tensor name)``, in float32, so that any
-subset of the tensors, in any order, reproduces the same values:
+tensor is drawn on its own from ``(seed, tensor name)``, in float32, by a counter-based
+generator whose arithmetic is the same on every device, so that any subset of the
+tensors, in any order, on the CPU or on the GPU, reproduces the same bits:
 matrices and embeddings N(0, std), norm weights 1 or 1 + N(0, std) as the part's
 ``TensorSpec`` says.
 """
@@ -25,24 +26,120 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
-def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
+# ---- a counter-based normal generator that gives the same bits on the CPU and on the GPU
+#
+# Element i of a tensor is a function of (tensor key, i) alone: splitmix64 of the counter gives 64
+# bits, of which two 24-bit fields become two uniforms, and Box-Muller turns those into one normal
+# deviate.  Every step is a single torch operation that is exactly rounded on both devices (integer
+# arithmetic, float32 add / multiply / divide / sqrt / floor): the logarithm and the cosine are
+# evaluated by series written out below, not by the devices' own libraries, which differ in the
+# last bit.  So ``random_tensor(spec, seed, dtype, "cpu")`` and ``(..., "cuda")`` hold identical bits,
+# as do a tensor drawn whole and the same tensor drawn in pieces.
+
+_CHUNK = 1 << 24        # elements drawn at a time (bounds the temporaries)
+
+
+def _i64(x: int) -> int:
+    """A 64-bit pattern as the signed integer torch's int64 holds."""
+    x &= (1 << 64) - 1
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+def _lshr(z: torch.Tensor, n: int) -> torch.Tensor:
+    """Logical right shift of int64 (torch's shift is arithmetic)."""
+    return (z >> n) & ((1 << (64 - n)) - 1)
+
+
+def _splitmix64(counter: torch.Tensor, key: int) -> torch.Tensor:
+    z = counter * _i64(0x9E3779B97F4A7C15) + _i64(key)
+    z = (z ^ _lshr(z, 30)) * _i64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lshr(z, 27)) * _i64(0x94D049BB133111EB)
+    return z ^ _lshr(z, 31)
+
+
+def _horner(x: torch.Tensor, coeffs) -> torch.Tensor:
+    """coeffs[0] + x (coeffs[1] + x (...)), one multiply and one add at a time (never fused)."""
+    acc = torch.full_like(x, coeffs[-1])
+    for c in reversed(coeffs[:-1]):
+        acc = acc * x
+        acc = acc + c
+    return acc
+
+
+_LN2_HI = 0.693145751953125          # the leading bits of ln 2: exact in float32, times |e| <= 24 exact too
+_LN2_LO = 1.42860682030941723212e-6
+_SQRT2 = 1.4142135381698608          # float32(sqrt 2)
+# ln m = 2 s (1 + s^2/3 + s^4/5 + ...), s = (m - 1) / (m + 1), for m in [1/sqrt 2, sqrt 2]: s^2 <= 0.0295
+_ATANH = [1.0, 1.0 / 3, 1.0 / 5, 1.0 / 7, 1.0 / 9, 1.0 / 11, 1.0 / 13]
+# cos x and sin x / x in powers of x^2, for x in [0, pi/2]
+_COS = [1.0, -1.0 / 2, 1.0 / 24, -1.0 / 720, 1.0 / 40320, -1.0 / 3628800, 1.0 / 479001600, -1.0 / 87178291200,
+        1.0 / 20922789888000]
+_SIN = [1.0, -1.0 / 6, 1.0 / 120, -1.0 / 5040, 1.0 / 362880, -1.0 / 39916800, 1.0 / 6227020800,
+        -1.0 / 1307674368000, 1.0 / 355687428096000]
+_HALF_PI = 1.5707963705062866        # float32(pi / 2)
+
+
+def _neg_log(u: torch.Tensor) -> torch.Tensor:
+    """-ln u for float32 u in (0, 1]."""
+    bits = u.view(torch.int32)
+    e = ((bits >> 23) & 0xFF) - 127
+    m = ((bits & 0x7FFFFF) | 0x3F800000).view(torch.float32)          # in [1, 2)
+    big = m > _SQRT2
+    m = torch.where(big, m * 0.5, m)
+    e = torch.where(big, e + 1, e).to(torch.float32)
+    s = (m - 1.0) / (m + 1.0)
+    ln_m = (s + s) * _horner(s * s, _ATANH)
+    return -(e * _LN2_HI + (e * _LN2_LO + ln_m))
+
+
+def _cos_turns(t: torch.Tensor) -> torch.Tensor:
+    """cos(2 pi t) for float32 t in [0, 1) on a 2^-24 grid: the quadrant is split off exactly."""
+    t4 = t * 4.0
+    quad = torch.floor(t4)
+    x = (t4 - quad) * _HALF_PI
+    x2 = x * x
+    c = _horner(x2, _COS)
+    sn = x * _horner(x2, _SIN)
+    return torch.where(quad == 0, c, torch.where(quad == 1, -sn, torch.where(quad == 2, -c, sn)))
+
+
+def standard_normal(n: int, key: int, device="cpu", start: int = 0) -> torch.Tensor:
+    """Elements ``start .. start + n - 1`` of the stream ``key``: float32 N(0, 1) deviates (to about
+    1e-6; 24-bit uniforms, so |z| <= 5.8), bit-identical on every device."""
     dev = torch.device(device)
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(_tensor_seed(seed, spec.name))
+    counter = torch.arange(start + 1, start + n + 1, dtype=torch.int64, device=dev)
+    z = _splitmix64(counter, key)
+    u1 = (_lshr(z, 40) + 1).to(torch.float32) * (1.0 / 16777216.0)           # (0, 1]
+    u2 = (_lshr(z, 16) & 0xFFFFFF).to(torch.float32) * (1.0 / 16777216.0)    # [0, 1)
+    r = torch.sqrt(_neg_log(u1) * 2.0)
+    return r * _cos_turns(u2)
+
+
+def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
+    """The tensor ``spec`` names, drawn from ``(seed, spec.name)``: the same bits whatever the
+    device, and whatever else is drawn before or after it."""
+    dev = torch.device(device)
     shape = tuple(spec.shape)
     if spec.role == "int":
         return torch.zeros(shape, dtype=torch.int32, device=dev)
     if spec.init == "ones":
-        t = torch.ones(shape, dtype=torch.float32, device=dev)
-    elif spec.init == "zeros":
-        t = torch.zeros(shape, dtype=torch.float32, device=dev)
-    elif spec.init == "normal":
-        t = torch.randn(shape, generator=gen, dtype=torch.float32, device=dev) * spec.std
-    elif spec.init == "ones_plus_normal":
-        t = 1.0 + torch.randn(shape, generator=gen, dtype=torch.float32, device=dev) * spec.std
-    else:
+        return torch.ones(shape, dtype=dtype, device=dev)
+    if spec.init == "zeros":
+        return torch.zeros(shape, dtype=dtype, device=dev)
+    if spec.init not in ("normal", "ones_plus_normal"):
         raise ValueError(f"unknown init {spec.init!r} for {spec.name}")
-    return t.to(dtype)
+    n = 1
+    for d in shape:
+        n *= int(d)
+    key = _tensor_seed(seed, spec.name)
+    out = torch.empty(n, dtype=dtype, device=dev)
+    for start in range(0, n, _CHUNK):
+        m = min(_CHUNK, n - start)
+        t = standard_normal(m, key, dev, start) * float(spec.std)
+        if spec.init == "ones_plus_normal":
+            t = t + 1.0
+        out[start:start + m] = t.to(dtype)
+    return out.view(shape)
 
 
 def random_tensors(specs: Sequence[TensorSpec], seed: int, dtype: torch.dtype, device="cpu") -> Dict[str, torch.Tensor]:

@@ -43,7 +43,7 @@ def add_rmsnorm(residual, delta, weight, eps, out_dtype):
     return (residual * torch.rsqrt(var + eps) * weight.to(torch.float32)).to(out_dtype)
 
 
-def linear(x, w, out_dtype, add_to=None):
+def linear(x, w, out_dtype, add_to=None, options=None):
     return (x.to(torch.float32) @ w.to(torch.float32).T).to(out_dtype)
 
 
@@ -58,15 +58,35 @@ def _positions(meta):
     return pos, seq
 
 
-def rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=True):
+def rotate(x, positions, inv_freq, rotary_dim, interleaved):
+    """x: [T, heads, D]; the first ``rotary_dim`` dims of every head rotated by position *
+    inv_freq, in pairs (i, i + rotary_dim/2) or, ``interleaved``, (2i, 2i+1); the rest untouched."""
+    ang = torch.outer(torch.as_tensor(positions, dtype=torch.float32), inv_freq.cpu().float())
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    out = x.clone()
+    half = rotary_dim // 2
+    if interleaved:
+        a, c = x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2]
+        out[..., 0:rotary_dim:2] = a * cos - c * sin
+        out[..., 1:rotary_dim:2] = c * cos + a * sin
+    else:
+        a, c = x[..., :half], x[..., half:rotary_dim]
+        out[..., :half] = a * cos - c * sin
+        out[..., half:rotary_dim] = c * cos + a * sin
+    return out
+
+
+def rope_kv_write(qkv, rotary, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=True):
     n = qkv.shape[0]
     pos, seq = _positions(meta)
     x = qkv.view(n, n_heads + 2 * n_kv_heads, head_dim).to(torch.float32)
     q, k, v = x[:, :n_heads], x[:, n_heads:n_heads + n_kv_heads], x[:, n_heads + n_kv_heads:]
-    if inv_freq is not None:
-        cos, sin = plain_llama.rope_tables(torch.tensor(pos), inv_freq.cpu())
-        q = plain_llama.rope_apply(q, cos, sin)
-        k = plain_llama.rope_apply(k, cos, sin)
+    if rotary is not None:
+        inv_freq = getattr(rotary, "inv_freq", rotary)
+        rotary_dim = int(getattr(rotary, "rotary_dim", None) or 2 * inv_freq.numel())
+        interleaved = bool(getattr(rotary, "interleaved", False))
+        q = rotate(q, pos, inv_freq, rotary_dim, interleaved)
+        k = rotate(k, pos, inv_freq, rotary_dim, interleaved)
     qkv.view(n, n_heads + 2 * n_kv_heads, head_dim)[:, :n_heads] = q.to(qkv.dtype)
     if not write_kv:
         return
@@ -89,7 +109,7 @@ def _gather_kv(kv, slot, length):
     return k.to(torch.float32), v.to(torch.float32)
 
 
-def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=None):
+def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=None, options=None):
     n = qkv.shape[0]
     out = torch.zeros(n, n_heads * head_dim, dtype=torch.float32)
     q_all = qkv.view(n, n_heads + 2 * n_kv_heads, head_dim)[:, :n_heads].to(torch.float32)
@@ -109,8 +129,9 @@ def attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=None):
     return out.to(qkv.dtype)
 
 
-def rope_and_attention(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, scale, write_kv=True, window=None):
-    rope_kv_write(qkv, inv_freq, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
+def rope_and_attention(qkv, rotary, kv, meta, n_heads, n_kv_heads, head_dim, scale, write_kv=True, window=None,
+                       options=None):
+    rope_kv_write(qkv, rotary, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
     return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=window)
 
 
@@ -121,7 +142,7 @@ def swiglu(gate_up, interleaved=False):
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
 
 
-def linear_swiglu(x, w_interleaved):
+def linear_swiglu(x, w_interleaved, options=None):
     return swiglu(linear(x, w_interleaved, torch.float32), interleaved=True).to(x.dtype)
 
 

@@ -156,11 +156,13 @@ def block(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, c: dict, inv_freq
 
 # ----------------------------------------------------------------------------- whole model
 def forward(weights: Dict[str, torch.Tensor], raw_config: dict, tokens: Sequence[int],
-            schedule: Optional[List[tuple]] = None, windows: Optional[dict] = None) -> torch.Tensor:
+            schedule: Optional[List[tuple]] = None, windows: Optional[dict] = None,
+            rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence (model/llama.py:170-199,
     without its last-position slice).  ``schedule``: optional run order as
     (layer, cache_entry, writes_cache) tuples; default layer 0..L-1.  ``windows``: layer -> key
-    window, for tests of windowed layers only (see ``attention_causal``)."""
+    window, for tests of windowed layers only (see ``attention_causal``).  ``rows``: the positions
+    whose logits are returned ([len(rows), V]; the reference keeps the last one, model/llama.py:189-191)."""
     windows = windows or {}
     c = parse_config(raw_config)
     w = {k: v.to(torch.float32) for k, v in weights.items()}
@@ -178,6 +180,8 @@ def forward(weights: Dict[str, torch.Tensor], raw_config: dict, tokens: Sequence
                 stored[entry] = kv
             else:
                 x = block(x, w, layer, c, inv_freq, kv_override=stored[entry])
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rmsnorm(x, w["model.norm.weight"], c["eps"])             # model/llama.py:194
     head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]   # ops/embedding.py:109-126
     return x @ head.T

@@ -31,6 +31,6 @@ def test_a_cache_too_small_for_the_prompt_and_the_steps_is_refused():
     assert p.returncode == 2 and "holds no prompt" in p.stdout
 
 
-def test_unknown_preset_is_refused_by_the_parser():
+def test_unknown_preset_is_refused_with_the_names_there_are():
     p = run_bench("--model", "llama-9-900b")
-    assert p.returncode == 2 and "invalid choice" in p.stderr
+    assert p.returncode == 2 and "no preset 'llama-9-900b'" in p.stdout and "llama-3.1-8b" in p.stdout

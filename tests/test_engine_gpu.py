@@ -9,11 +9,17 @@ import torch
 
 import simple_inference_autoresearch_b200 as siar
 from simple_inference_autoresearch_b200 import SamplingParams, StepEntry
+from simple_inference_autoresearch_b200.engine import generation
+from simple_inference_autoresearch_b200.sampling.params import GREEDY, request_seed
 from tests import plain_llama, tiny_configs
 
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
+NAMES = "ABCDE"
+#: the configurations whose heads have real sizes (64 and 128): in bfloat16 their attention runs on
+#: the tensor-core kernels and their products on the tcgen05 kernel, as the 8B shape's do
+WIDE = "DE"
 
 # Largest |logit difference| allowed against the plain float32 implementation
 # (run on the same stored weights), relative to the largest |logit| of the
@@ -36,7 +42,7 @@ def prompts(vocab, lengths, seed=0):
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     tmp = tmp_path_factory.mktemp("models")
-    return {n: tiny_configs.make_folder(tmp, n, seed=11 + i) for i, n in enumerate("ABC")}
+    return {n: tiny_configs.make_folder(tmp, n, seed=11 + i) for i, n in enumerate(NAMES)}
 
 
 @pytest.fixture(scope="module")
@@ -60,11 +66,12 @@ def engine_for(folders, name, dtype, **kw):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABC")
+@pytest.mark.parametrize("name", NAMES)
 def test_whole_requests(folders, oracle, name, dtype):
     eng = engine_for(folders, name, dtype)
     vocab = tiny_configs.CONFIGS[name]["vocab_size"]
-    for toks in prompts(vocab, [1, 5, 40, 97]):
+    # the longer prompts span several query tiles of the tensor-core prompt attention
+    for toks in prompts(vocab, [1, 5, 40, 97] + ([129, 300] if name in WIDE else [])):
         s = eng.open()
         out = eng.step([StepEntry(s, toks, range(len(toks)))])
         close(out, oracle(name, toks), dtype, f"whole {len(toks)}")
@@ -72,11 +79,12 @@ def test_whole_requests(folders, oracle, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABC")
+@pytest.mark.parametrize("name", NAMES)
 def test_last_32_tokens_one_by_one(folders, oracle, name, dtype):
     eng = engine_for(folders, name, dtype)
     vocab = tiny_configs.CONFIGS[name]["vocab_size"]
-    for toks in prompts(vocab, [33, 70, 100], seed=1):
+    # 600 tokens: the single tokens read more than one chunk of keys
+    for toks in prompts(vocab, [33, 70, 100] + ([200, 600] if name in WIDE else []), seed=1):
         s = eng.open()
         head = len(toks) - 32
         outs = [eng.step([StepEntry(s, toks[:head], range(head))])]
@@ -87,15 +95,20 @@ def test_last_32_tokens_one_by_one(folders, oracle, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "ABC")
+@pytest.mark.parametrize("name", NAMES)
 def test_unequal_batches_one_after_another(folders, oracle, name, dtype):
-    """Three batches on a cache that only holds one of them at a time: prompts of
-    unequal lengths start together, then one token each; shorter requests end
-    earlier and free their slot, which the next batch takes."""
+    """Three batches (five with the longer prompts of the wide configurations) on a cache that
+    only holds one of them at a time: prompts of unequal lengths start together, then one token
+    each; shorter requests end earlier and free their slot, which the next batch takes."""
     vocab = tiny_configs.CONFIGS[name]["vocab_size"]
-    eng = engine_for(folders, name, dtype, max_batch=4, max_tokens=4 * 128)
+    batches = [[5, 11, 17, 60], [1, 7, 23, 40], [90, 2, 64]]
+    max_tokens = 4 * 128
+    if name in WIDE:
+        batches += [[300, 129, 64, 513], [100, 700, 33]]
+        max_tokens = 18 * 64                # the pages of the largest batch, no more
+    eng = engine_for(folders, name, dtype, max_batch=4, max_tokens=max_tokens)
     seen_slots = []
-    for bi, lens in enumerate([[5, 11, 17, 60], [1, 7, 23, 40], [90, 2, 64]]):
+    for bi, lens in enumerate(batches):
         reqs = prompts(vocab, lens, seed=20 + bi)
         tails = [min(len(r) - 1, 3 + 2 * i) for i, r in enumerate(reqs)]   # tokens fed one by one
         slots = [eng.open() for _ in reqs]
@@ -145,12 +158,12 @@ def test_padding_changes_nothing(folders, oracle, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(folders, oracle, dtype):
-    """300 single-token steps after a short prompt: crosses pages (64), attention
-    tiles (32) and the decode chunk (256)."""
-    name = "C"
+@pytest.mark.parametrize("name", "CDE")
+def test_long_decoding(folders, oracle, name, dtype):
+    """300 single-token steps after a short prompt (690 for the wide configurations): crosses pages
+    (64), attention tiles (32, 16), decode chunks (128, 256) and 512 keys."""
     vocab = tiny_configs.CONFIGS[name]["vocab_size"]
-    toks = prompts(vocab, [310], seed=9)[0]
+    toks = prompts(vocab, [700 if name in WIDE else 310], seed=9)[0]
     eng = engine_for(folders, name, dtype, max_batch=2)
     s = eng.open()
     outs = [eng.step([StepEntry(s, toks[:10], range(10))])]
@@ -160,7 +173,7 @@ def test_long_decoding(folders, oracle, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", "AB")
+@pytest.mark.parametrize("name", "ABDE")
 def test_first_tokens_of_a_sequence(folders, oracle, name, dtype):
     vocab = tiny_configs.CONFIGS[name]["vocab_size"]
     toks = prompts(vocab, [4], seed=3)[0]
@@ -168,6 +181,136 @@ def test_first_tokens_of_a_sequence(folders, oracle, name, dtype):
     s = eng.open()
     outs = [eng.step([StepEntry(s, [t], [0])]) for t in toks]
     close(torch.cat(outs), oracle(name, toks), dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,n_seqs", [("B", 5), ("D", 24), ("E", 40), ("D", 70), ("E", 9)])
+def test_captured_decode_steps_give_the_plain_logits(folders, oracle, name, n_seqs, dtype):
+    """Decode steps through ``Engine.run`` with CUDA graphs on, fed the requests' own tokens: the
+    logits of every captured step (its static output buffer) against the plain implementation.
+    Prompts of unequal lengths start together; the sequences end at different times, so the batch
+    shrinks through many sizes (9 .. 70 live sequences: every tile width of the few-rows products);
+    the longest sequence crosses 512 keys while it decodes (a second length bucket); a second batch
+    then takes the slots and pages of the first."""
+    vocab = tiny_configs.CONFIGS[name]["vocab_size"]
+    wide = name in WIDE
+    g = torch.Generator().manual_seed(100 + n_seqs)
+    lens = torch.randint(2, 150 if wide else 60, (n_seqs,), generator=g).tolist()
+    tails = [min(n - 1, 1 + (5 * i) % 11) for i, n in enumerate(lens)]
+    if wide:
+        lens[0], tails[0] = 517, 12                      # 505 keys after the prompt step, 517 at the end
+    pages = sum(-(-n // 64) for n in lens)
+    eng = engine_for(folders, name, dtype, max_batch=n_seqs, max_tokens=64 * pages, use_cuda_graph=True)
+    for rnd_i in range(2):
+        toks = prompts(vocab, lens, seed=40 + rnd_i)
+        reqs = [generation.Request(t, 0, GREEDY, index=i) for i, t in enumerate(toks)]
+        for r in reqs:
+            r.slot = eng.open()
+        heads = [len(t) - tl for t, tl in zip(toks, tails)]
+        got = [[] for _ in reqs]
+        out = eng.step([StepEntry(r.slot, t[:h], range(h)) for r, t, h in zip(reqs, toks, heads)])
+        o = 0
+        for i, h in enumerate(heads):
+            got[i].append(out[o:o + h].cpu()); o += h
+        sizes = set()
+        for k in range(max(tails)):
+            for r, tl in zip(reqs, tails):
+                if r.slot is not None and k >= tl:
+                    eng.close(r.slot); r.slot = None
+            live = [i for i, tl in enumerate(tails) if k < tl]
+            eng.run([reqs[i] for i in live], [[toks[i][heads[i] + k]] for i in live])
+            step_logits = eng.last_logits()
+            assert step_logits.shape == (len(live), vocab)
+            step_logits = step_logits.cpu()
+            for j, i in enumerate(live):
+                got[i].append(step_logits[j:j + 1])
+            sizes.add(len(live))
+        for r in reqs:
+            if r.slot is not None:
+                eng.close(r.slot); r.slot = None
+        assert len(eng._graphs) >= 2                         # captured steps did run
+        for i, t in enumerate(toks):
+            close(torch.cat(got[i]), oracle(name, t), dtype, f"round {rnd_i} request {i} of {n_seqs}")
+        assert eng.cache.slots.held == 0 and all(gr.pages.held == 0 for gr in eng.cache.groups)
+    if wide:
+        assert len({b for (_, b) in eng._graphs}) == 2, "the 512-key bucket edge was not crossed"
+
+
+def test_more_sequences_than_the_captured_buffers_hold(folders):
+    """``run`` with more sequences than ``max_batch``: the buffers of the captured steps are made
+    again, and the steps captured against the old ones go with them (a later step with an earlier
+    batch size would otherwise replay a graph that reads the old buffers)."""
+    name = "A"
+    vocab = tiny_configs.CONFIGS[name]["vocab_size"]
+    toks = prompts(vocab, [6, 9, 4, 12, 7], seed=31)
+    loaded = siar.load_model(folders[name], device="cuda", dtype=torch.float32)
+    drawn = {}
+    for graph in (True, False):
+        eng = siar.Engine(loaded.model, max_batch=2, max_slots=8, max_seq_len=64, use_cuda_graph=graph)
+        reqs = [generation.Request(t, 0, GREEDY, index=i) for i, t in enumerate(toks)]
+        for r in reqs:
+            r.slot = eng.open()
+        eng.step([StepEntry(r.slot, t[:-1]) for r, t in zip(reqs, toks)])
+        feed = {i: t[-1] for i, t in enumerate(toks)}
+        out = []
+        for group in ([0], [1, 2, 3, 4], [0], [1, 2], [0, 3, 4, 1]):     # 1, then 4 (> max_batch), then 1 again
+            res = eng.run([reqs[i] for i in group], [[feed[i]] for i in group])
+            for i, t in zip(group, res):
+                feed[i] = t
+            out.append(res)
+        drawn[graph] = out
+    assert drawn[True] == drawn[False]
+
+
+def plain_check_draw(logits_row, params, u, tok, what=""):
+    """The token the engine drew from ``logits_row`` must be the plain sampler's choice for the
+    same uniform, or (the uniform within rounding of an edge of the cumulative distribution)
+    a kept token whose interval reaches ``u`` within 1e-5."""
+    x = logits_row.double().cpu()
+    if params.temperature > 0 and 0 < params.top_k < x.numel():
+        # tokens outside the k largest have probability zero: the plain sampler on the candidates
+        # alone (kept in token order; ten more than k, so that tokens tied with the k-th are all
+        # there) is the plain sampler on the whole row
+        cand = sorted(torch.topk(x, min(x.numel(), params.top_k + 10)).indices.tolist())
+    else:
+        cand = list(range(x.numel()))
+    sub = x[cand]
+    want = cand[plain_llama.sample(sub, params.temperature, params.top_k, params.top_p, u)]
+    if tok == want:
+        return
+    assert tok in cand, f"{what}: drew token {tok}, outside the candidates"
+    probs = plain_llama.kept_probabilities(sub, params.temperature, params.top_k, params.top_p)
+    cdf = torch.cumsum(probs, 0)
+    j = cand.index(tok)
+    assert probs[j] > 0, f"{what}: drew token {tok}, which the plain sampler does not keep"
+    lo = cdf[j] - probs[j]
+    assert lo - 1e-5 <= u <= cdf[j] + 1e-5, (what, tok, want, u, float(lo), float(cdf[j]))
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_sampled_generation_draws_what_the_plain_sampler_draws(folders, graph):
+    """Configuration B, float32, 4 prompts of 1, 7, 23 and 40 tokens, 12 tokens each at
+    temperature 0.8 (and once with top-k and top-p): every drawn token against the plain
+    implementation's logits for the tokens so far and the plain sampler fed the same counter
+    uniform; and a request repeated alone under its request id draws the same tokens."""
+    name = "B"
+    raw, w = tiny_configs.read_folder(folders[name])
+    reqs = prompts(raw["vocab_size"], [1, 7, 23, 40], seed=6)
+    loaded = siar.load_model(folders[name], device="cuda", dtype=torch.float32)
+    eng = siar.build_engine(loaded, max_batch=4, max_seq_len=128, use_cuda_graph=graph)
+    for params in (SamplingParams(temperature=0.8, seed=123), SamplingParams(0.8, 20, 0.9, seed=7)):
+        ids = [11, 3, 8, 5]
+        outs = eng.generate(reqs, params, max_new_tokens=12, ignore_eos=True, request_ids=ids)
+        for r, o, rid in zip(reqs, outs, ids):
+            assert len(o) == 12
+            seed64 = request_seed(params.seed, rid)
+            for n, tok in enumerate(o):
+                logits = plain_llama.forward(w, raw, list(r) + o[:n])[-1]
+                plain_check_draw(logits, params, plain_llama.counter_uniform(seed64, n), tok, f"request {rid} token {n}")
+        # the third request alone, at index 0 of its own call, under its id
+        eng1 = siar.build_engine(loaded, max_batch=1, max_seq_len=128, use_cuda_graph=graph)
+        assert eng1.generate([reqs[2]], params, max_new_tokens=12, ignore_eos=True, request_ids=[ids[2]])[0] == outs[2]
+        assert eng.generate(reqs, params, max_new_tokens=12, ignore_eos=True, request_ids=ids) == outs
 
 
 def plain_greedy(folder, prompt, n, stop=()):
@@ -244,11 +387,11 @@ def test_generation_stops_at_stop_tokens_and_samples_reproducibly(folders):
     a = eng.generate(reqs, p, max_new_tokens=12, ignore_eos=True)
     b = eng.generate(reqs, p, max_new_tokens=12, ignore_eos=True)
     assert a == b
-    # a request draws the same tokens alone as in the batch (per-request counter RNG);
-    # request index 2 alone is index 0, so give it the seed stream of index 2 explicitly
+    # a request draws the same tokens alone as in the batch (per-request counter RNG): the request
+    # at index 2, alone at index 0 of another call, under request id 2
     eng1 = siar.build_engine(loaded, max_batch=1, max_seq_len=128, use_cuda_graph=False)
-    alone = eng1.generate([reqs[0]], p, max_new_tokens=12, ignore_eos=True)
-    assert alone[0] == a[0]
+    alone = eng1.generate([reqs[2]], p, max_new_tokens=12, ignore_eos=True, request_ids=[2])
+    assert alone[0] == a[2]
 
 
 def test_programmatic_launch_on_and_off_give_the_same_tokens_and_logits(folders):
@@ -273,7 +416,7 @@ def test_programmatic_launch_on_and_off_give_the_same_tokens_and_logits(folders)
     assert torch.equal(results[0][1], results[1][1]) and torch.equal(results[0][1], results[2][1])
 
 
-@pytest.mark.parametrize("name", "ABC")
+@pytest.mark.parametrize("name", NAMES)
 def test_products_inside_the_residual_stream_change_rounding_only(folders, oracle, name):
     """Decode steps with the residual add and the norm inside the products, and with the separate
     norm kernel: both within the bfloat16 tolerance of the plain implementation, and close to each
@@ -284,15 +427,12 @@ def test_products_inside_the_residual_stream_change_rounding_only(folders, oracl
     ref = oracle(name, req)
     outs = []
     for fuse in (True, False):
-        ops.fuse_residual_stream = fuse
-        try:
-            eng = engine_for(folders, name, torch.bfloat16, max_batch=1)
-            s = eng.open()
-            o = [eng.step([StepEntry(s, req[:10], range(10))])]
-            o += [eng.step([StepEntry(s, [t], [0])]) for t in req[10:]]
-            outs.append(torch.cat(o).float().cpu())
-        finally:
-            ops.fuse_residual_stream = True
+        eng = engine_for(folders, name, torch.bfloat16, max_batch=1,
+                         options=siar.KernelOptions(fuse_residual_stream=fuse))
+        s = eng.open()
+        o = [eng.step([StepEntry(s, req[:10], range(10))])]
+        o += [eng.step([StepEntry(s, [t], [0])]) for t in req[10:]]
+        outs.append(torch.cat(o).float().cpu())
     scale = ref.abs().max().item()
     for o in outs:
         assert (o - ref).abs().max().item() <= REL_TOL[torch.bfloat16] * scale

@@ -11,6 +11,7 @@ import torch
 from simple_inference_autoresearch_b200.cache import SequenceCache
 from simple_inference_autoresearch_b200.engine.batch import BatchMeta, StepEntry
 from simple_inference_autoresearch_b200.kernels import ops
+from simple_inference_autoresearch_b200.kernels.options import DEFAULT as OPTS
 from simple_inference_autoresearch_b200.parts.base import KVNeed
 from tests import emulated_kernels as emu
 from tests import plain_llama
@@ -160,12 +161,12 @@ def make_cache(n_kv, d, dtype, device, max_tokens=8192, max_slots=12, max_seq_le
 
 
 def run_attention_case(dtype, hq, hkv, d, lens_before, q_lens, seed=0, theta=10000.0, boost=None, qk_scale=1.0,
-                       window=None, cache_size=None):
+                       window=None, cache_size=None, options=OPTS):
     """Fills two caches (GPU kernel / CPU restatement) with the same history through
     rope_kv_write, then compares rope + attention of a last step."""
     torch.manual_seed(seed)
     caches = {dev: make_cache(hkv, d, dtype, dev, window=window, **(cache_size or {})) for dev in ("cpu", DEV)}
-    kw = {} if window is None else {"window": window}
+    kw = {"options": options} if window is None else {"window": window, "options": options}
     backends = {"cpu": emu, DEV: ops}
     inv_freq = plain_llama.rope_inv_freq(d, theta, None)
     b = len(q_lens)
@@ -470,11 +471,7 @@ def test_tensor_core_linear(m, n, k):
         bound = 1e-5 * k ** 0.5 + (0 if out_dtype == torch.float32 else 8e-3 * ref.abs().max().item())
         assert (got - ref).abs().max().item() <= bound + 1e-4, (m, n, k, out_dtype)
     # the CUDA-core kernel gives the same numbers beyond rounding
-    gemm_tc.enabled = False
-    try:
-        simt = ops.linear(x.to(DEV), w.to(DEV), torch.float32).cpu()
-    finally:
-        gemm_tc.enabled = True
+    simt = ops.linear(x.to(DEV), w.to(DEV), torch.float32, options=OPTS.but(use_tc_gemm=False)).cpu()
     tc = ops.linear(x.to(DEV), w.to(DEV), torch.float32).cpu()
     torch.testing.assert_close(tc, simt, rtol=1e-4, atol=1e-4)
 
@@ -489,15 +486,12 @@ def test_two_sms_on_one_tile_give_the_one_sm_kernels_numbers(m, n, k):
     w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
     outs = []
     for pairs in (2, 0):
-        gemm_tc.set_pairs(pairs)
-        try:
-            a = ops.linear(x, w, torch.float32)
-            b = ops.linear(x, w, torch.bfloat16)
-            c = ops.linear_swiglu(x, w)
-            res = torch.ones(m, n, device=DEV)
-            assert isinstance(ops.linear(x, w, torch.float32, add_to=res), ops.Added)
-        finally:
-            gemm_tc.set_pairs(1)
+        o = OPTS.but(pair_mode=pairs)
+        a = ops.linear(x, w, torch.float32, options=o)
+        b = ops.linear(x, w, torch.bfloat16, options=o)
+        c = ops.linear_swiglu(x, w, options=o)
+        res = torch.ones(m, n, device=DEV)
+        assert isinstance(ops.linear(x, w, torch.float32, add_to=res, options=o), ops.Added)
         ops.check_status(DEV)
         outs.append((a.cpu(), b.float().cpu(), c.float().cpu(), res.cpu()))
     ref = x.cpu().double() @ w.cpu().double().T
@@ -610,11 +604,8 @@ def test_fused_residual_stream_is_refused_from_17_to_128_rows_and_can_be_switche
     before = res.clone()
     out = ops.linear(x, w, torch.float32, add_to=res)
     assert isinstance(out, torch.Tensor) and torch.equal(res, before)       # the caller adds later
-    ops.fuse_residual_stream = False
-    try:
-        out8 = ops.linear(x[:8].contiguous(), w, torch.float32, add_to=res[:8].contiguous())
-    finally:
-        ops.fuse_residual_stream = True
+    out8 = ops.linear(x[:8].contiguous(), w, torch.float32, add_to=res[:8].contiguous(),
+                      options=OPTS.but(fuse_residual_stream=False))
     assert isinstance(out8, torch.Tensor)
 
 
@@ -633,11 +624,8 @@ def test_mma_attention_prefill_groups_and_lengths(hq, hkv, d):
 def test_mma_and_cuda_core_attention_agree():
     for lens_before, q_lens in (([500, 64], [1, 1]), ([100, 0], [90, 130])):
         a = run_attention_case(torch.bfloat16, 8, 2, 128, lens_before, q_lens)[DEV][0]
-        ops.use_mma_attention = False
-        try:
-            b = run_attention_case(torch.bfloat16, 8, 2, 128, lens_before, q_lens)[DEV][0]
-        finally:
-            ops.use_mma_attention = True
+        b = run_attention_case(torch.bfloat16, 8, 2, 128, lens_before, q_lens,
+                               options=OPTS.but(use_mma_attention=False))[DEV][0]
         torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
 
 
@@ -716,12 +704,9 @@ def test_tc_attention_large_scores_rescale():
 def test_tc_and_mma_attention_agree_and_rows_do_not_depend_on_batch():
     hq, hkv, d = 8, 2, 128
     a = run_attention_case(torch.bfloat16, hq, hkv, d, [100, 0], [90, 330])[DEV][0]
-    ops.use_tc_attention = False
-    try:
-        assert not ops.tc_attention_takes(torch.bfloat16, hq, hkv, d, 64)
-        b = run_attention_case(torch.bfloat16, hq, hkv, d, [100, 0], [90, 330])[DEV][0]
-    finally:
-        ops.use_tc_attention = True
+    no_tc = OPTS.but(use_tc_attention=False)
+    assert ops.tc_attention_takes(torch.bfloat16, hq, hkv, d, 64) and not ops.tc_attention_takes(torch.bfloat16, hq, hkv, d, 64, no_tc)
+    b = run_attention_case(torch.bfloat16, hq, hkv, d, [100, 0], [90, 330], options=no_tc)[DEV][0]
     torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
     alone = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0], q_lens=[150])[DEV][0]
     both = run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0], q_lens=[150, 77])[DEV][0]
@@ -761,12 +746,10 @@ def test_fused_rope_decode_attention_equals_the_two_kernels(hq, hkv, d, write_kv
                               hq, hkv, d)
         new = rnd(len(lens), width, dtype=torch.bfloat16, seed=50).to(DEV)
         meta = BatchMeta.build([StepEntry(s, [0]) for s in slots], lens, DEV)
-        ops.fuse_decode_rope = fused
-        try:
-            assert ops.decode_fuses_rope(meta, torch.bfloat16, hq, hkv, d, 64) == fused
-            out = ops.rope_and_attention(new, inv_freq, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d), write_kv=write_kv)
-        finally:
-            ops.fuse_decode_rope = True
+        o = OPTS.but(fuse_decode_rope=fused)
+        assert ops.decode_fuses_rope(meta, torch.bfloat16, hq, hkv, d, 64, o) == fused
+        out = ops.rope_and_attention(new, inv_freq, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d), write_kv=write_kv,
+                                     options=o)
         results.append((out.float().cpu(), c.entry(0).k.float().cpu(), c.entry(0).v.float().cpu()))
     ops.check_status(DEV)
     torch.testing.assert_close(results[0][1], results[1][1], rtol=0, atol=0)     # cached keys: same rounding, same bits
@@ -775,14 +758,19 @@ def test_fused_rope_decode_attention_equals_the_two_kernels(hq, hkv, d, write_kv
 
 
 @pytest.mark.parametrize("dtype,path", [(torch.bfloat16, "fused"), (torch.bfloat16, "mma"), (torch.bfloat16, "mma_prefill"),
-                                        (torch.bfloat16, "cuda_core"), (torch.float32, "cuda_core")])
-def test_a_page_the_sequence_does_not_hold_is_reported_and_no_other_memory_is_touched(dtype, path):
+                                        (torch.bfloat16, "tc_prefill"), (torch.bfloat16, "cuda_core"),
+                                        (torch.bfloat16, "cuda_core_prefill"), (torch.float32, "cuda_core"),
+                                        (torch.float32, "cuda_core_prefill")])
+@pytest.mark.parametrize("history_only", [False, True])
+def test_a_page_the_sequence_does_not_hold_is_reported_and_no_other_memory_is_touched(dtype, path, history_only):
     """A block-table cell of -1 inside the keys a step reads and writes (a replay of a captured step
     without the pages reserved first would meet one): the kernels read page 0 instead of an address
-    in front of the pool, store nothing for the token without a page, and the status word says so."""
+    in front of the pool, store nothing for the token without a page, and the status word says so.
+    ``history_only``: only a page of earlier keys is absent, so the report has to come from the
+    attention kernel itself (the rotate-and-write kernel meets no absent page)."""
     hq, hkv, d = 8, 2, 128
     width = (hq + 2 * hkv) * d
-    n_before, q_len = 300, (70 if path == "mma_prefill" else 1)
+    n_before, q_len = 300, (70 if path.endswith("prefill") else 1)
     c = make_cache(hkv, d, dtype, DEV, max_tokens=4096, max_slots=4)
     decoy, slot = c.alloc(), c.alloc()
     c.reserve([decoy], [64]); c.commit([decoy], [64])           # page 0 belongs to another sequence
@@ -794,25 +782,21 @@ def test_a_page_the_sequence_does_not_hold_is_reported_and_no_other_memory_is_to
     ops.check_status(DEV)
     table = c.entry(0).block_table
     table[slot, 2] = -1                                          # keys 128..191 of the history
-    table[slot, (n_before + q_len - 1) // 64] = -1               # and the page of the newest token
+    if not history_only:
+        table[slot, (n_before + q_len - 1) // 64] = -1           # and the page of the newest token
     k_before, v_before = c.entry(0).k.clone(), c.entry(0).v.clone()
     new = rnd(q_len, width, dtype=dtype, seed=4).to(DEV)
     meta = BatchMeta.build([StepEntry(slot, [0] * q_len)], [n_before], DEV)
-    saved = ops.fuse_decode_rope, ops.use_mma_attention, ops.use_tc_attention
-    ops.fuse_decode_rope = path == "fused"
-    ops.use_mma_attention = path != "cuda_core"
-    ops.use_tc_attention = False
-    try:
-        out = ops.rope_and_attention(new, None, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d))
-        torch.cuda.synchronize()
-    finally:
-        ops.fuse_decode_rope, ops.use_mma_attention, ops.use_tc_attention = saved
+    o = OPTS.but(fuse_decode_rope=path == "fused", use_mma_attention=not path.startswith("cuda_core"),
+                 use_tc_attention=path == "tc_prefill")
+    out = ops.rope_and_attention(new, None, c.entry(0), meta, hq, hkv, d, 1.0 / math.sqrt(d), options=o)
+    torch.cuda.synchronize()
     assert out.shape == (q_len, hq * d)
     with pytest.raises(RuntimeError, match="without a page"):
         ops.check_status(DEV)
     ops.check_status(DEV)                                        # the word is cleared once it has been read
     # tokens whose page exists were stored (a prompt's first tokens), the one without a page nowhere
-    first_new_page = table[slot, n_before // 64].item()
+    new_pages = {table[slot, i].item() for i in range(n_before // 64, (n_before + q_len - 1) // 64 + 1)}
     changed_k = (c.entry(0).k != k_before).flatten(1).any(1).nonzero().flatten().tolist()
-    assert set(changed_k) <= {first_new_page} - {-1}
+    assert set(changed_k) <= new_pages - {-1}
     assert torch.equal(c.entry(0).v[0], v_before[0]) and torch.equal(c.entry(0).k[0], k_before[0])

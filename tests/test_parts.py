@@ -402,6 +402,138 @@ def test_toy_routed_feed_forward_and_learned_positions(device):
         POSITION_ENCODINGS.unregister("learned")
 
 
+# ----------------------------------------------------------------------------- rotary layouts that are not Llama's
+def plain_forward_with_rotary_layout(w, raw, tokens, rotary_dim, interleaved):
+    """plain_llama.forward with the rotation of q and k replaced by a partial and / or interleaved one."""
+    c = plain_llama.parse_config(raw)
+    w = {k: v.float() for k, v in w.items()}
+    inv = plain_llama.rope_inv_freq(rotary_dim, c["theta"], c["scaling"])
+    t = len(tokens)
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    for i in range(c["L"]):
+        p = f"model.layers.{i}."
+        hn = plain_llama.rmsnorm(x, w[p + "input_layernorm.weight"], c["eps"])
+        q = (hn @ w[p + "self_attn.q_proj.weight"].T).view(t, c["Hq"], c["D"])
+        k = (hn @ w[p + "self_attn.k_proj.weight"].T).view(t, c["Hkv"], c["D"])
+        v = (hn @ w[p + "self_attn.v_proj.weight"].T).view(t, c["Hkv"], c["D"])
+        q = emulated_kernels.rotate(q, list(range(t)), inv, rotary_dim, interleaved)
+        k = emulated_kernels.rotate(k, list(range(t)), inv, rotary_dim, interleaved)
+        x = x + plain_llama.attention_causal(q, k, v) @ w[p + "self_attn.o_proj.weight"].T
+        x = x + plain_llama.swiglu_mlp(plain_llama.rmsnorm(x, w[p + "post_attention_layernorm.weight"], c["eps"]), w, p + "mlp.")
+    head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
+    return plain_llama.rmsnorm(x, w["model.norm.weight"], c["eps"]) @ head.T
+
+
+@pytest.mark.parametrize("name,dtype,rotary_dim,interleaved", [
+    ("C", torch.float32, 32, True),        # head_dim 48: two thirds of a head rotated, pairs (2i, 2i+1)
+    ("C", torch.float32, 48, True),
+    ("D", torch.bfloat16, 32, False),      # head_dim 64 on the tensor-core path: half a head rotated
+    ("E", torch.bfloat16, 128, True),
+])
+def test_partial_and_interleaved_rotary_are_parameters_of_the_position_encoding(device, tmp_path, name, dtype,
+                                                                                rotary_dim, interleaved):
+    """The Llama parts with another rotary layout, given as parameters of the ``rotary`` position
+    encoding: whole prompt, then single tokens (on the bfloat16 tensor-core path the decode step
+    cannot take the kernel that rotates inside attention and goes the two-kernel way)."""
+    if device == "cpu" and dtype != torch.float32:
+        pytest.skip("the emulated kernels check the wiring once, in float32")
+    folder = tiny_configs.make_folder(tmp_path, name, seed=3)
+    raw, w = tiny_configs.read_folder(folder)
+    base = llama_model_spec(LlamaConfig.from_dict(raw))
+    position = PartSpec("rotary", {**base.position.params, "rotary_dim": rotary_dim, "interleaved": interleaved})
+    model = DecoderModel(ModelSpec(**{**base.__dict__, "position": position}), dtype, device)
+    model.load({k: v.to(dtype).to(device) for k, v in w.items()})
+    eng = siar.Engine(model, max_batch=2, max_seq_len=256, use_cuda_graph=False)
+    toks = torch.randint(0, raw["vocab_size"], (90,), generator=torch.Generator().manual_seed(2)).tolist()
+    s = eng.open()
+    outs = [eng.step([StepEntry(s, toks[:70], range(70))])]
+    outs += [eng.step([StepEntry(s, [t], [0])]) for t in toks[70:]]
+    got = torch.cat(outs).float().cpu()
+    ref = plain_forward_with_rotary_layout(w, raw, toks, rotary_dim, interleaved)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert (got - ref).abs().max().item() <= tol * ref.abs().max().item()
+    assert (ref - plain_llama.forward(w, raw, toks)).abs().max() > 1e-3        # the layout really matters
+    with pytest.raises(ValueError, match="rotary_dim"):
+        POSITION_ENCODINGS.build(PartSpec("rotary", {"head_dim": 16, "theta": 1e4, "rotary_dim": 18}))
+
+
+# ----------------------------------------------------------------------------- another architecture from outside, through the command line
+class ToyConfig:
+    """The typed configuration of an architecture that is not Llama: its own config.json keys."""
+
+    def __init__(self, width, vocab, depth, stop):
+        self.width, self.vocab, self.depth, self.stop = width, vocab, depth, stop
+        self.vocab_size, self.bos_token_id = vocab, 0          # what the command line reads of any configuration
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(int(d["width"]), int(d["vocab"]), int(d["depth"]), int(d.get("stop", 1)))
+
+    def to_dict(self):
+        return {"architectures": ["ToyMeanForCausalLM"], "model_type": "toy_mean", "width": self.width,
+                "vocab": self.vocab, "depth": self.depth, "stop": self.stop}
+
+
+def toy_mean_spec(cfg, **_):
+    norm = lambda p: PartSpec("rmsnorm", {"prefix": p, "hidden_size": cfg.width, "eps": 1e-5})  # noqa: E731
+    layer = lambda i: PartSpec("prenorm", {  # noqa: E731
+        "prefix": f"l{i}.", "mixer": PartSpec("running_mean", {"prefix": "mix.", "hidden_size": cfg.width}),
+        "feed_forward": PartSpec("swiglu", {"prefix": "ffn.", "hidden_size": cfg.width, "intermediate_size": 2 * cfg.width}),
+        "mixer_norm": norm("n1."), "ffn_norm": norm("n2.")})
+    return ModelSpec(architecture="ToyMeanForCausalLM", vocab_size=cfg.vocab, hidden_size=cfg.width, max_position=256,
+                     embedding_name="emb", head_name=None, position=PartSpec("none", {}),
+                     layers=tuple(layer(i) for i in range(cfg.depth)), final_norm=norm("nf."),
+                     stop_token_ids=(cfg.stop,))
+
+
+@pytest.mark.gpu
+def test_another_architecture_runs_from_the_command_line_without_a_change_to_the_library(tmp_path, capsys):
+    """An architecture with its own configuration class, its own config.json keys and a mixer with
+    state, registered from here together with a named configuration: ``inference.py --model NAME
+    --random-weights`` resolves it through the registry and generates; the same seed gives the
+    same tokens, and they are the plain implementation's."""
+    import json
+
+    from simple_inference_autoresearch_b200 import config as config_module
+    from simple_inference_autoresearch_b200 import inference
+
+    MIXERS.register("running_mean")(RunningMeanMixer)
+    registry.register_architecture("ToyMeanForCausalLM", ("toy_mean",), config_cls=ToyConfig, spec_builder=toy_mean_spec)
+    path = tmp_path / "toy-mean.json"
+    path.write_text(json.dumps(ToyConfig(32, 60, 2, 59).to_dict()))
+    config_module.register_preset("toy-mean", path)
+    try:
+        args = ["--model", "toy-mean", "--random-weights", "--seed", "4", "--prompt-ids", "5,6,7,8", "--max-new-tokens", "6",
+                "--temperature", "0", "--dtype", "float32", "--ignore-eos"]
+        assert inference.main(args) == 0
+        first = capsys.readouterr().out.splitlines()[0]
+        assert inference.main(args) == 0
+        assert capsys.readouterr().out.splitlines()[0] == first
+        tokens = [int(t) for t in first.split()]
+        assert len(tokens) == 6
+        # the plain model: running mean mixer + SwiGLU, greedy
+        arch, cfg = registry.resolve_path(path)
+        model = DecoderModel(arch.spec_builder(cfg), torch.float32, "cpu")
+        w = random_tensors(model.tensor_specs(), 4, torch.bfloat16)
+        w = {k: v.float() for k, v in w.items()}
+        seq = [5, 6, 7, 8]
+        for tok in tokens:
+            x = w["emb"][torch.tensor(seq)]
+            for i in range(2):
+                p = f"l{i}."
+                hn = plain_llama.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+                mean = torch.cumsum(hn, 0) / torch.arange(1, len(seq) + 1)[:, None]
+                x = x + mean @ w[p + "mix.w"].T
+                x = x + plain_llama.swiglu_mlp(plain_llama.rmsnorm(x, w[p + "n2.weight"], 1e-5), w, p + "ffn.")
+            logits = plain_llama.rmsnorm(x, w["nf.weight"], 1e-5) @ w["emb"].T
+            assert int(logits[-1].argmax()) == tok
+            seq.append(tok)
+    finally:
+        MIXERS.unregister("running_mean")
+        registry.unregister_architecture("ToyMeanForCausalLM")
+        config_module._registered.pop("toy-mean", None)
+
+
 def test_unknown_part_kind_is_a_clear_error():
     with pytest.raises(ValueError, match="unknown mixer kind 'nope'"):
         MIXERS.build(PartSpec("nope"))

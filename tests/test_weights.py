@@ -116,3 +116,66 @@ def test_folder_without_weights(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(tiny_configs.TINY_A))
     with pytest.raises(FileNotFoundError, match="neither"):
         siar.load_model(tmp_path, device="cpu", dtype=torch.float32)
+
+
+# ----------------------------------------------------------------------------- the seeded generator
+def test_random_values_are_normal_and_do_not_depend_on_how_they_are_drawn(monkeypatch):
+    from simple_inference_autoresearch_b200.parts.base import TensorSpec
+    from simple_inference_autoresearch_b200.weights import random_init
+
+    z = random_init.standard_normal(400_000, key=random_init._tensor_seed(3, "some.tensor"))
+    assert abs(z.mean().item()) < 0.01 and abs(z.std().item() - 1) < 0.01
+    assert abs((z ** 3).mean().item()) < 0.03 and abs((z ** 4).mean().item() - 3) < 0.06
+    assert 4.0 < z.abs().max().item() < 6.0 and torch.isfinite(z).all()
+    # a tensor drawn whole and in pieces (the writer draws 2^24 elements at a time): the same bits
+    spec = TensorSpec("model.layers.0.mlp.up_proj.weight", (37, 53), std=0.02)
+    whole = random_init.random_tensor(spec, 5, torch.float32)
+    monkeypatch.setattr(random_init, "_CHUNK", 100)
+    assert torch.equal(random_init.random_tensor(spec, 5, torch.float32), whole)
+    # another name or another seed: another stream
+    other = random_init.random_tensor(TensorSpec("model.layers.1.mlp.up_proj.weight", (37, 53)), 5, torch.float32)
+    assert not torch.equal(other, whole) and not torch.equal(random_init.random_tensor(spec, 6, torch.float32), whole)
+
+
+def test_the_shipped_tiny_b_configuration_carries_its_rule_for_norm_weights(tmp_path):
+    """``--model tiny-b --random-weights`` is the second tiny configuration as specified: norm
+    weights 1 + N(0, 0.02), everything else N(0, 0.02); the rule travels in the configuration
+    (``norm_weight_init``) and survives a round trip through config.json."""
+    from simple_inference_autoresearch_b200 import registry
+    from simple_inference_autoresearch_b200.config import preset_path
+
+    _arch, cfg = registry.resolve_path(preset_path("tiny-b"))
+    assert cfg.norm_weight_init == "ones_plus_normal" and cfg.initializer_range == 0.02
+    folder = write_model_folder(tmp_path / "b", cfg, seed=1)
+    w = load_file(str(folder / SINGLE_FILE))
+    norm = w["model.layers.1.post_attention_layernorm.weight"].float()
+    assert not torch.all(norm == 1) and abs(norm.mean().item() - 1) < 0.02 and 0.005 < norm.std().item() < 0.04
+    _arch, again = registry.resolve_path(folder)
+    assert again.norm_weight_init == "ones_plus_normal"
+    _arch, a = registry.resolve_path(preset_path("tiny-a"))
+    assert a.norm_weight_init == "ones" and "norm_weight_init" not in a.to_dict()
+
+
+@pytest.mark.gpu
+def test_random_weights_hold_the_same_bits_on_the_cpu_and_on_the_gpu(tmp_path):
+    """``init_random`` (drawn on the GPU) and ``write_model_folder`` (drawn on the CPU) give identical
+    tensors for one seed: every tensor of the second tiny configuration, and a tensor longer than
+    one piece of the generator."""
+    from simple_inference_autoresearch_b200 import registry
+    from simple_inference_autoresearch_b200.config import preset_path
+    from simple_inference_autoresearch_b200.parts.base import TensorSpec
+    from simple_inference_autoresearch_b200.weights import random_init, random_tensors
+
+    _arch, cfg = registry.resolve_path(preset_path("tiny-b"))
+    loaded = siar.build_model(cfg, torch.bfloat16, "cuda")
+    specs = loaded.model.tensor_specs()
+    on_gpu = random_tensors(specs, 21, torch.bfloat16, "cuda")
+    on_cpu = random_tensors(specs, 21, torch.bfloat16, "cpu")
+    assert all(torch.equal(on_gpu[s.name].cpu(), on_cpu[s.name]) for s in specs)
+    folder = write_model_folder(tmp_path / "b", cfg, seed=21)
+    stored = load_file(str(folder / SINGLE_FILE))
+    assert all(torch.equal(on_gpu[s.name].cpu(), stored[s.name]) for s in specs)
+    big = TensorSpec("big", (random_init._CHUNK + 4097,), std=1.0)
+    a = random_init.random_tensor(big, 2, torch.float32, "cuda").cpu()
+    b = random_init.random_tensor(big, 2, torch.float32, "cpu")
+    assert torch.equal(a, b)

@@ -102,9 +102,12 @@ def test_no_alloc_entry_refuses_what_does_not_fit():
     assert need(256, hq, hkv, d, 4096, sms) > limit
     rc, msg = call_noalloc(f, qkv, cache.entry(0), meta, hq, hkv, d, out)
     assert rc == -3 and "floats of scratch" in msg and str(limit) in msg, (rc, msg)
-    meta.n_seqs = 1024                                # more (sequence, kv head) pairs than counters
-    rc, msg = call_noalloc(f, qkv, cache.entry(0), meta, hq, hkv, d, out)
-    assert rc == -3, (rc, msg)
+    # more (sequence, kv head) pairs than counters, with partials that would fit: 1,024 sequences of
+    # 8 kv heads, one chunk each
+    meta.n_seqs, meta.max_kv_len = 1024, 128
+    assert need(1024, 8, 8, 64, 128, sms) <= limit
+    rc, msg = call_noalloc(f, qkv, cache.entry(0), meta, 8, 8, 64, out)
+    assert rc == -3 and "pairs" in msg and "8192" in msg, (rc, msg)
     meta.n_seqs, meta.max_kv_len = 1, 301
     rc, msg = call_noalloc(f, qkv, cache.entry(0), meta, hq, hkv, 48, out)     # a head size the kernel does not take
     assert rc == -2 and "head_dim 48" in msg, (rc, msg)

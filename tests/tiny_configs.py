@@ -38,8 +38,31 @@ TINY_C = {
     "tie_word_embeddings": False, "bos_token_id": 0, "eos_token_id": 330, "torch_dtype": "bfloat16",
 }
 
-NORM_INIT = {"A": "ones", "B": "ones_plus_normal", "C": "ones_plus_normal"}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Tiny widths with heads of real size, so that the bfloat16 path runs on the tensor-core attention
+# kernels (head_dim 64 and 128) and the tensor-core products while the plain implementation stays cheap.
+# D: head_dim 64, pairs of query heads, tied, llama3 scaling whose bands all occur below position 1024
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 256, "intermediate_size": 344, "num_hidden_layers": 2, "vocab_size": 500,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "max_position_embeddings": 1024,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "tie_word_embeddings": True, "bos_token_id": 1, "eos_token_id": 2, "torch_dtype": "bfloat16",
+}
+
+# E: head_dim 128 given explicitly (hidden / heads would be 53.3), groups of 3 query heads, untied,
+# norm weights 1 + noise, an odd vocabulary
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 320, "intermediate_size": 520, "num_hidden_layers": 2, "vocab_size": 777,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128, "rms_norm_eps": 1e-6,
+    "rope_theta": 10000.0, "max_position_embeddings": 1024, "rope_scaling": None,
+    "tie_word_embeddings": False, "bos_token_id": 0, "eos_token_id": [775, 776], "torch_dtype": "bfloat16",
+}
+
+NORM_INIT = {"A": "ones", "B": "ones_plus_normal", "C": "ones_plus_normal", "D": "ones", "E": "ones_plus_normal"}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_folder(tmp_path, name: str, seed: int = 0, store_dtype=torch.bfloat16, vector_dtype=None) -> Path:
