@@ -31,9 +31,10 @@ def _tensor_seed(seed: int, name: str) -> int:
 # Element i of a tensor is a function of (tensor key, i) alone: splitmix64 of the counter gives 64
 # bits, of which two 24-bit fields become two uniforms, and Box-Muller turns those into one normal
 # deviate.  Every step is a single torch operation that is exactly rounded on both devices (integer
-# arithmetic, float32 add / multiply / divide / sqrt / floor): the logarithm and the cosine are
-# evaluated by series written out below, not by the devices' own libraries, which differ in the
-# last bit.  So ``random_tensor(spec, seed, dtype, "cpu")`` and ``(..., "cuda")`` hold identical bits,
+# arithmetic, float32 add / multiply / divide / floor): the logarithm, the cosine and the square
+# root are evaluated by series and iterations written out below, not by the devices' own
+# libraries, which differ in the last bit (torch's float32 sqrt on the GPU is not exactly rounded:
+# 0.7% of its results differ from the CPU's).  So ``random_tensor(spec, seed, dtype, "cpu")`` and ``(..., "cuda")`` hold identical bits,
 # as do a tensor drawn whole and the same tensor drawn in pieces.
 
 _CHUNK = 1 << 24        # elements drawn at a time (bounds the temporaries)
@@ -92,6 +93,16 @@ def _neg_log(u: torch.Tensor) -> torch.Tensor:
     return -(e * _LN2_HI + (e * _LN2_LO + ln_m))
 
 
+def _sqrt(y: torch.Tensor) -> torch.Tensor:
+    """sqrt y for float32 y >= 0 to the last bit or two, from operations that round alike everywhere:
+    a first guess from the bit pattern (halved exponent, 3.5% off at most), then Newton steps
+    r <- (r + y / r) / 2, each of which squares the error."""
+    r = ((y.view(torch.int32) >> 1) + 0x1FBD1DF5).view(torch.float32)
+    for _ in range(4):
+        r = (r + y / r) * 0.5
+    return torch.where(y > 0, r, torch.zeros_like(y))
+
+
 def _cos_turns(t: torch.Tensor) -> torch.Tensor:
     """cos(2 pi t) for float32 t in [0, 1) on a 2^-24 grid: the quadrant is split off exactly."""
     t4 = t * 4.0
@@ -111,7 +122,7 @@ def standard_normal(n: int, key: int, device="cpu", start: int = 0) -> torch.Ten
     z = _splitmix64(counter, key)
     u1 = (_lshr(z, 40) + 1).to(torch.float32) * (1.0 / 16777216.0)           # (0, 1]
     u2 = (_lshr(z, 16) & 0xFFFFFF).to(torch.float32) * (1.0 / 16777216.0)    # [0, 1)
-    r = torch.sqrt(_neg_log(u1) * 2.0)
+    r = _sqrt(_neg_log(u1) * 2.0)
     return r * _cos_turns(u2)
 
 

@@ -246,7 +246,7 @@ def test_more_sequences_than_the_captured_buffers_hold(folders):
     loaded = siar.load_model(folders[name], device="cuda", dtype=torch.float32)
     drawn = {}
     for graph in (True, False):
-        eng = siar.Engine(loaded.model, max_batch=2, max_slots=8, max_seq_len=64, use_cuda_graph=graph)
+        eng = siar.Engine(loaded.model, max_batch=2, max_slots=8, max_tokens=8 * 64, max_seq_len=64, use_cuda_graph=graph)
         reqs = [generation.Request(t, 0, GREEDY, index=i) for i, t in enumerate(toks)]
         for r in reqs:
             r.slot = eng.open()

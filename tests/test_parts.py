@@ -504,7 +504,8 @@ def test_another_architecture_runs_from_the_command_line_without_a_change_to_the
     config_module.register_preset("toy-mean", path)
     try:
         args = ["--model", "toy-mean", "--random-weights", "--seed", "4", "--prompt-ids", "5,6,7,8", "--max-new-tokens", "6",
-                "--temperature", "0", "--dtype", "float32", "--ignore-eos"]
+                "--temperature", "0", "--dtype", "float32", "--ignore-eos", "--no-cuda-graph"]
+        # (the toy mixer is written in Python against the batch's host-side lists, which a captured step has not)
         assert inference.main(args) == 0
         first = capsys.readouterr().out.splitlines()[0]
         assert inference.main(args) == 0
