@@ -49,6 +49,23 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define SIAR_STAMP(i)
 #endif
 
+// Loads of what the kernel in front of this one wrote (the fused qkv rows), for code that runs after
+// pdl_wait() in a kernel that has other work in front of the wait.  A load through a const
+// __restrict__ pointer is an "invariant" load to the compiler (the location is promised not to change
+// while the kernel lives), and invariant loads may be moved above any barrier, the dependency wait
+// included: the query was then read while the product in front was still writing it.  A volatile asm
+// with a memory clobber stays behind the wait.
+__device__ __forceinline__ uint32_t ld_after_wait_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ __nv_bfloat16 ld_after_wait_bf16(const __nv_bfloat16* p) {
+  unsigned short v;
+  asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p) : "memory");
+  return __ushort_as_bfloat16(v);
+}
+
 // ------------------------------------------------------------------ decode
 // grid (chunks, Hkv, B), 128 threads.  A block owns `chunk_keys` consecutive keys of one
 // (sequence, kv head); warp w walks keys [c0 + 64 it + 16 w, +16) for it = 0, 1, ... with a
@@ -71,8 +88,19 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
   __shared__ float cs_s[D];                     // cos[D/2], sin[D/2] of the new token's position
   pdl_launch_dependents();
   SIAR_TRACE(20, 0);
-  pdl_wait();
-  SIAR_TRACE(20, 2);
+  // What this kernel reads before its query: the batch description and the block table (written
+  // before the step's first kernel, behind a copy that nothing overtakes) and the keys and values of
+  // earlier positions.  When the kernel itself is the step's only writer of its cache entry
+  // (fuse_rope && write_kv) those are final since earlier steps, so the whole prologue (lengths ->
+  // block table -> first tiles, three dependent trips to L2, and the rotation angles) runs while the
+  // product in front is still at work, and only the query waits.  A layer that reads the cache another
+  // layer of this step writes (write_kv == 0), or whose new keys a separate kernel stores (no fuse_rope),
+  // waits first.
+  const bool early = fuse_rope && write_kv;
+  if (!early) {
+    pdl_wait();
+    SIAR_TRACE(20, 2);
+  }
   constexpr int RS = D + kPad;                 // row stride in elements
   constexpr int CPR = D / 8;                   // 16-byte pieces per row
   constexpr int WK = decode_warp_keys(D);      // keys per warp and step
@@ -151,6 +179,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       cs_s[D / 2 + threadIdx.x] = sn;
     }
   }
+  if (early) {
+    pdl_wait();            // the fused qkv rows of this step are complete
+    SIAR_TRACE(20, 2);
+  }
   // query fragments straight from global memory: rows g and g + 8 of the (padded) group
   const size_t tok_row = (size_t)row_b * (Hq + 2 * Hkv) * D;
   uint32_t qa[D / 16][4];
@@ -159,10 +191,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const int col = kk * 16 + q * 2;
-      qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col) : 0u;
-      qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col) : 0u;
-      qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)g * D + col + 8) : 0u;
-      qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
+      qa[kk][0] = g < G ? ld_after_wait_u32(qrow + (size_t)g * D + col) : 0u;
+      qa[kk][1] = g + 8 < G ? ld_after_wait_u32(qrow + (size_t)(g + 8) * D + col) : 0u;
+      qa[kk][2] = g < G ? ld_after_wait_u32(qrow + (size_t)g * D + col + 8) : 0u;
+      qa[kk][3] = g + 8 < G ? ld_after_wait_u32(qrow + (size_t)(g + 8) * D + col + 8) : 0u;
     }
   }
 
@@ -217,14 +249,14 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
       __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(k_pool) + grow;
       __nv_bfloat16* vdst = const_cast<__nv_bfloat16*>(v_pool) + grow;
       for (int i = lane; i < D / 2; i += 32) {
-        const float a = __bfloat162float(krow[i]), c2 = __bfloat162float(krow[i + D / 2]);
+        const float a = __bfloat162float(ld_after_wait_bf16(krow + i)), c2 = __bfloat162float(ld_after_wait_bf16(krow + i + D / 2));
         const __nv_bfloat16 oa = __float2bfloat16_rn(a * cs_s[i] - c2 * cs_s[D / 2 + i]);
         const __nv_bfloat16 oc = __float2bfloat16_rn(c2 * cs_s[i] + a * cs_s[D / 2 + i]);
         ks[i] = oa; ks[i + D / 2] = oc;
         if (held) { kdst[i] = oa; kdst[i + D / 2] = oc; }
       }
       for (int d = lane; d < D; d += 32) {
-        const __nv_bfloat16 v = vrow[d];
+        const __nv_bfloat16 v = ld_after_wait_bf16(vrow + d);
         vs[d] = v;
         if (held) vdst[d] = v;
       }
@@ -615,7 +647,10 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
 // costs a fixed part (set-up, joining its warps, the partial, the counter) plus a part per
 // tile, and blocks run in waves of kDecodeBlocksPerSM * sm_count.  The t with the smallest estimate wins, with
 // at most 64 chunks per sequence.  (Measured on B200: about 6 us fixed and 2.8 us per tile
-// with three blocks sharing an SM's bandwidth.)
+// with three blocks sharing an SM's bandwidth.  An estimate that let a block's fixed part hide behind
+// its neighbour's streaming, and so cut batch 64 at 2,048 keys into two chunks per sequence instead of
+// one, 1,024 blocks instead of 512, was 6% slower there: a block alone does not draw an SM's whole
+// share of the bandwidth.)
 static int decode_chunk_keys(int B, int Hkv, int max_kv_len, int sm_count) {
   const int tiles = (max_kv_len + kMmaDecodeChunk - 1) / kMmaDecodeChunk;
   const long long pairs = (long long)B * Hkv;

@@ -83,6 +83,12 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // prologue) and pdl_wait() before it reads or writes anything an earlier kernel touches;
 // pdl_wait() returns once all earlier kernels have completed and their writes are visible.
 // Both are no-ops for a kernel launched without the attribute.
+// One rule for code in front of pdl_wait(): whatever is read there must have been written before
+// the step's first kernel (weights, the batch description, the block table, cache positions of
+// earlier steps).  And one for code behind it: data of the kernel in front must not be read through a
+// const __restrict__ pointer when the address is known before the wait, because the compiler may
+// move such ("invariant") loads above the wait; read it through a plain pointer or with the
+// volatile loads of attention_mma.cu.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

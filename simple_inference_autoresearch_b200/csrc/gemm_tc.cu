@@ -49,19 +49,28 @@ struct GemmParams {
   int kb_per_split;   // k-blocks of 64 per split
   int x_is_weight;    // X is written by no kernel (swap-AB): its tiles may load before pdl_wait()
   int swiglu;         // weight rows interleaved (gate_j, up_j): write silu(gate) * up, half as many outputs
-  // Fused residual stream (small-batch kernel with BN = 16 only):
-  //  * accumulate: C (float32) += D instead of C = D, and ss_out[q][tile] receives the sum of squares
-  //    of the new C over the 128 outputs of tile blockIdx.x, for the norm that follows;
-  //  * y_resid: the activation operand is not loaded but made: row q of it is
-  //    rmsnorm(y_resid[q]) * norm_w, with the sum of squares taken from ss_in[q][0..ss_tiles).
+  // The residual stream inside the products.  With r the float32 residual, w the weight of the
+  // RMSNorm that follows and W the weight of the product after it,
+  //     (r * rsqrt(mean(r^2) + eps) * w) W^T  =  rsqrt(mean(r^2) + eps) * ((r * w) W^T):
+  // the norm's row factor can be applied to the product's rows afterwards.  So
+  //  * a product that ends a sublayer (accumulate) adds itself into the residual, C (float32) += D,
+  //    and, when rb_out is given, also writes rb_out = bf16(C_new * next_w) [rows, ldc] (the operand
+  //    of the next product) and ss_out[row][part] = the sum of squares of C_new over this block's
+  //    outputs of the row (ss_parts parts per row, every one written by exactly one block);
+  //  * the product that follows (ss_in given) loads rb as an ordinary operand and multiplies each
+  //    of its rows by rsqrt(sum(ss_in[row][0..ss_in_parts)) * inv_width + eps) on the accumulators,
+  //    before the activation (SwiGLU epilogue) or the store.
+  // No norm kernel runs between the two, and nothing but the bf16 operand is rounded.
   int accumulate;
   float* ss_out;
-  const float* y_resid;
+  int ss_parts;
+  __nv_bfloat16* rb_out;
+  const void* next_w;      // [outputs] norm weight, bfloat16 or (next_w_f32) float32
+  int next_w_f32;
   const float* ss_in;
-  const __nv_bfloat16* norm_w;
+  int ss_in_parts;
+  float inv_width;         // 1 / (width of the normed row) = 1 / K
   float eps;
-  int ss_tiles;
-  int y_ld;
 #ifdef SIAR_TIMING
   unsigned long long* stamps;   // [blocks][8] globaltimer marks, for profiling builds only
 #endif
@@ -80,6 +89,26 @@ __device__ __forceinline__ unsigned long long gtime() {
 #endif
 
 // ------------------------------------------------------------------ kernel
+__device__ __forceinline__ float load_norm_w(const void* w, int is_f32, long long i) {
+  return is_f32 ? reinterpret_cast<const float*>(w)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]);
+}
+// Eight consecutive norm weights from index i (a multiple of 8; w is 16-byte aligned).
+__device__ __forceinline__ void load_norm_w8(const void* w, int is_f32, long long i, float (&out)[8]) {
+  if (is_f32) {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i);
+    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      out[2 * e] = f.x; out[2 * e + 1] = f.y;
+    }
+  }
+}
+
 // At most 112 registers per thread (three blocks' worth per SM): a block of this kernel then fits
 // on an SM beside two blocks of the decode attention kernel, so it starts, sets up and asks for
 // its first weight tiles while the attention in front of it is still running.
@@ -90,6 +119,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   constexpr uint32_t kYBytes = BN * kBK * 2;
   constexpr uint32_t kStageBytes = kXBytes + kYBytes;
   constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  constexpr int kSsSlots = 64;                     // most columns one block owns when it adds (see below)
 
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -97,11 +127,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   __shared__ __align__(8) uint64_t tmem_full_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float ss_red[4][16];
+  __shared__ float ss_red[4][kSsSlots];
+  __shared__ float inv_s[BN < 128 ? BN : 128];     // row factors of the norm in front, by tile column (few rows)
 
   const uint32_t dyn = smem_u32(smem_dyn);
   unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
-  const bool make_y = BN == 16 && prm.y_resid != nullptr;   // the epilogue warps produce the activation tiles
 
   pdl_launch_dependents();
   SIAR_TRACE(10, 0);
@@ -116,7 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], make_y ? 129 : 1);     // the TMA thread, and the 128 threads that write Y
+      mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full_bar, 1);
@@ -136,7 +166,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   float* stage = reinterpret_cast<float*>(tiles);
   TOut* C = (TOut*)prm.C;
   bool acc_ok = false;      // epilogue threads: the accumulator in tensor memory is complete
-  float old_c[16];          // accumulate: the values of C this thread adds to
+  float old_c[16];          // accumulate, 16-column tiles: the values of C this thread adds to
+  float inv_row = 1.f;      // the norm's factor of this thread's tile row (many rows on the tile's rows)
+  const bool scaled = prm.ss_in != nullptr;
 
   {
   if (dead) {
@@ -147,14 +179,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tmY) : "memory");
       int issued = 0;
-      // Weights do not depend on earlier kernels: when X is the weight, the first STAGES
-      // tiles of it are requested before this grid waits for its predecessors.
+      // Weights do not depend on earlier kernels: the first STAGES tiles of the weight operand
+      // are requested before this grid waits for its predecessors.
       // x_is_weight: 1 the X operand is the weight, 2 the Y operand is (the many-row orientation)
       const int pre = prm.x_is_weight ? min(STAGES, num_kb) : 0;
       const bool y_first = prm.x_is_weight == 2;
-      const uint32_t tx_bytes = make_y ? kXBytes : kStageBytes;
       for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&full_bar[i], tx_bytes);
+        mbar_expect_tx(&full_bar[i], kStageBytes);
         if (y_first)
           tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
         else
@@ -167,7 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (y_first) {
         for (int i = 0; i < pre; ++i)
           tma_load_2d(tiles + (size_t)i * kStageBytes, &tmX, &full_bar[i], (kb_begin + i) * kBK, p0);
-      } else if (!make_y) {
+      } else {
         for (int i = 0; i < pre; ++i)
           tma_load_2d(tiles + (size_t)i * kStageBytes + kXBytes, &tmY, &full_bar[i], (kb_begin + i) * kBK, q0);
       }
@@ -181,9 +212,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           break;
         }
         unsigned char* xs = tiles + (size_t)s * kStageBytes;
-        mbar_expect_tx(&full_bar[s], tx_bytes);
+        mbar_expect_tx(&full_bar[s], kStageBytes);
         tma_load_2d(xs, &tmX, &full_bar[s], (kb_begin + i) * kBK, p0);
-        if (!make_y) tma_load_2d(xs + kXBytes, &tmY, &full_bar[s], (kb_begin + i) * kBK, q0);
+        tma_load_2d(xs + kXBytes, &tmY, &full_bar[s], (kb_begin + i) * kBK, q0);
         issued = i + 1;
       }
       if (*(volatile int*)&abort_flag) {
@@ -220,83 +251,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   } else {
     // ---------------- epilogue: TMEM -> registers -> shared-memory stage
     const int quad = warp & 3;
-    pdl_wait();   // C may still be read by an earlier kernel
+    const int et = (int)threadIdx.x - 64;
+    pdl_wait();   // C may still be read by an earlier kernel; ss_in is written by the product in front
     bool ok = true;
+    if (scaled) {
+      // the factors of the norm in front: one per row of the activations, which are the tile's
+      // columns (few rows, transposed output) or its rows; the parts are added in their own order
+      if (prm.transpose_out) {
+        if (et < BN && et < 128) {
+          const int q = q0 + et;
+          float ss = 0.f;
+          if (q < prm.Q)
+            for (int t = 0; t < prm.ss_in_parts; ++t) ss += prm.ss_in[(size_t)q * prm.ss_in_parts + t];
+          inv_s[et] = rsqrtf(ss * prm.inv_width + prm.eps);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      } else {
+        const int pp = p0 + et;
+        float ss = 0.f;
+        if (pp < prm.P)
+          for (int t = 0; t < prm.ss_in_parts; ++t) ss += prm.ss_in[(size_t)pp * prm.ss_in_parts + t];
+        inv_row = rsqrtf(ss * prm.inv_width + prm.eps);
+      }
+    }
     if constexpr (BN == 16 && sizeof(TOut) == 4) {
       // accumulate: this thread's outputs (tile row threadIdx.x - 64, its rank's columns) are read
       // now, long before the sums arrive
-      if (!make_y) {        // (never together with a made activation operand: the launcher refuses that)
-        const int pp = p0 + (int)threadIdx.x - 64;
+      const int pp = p0 + et;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int jq = splits > 1 ? j * splits + (int)blockIdx.z : j;
-          const int q = q0 + jq;
-          old_c[j] = (prm.accumulate && jq < BN && q < prm.Q && pp < prm.P)
-                         ? reinterpret_cast<const float*>(C)[(long long)q * prm.ldc + pp] : 0.f;
-        }
+      for (int j = 0; j < 16; ++j) {
+        const int jq = splits > 1 ? j * splits + (int)blockIdx.z : j;
+        const int q = q0 + jq;
+        old_c[j] = (prm.accumulate && jq < BN && q < prm.Q && pp < prm.P)
+                       ? reinterpret_cast<const float*>(C)[(long long)q * prm.ldc + pp] : 0.f;
       }
     }
-    if constexpr (BN == 16) {
-      if (make_y) {
-        // ---------------- the activation tiles, made here: thread (row, piece) owns 8 consecutive
-        // columns of one of the 16 rows in every k-block; values are read PF k-blocks ahead.
-        const int pt = threadIdx.x - 64, row = pt >> 3, piece = pt & 7;
-        const int qrow = q0 + row;
-        const bool live = qrow < prm.Q;
-        const float* src = prm.y_resid + (size_t)(live ? qrow : 0) * prm.y_ld + piece * 8;
-        const __nv_bfloat16* wsrc = prm.norm_w + piece * 8;
-        constexpr int PF = 4;
-        float4 a0[PF], a1[PF];
-        uint4 wv[PF];
-        auto fetch = [&](int i, float4& x0, float4& x1, uint4& w) {
-          const int k = (kb_begin + i) * kBK;
-          if (live && i < num_kb && k + piece * 8 < prm.K) {
-            x0 = *reinterpret_cast<const float4*>(src + k);
-            x1 = *reinterpret_cast<const float4*>(src + k + 4);
-            w = *reinterpret_cast<const uint4*>(wsrc + k);
-          } else {
-            x0 = x1 = make_float4(0.f, 0.f, 0.f, 0.f);
-            w = make_uint4(0u, 0u, 0u, 0u);
-          }
-        };
+    if constexpr (BN >= 32 && sizeof(TOut) == 4) {
+      // the same for wide tiles that add as a cluster, when this block owns at most four groups of
+      // four columns (otherwise the values are read after the hand-over, two groups at a time)
+      if (prm.accumulate && prm.transpose_out && splits > 1 && (BN / 4 + splits - 1) / splits <= 4) {
+        const int pp = p0 + et;
+        const int nlg = (BN / 4 + splits - 1) / splits;
 #pragma unroll
-        for (int j = 0; j < PF; ++j) fetch(j, a0[j], a1[j], wv[j]);
-        // the row's sum of squares, asked for after the first values so that both are on their way together
-        float part = 0.f;
-        if (live)
-          for (int t = piece; t < prm.ss_tiles; t += 8) part += __ldg(prm.ss_in + (size_t)qrow * prm.ss_tiles + t);
-        part += __shfl_xor_sync(0xffffffffu, part, 1);
-        part += __shfl_xor_sync(0xffffffffu, part, 2);
-        part += __shfl_xor_sync(0xffffffffu, part, 4);
-        const float inv = rsqrtf(part / (float)prm.K + prm.eps);
-        // k-blocks in groups of PF, so that every buffer has a fixed register and a value is
-        // touched only when its k-block comes up (PF k-blocks after it was asked for)
-        for (int i0 = 0; i0 < num_kb && ok; i0 += PF) {
-#pragma unroll
-          for (int u = 0; u < PF; ++u) {
-            const int i = i0 + u;
-            if (i >= num_kb) break;
-            const int s = i % STAGES;
-            if (!mbar_wait(&empty_bar[s], ((i / STAGES) & 1) ^ 1) || *(volatile int*)&abort_flag) {
-              abort_flag = 1;
-              atomicOr(prm.status, kStatusWaitExpired);
-              ok = false;
-              break;
-            }
-            const float2 w01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].x));
-            const float2 w23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].y));
-            const float2 w45 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].z));
-            const float2 w67 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[u].w));
-            uint4 pk;
-            pk.x = pack_bf16x2(a0[u].x * inv * w01.x, a0[u].y * inv * w01.y);
-            pk.y = pack_bf16x2(a0[u].z * inv * w23.x, a0[u].w * inv * w23.y);
-            pk.z = pack_bf16x2(a1[u].x * inv * w45.x, a1[u].y * inv * w45.y);
-            pk.w = pack_bf16x2(a1[u].z * inv * w67.x, a1[u].w * inv * w67.y);
-            *reinterpret_cast<uint4*>(tiles + (size_t)s * kStageBytes + kXBytes + row * 128 + ((piece ^ (row & 7)) << 4)) = pk;
-            fence_async_smem();
-            mbar_arrive(&full_bar[s]);
-            fetch(i + PF, a0[u], a1[u], wv[u]);
-          }
+        for (int j = 0; j < 16; ++j) {
+          const int gq = (j >> 2) * splits + (int)blockIdx.z, q = q0 + 4 * gq + (j & 3);
+          old_c[j] = ((j >> 2) < nlg && gq < BN / 4 && q < prm.Q && pp < prm.P)
+                         ? reinterpret_cast<const float*>(C)[(long long)q * prm.ldc + pp] : 0.f;
         }
       }
     }
@@ -320,6 +320,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            r[j] = __float_as_uint(__uint_as_float(r[j]) * (prm.transpose_out ? inv_s[(ch * 16 + j) & 127] : inv_row));
         }
         if (BN >= 32 && prm.transpose_out) {
           // wide tiles are staged column by column (stage[column][tile row]): a warp writes 32
@@ -371,6 +376,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
+          if (scaled) {       // every block scales its own partials: the factor is the row's, not the split's
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              r[j] = __float_as_uint(__uint_as_float(r[j]) * (prm.transpose_out ? inv_s[(ch * 32 + j) & 127] : inv_row));
+          }
 #pragma unroll
           for (int g4 = 0; g4 < 8; ++g4) {
             const uint32_t local = recv + (uint32_t)(((rank * NLg + push_gl) * 128 + tr) * 16);
@@ -397,6 +407,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            r[j] = __float_as_uint(__uint_as_float(r[j]) * (prm.transpose_out ? inv_s[(ch * 16 + j) & 127] : inv_row));
+        }
         // output jq goes to rank jq % splits, slot jq / splits: both kept as running counters
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -414,11 +429,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (warp >= 2 && !dead) {
       const int pp = p0 + et;
+      const int ew = et >> 5;
       const float* mine = reinterpret_cast<const float*>(tiles);
       bool stored = false;
       if constexpr (BN == 16 && sizeof(TOut) == 4) {
         if (prm.accumulate) {
           stored = true;
+          const float nw = (prm.rb_out != nullptr && pp < prm.P) ? load_norm_w(prm.next_w, prm.next_w_f32, pp) : 0.f;
 #pragma unroll
           for (int jl = 0; jl < 8; ++jl) {               // NL <= 8: 16 outputs over at least 2 ranks
             const int jq = jl * splits + rank;
@@ -430,22 +447,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (pp < prm.P) {
               r = old_c[jl] + acc;
               reinterpret_cast<float*>(C)[(long long)q * prm.ldc + pp] = r;
+              if (prm.rb_out != nullptr) prm.rb_out[(long long)q * prm.ldc + pp] = __float2bfloat16_rn(r * nw);
             }
             const float v = warp_sum(r * r);
-            if (lane == 0) ss_red[et >> 5][jl] = v;
+            if (lane == 0) ss_red[ew][jl] = v;
           }
         }
       }
       if constexpr (BN >= 32) {
         const float4* mine4 = reinterpret_cast<const float4*>(tiles);
+        if constexpr (sizeof(TOut) == 4) {
+          if (prm.accumulate && prm.transpose_out) {
+            // Few rows (17..128), the weight's rows on the tile's rows: this block owns groups of four
+            // columns (= four rows of the activations) for all 128 outputs p of the tile.  The old
+            // values of two groups are asked for at once; the sums of squares of a column are joined
+            // over the four warps through shared memory.
+            stored = true;
+            const float nw = (prm.rb_out != nullptr && pp < prm.P) ? load_norm_w(prm.next_w, prm.next_w_f32, pp) : 0.f;
+            float* Cf = reinterpret_cast<float*>(C);
+            // one owned group: the partials of all ranks in rank order, added to the old values, stored;
+            // the column's sum of squares over this warp's 32 rows goes to shared memory
+            auto add_group = [&](int gl, float o0, float o1, float o2, float o3) {
+              const int gq = gl * splits + rank, q = q0 + 4 * gq;
+              if (gq >= kGroups || q >= prm.Q) return;
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int z = 0; z < splits; ++z) {
+                const float4 v = mine4[(z * NLg + gl) * 128 + et];
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+              }
+              const float val[4] = {o0 + acc.x, o1 + acc.y, o2 + acc.z, o3 + acc.w};
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                if (q + c >= prm.Q) break;
+                float r = 0.f;
+                if (pp < prm.P) {
+                  r = val[c];
+                  Cf[(long long)(q + c) * prm.ldc + pp] = r;
+                  if (prm.rb_out != nullptr) prm.rb_out[(long long)(q + c) * prm.ldc + pp] = __float2bfloat16_rn(r * nw);
+                }
+                const float v = warp_sum(r * r);
+                if (lane == 0 && gl * 4 + c < kSsSlots) ss_red[ew][gl * 4 + c] = v;
+              }
+            };
+            if (NLg <= 4) {
+              // the old values were asked for at the start of the epilogue (old_c)
+#pragma unroll
+              for (int gl = 0; gl < 4; ++gl)
+                if (gl < NLg) add_group(gl, old_c[4 * gl], old_c[4 * gl + 1], old_c[4 * gl + 2], old_c[4 * gl + 3]);
+            } else {
+              for (int gl0 = 0; gl0 < NLg; gl0 += 2) {
+                float old[2][4];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const int gq = (gl0 + u) * splits + rank, q = q0 + 4 * gq;
+                  const bool okg = gl0 + u < NLg && gq < kGroups && q < prm.Q;
+#pragma unroll
+                  for (int c = 0; c < 4; ++c)
+                    old[u][c] = (okg && q + c < prm.Q && pp < prm.P) ? Cf[(long long)(q + c) * prm.ldc + pp] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                  if (gl0 + u < NLg) add_group(gl0 + u, old[u][0], old[u][1], old[u][2], old[u][3]);
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (prm.ss_out != nullptr && et < NLg * 4 && et < kSsSlots) {
+              const int gq = (et >> 2) * splits + rank, q = q0 + 4 * gq + (et & 3);
+              if (gq < kGroups && q < prm.Q)
+                prm.ss_out[(size_t)q * prm.ss_parts + blockIdx.x] =
+                    (ss_red[0][et] + ss_red[1][et]) + (ss_red[2][et] + ss_red[3][et]);
+            }
+          }
+        }
         // Adding into the residual in the plain orientation: the old values of four groups are asked
         // for at once (one trip to L2 for four groups instead of one trip each, in a row of them).
         bool batched = false;
         if constexpr (sizeof(TOut) == 4) {
-          if (prm.accumulate && !prm.transpose_out && pp < prm.P && prm.ldc % 4 == 0 &&
+          if (!stored && prm.accumulate && !prm.transpose_out && pp < prm.P && prm.ldc % 4 == 0 &&
               (reinterpret_cast<uintptr_t>(C) % 16) == 0) {
             batched = true;
             float* crow = reinterpret_cast<float*>(C) + (long long)pp * prm.ldc + q0;
+            __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)pp * prm.ldc + q0 : nullptr;
+            float ss_acc = 0.f;
             for (int gl0 = 0; gl0 < NLg; gl0 += 4) {
               float4 old[4];
               bool ok[4];
@@ -466,11 +549,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 }
                 acc.x += old[u].x; acc.y += old[u].y; acc.z += old[u].z; acc.w += old[u].w;
                 *reinterpret_cast<float4*>(crow + 4 * gq) = acc;
+                ss_acc += (acc.x * acc.x + acc.y * acc.y) + (acc.z * acc.z + acc.w * acc.w);
+                if (rbrow != nullptr) {
+                  const long long f = q0 + 4 * gq;
+                  uint2 pk;
+                  pk.x = pack_bf16x2(acc.x * load_norm_w(prm.next_w, prm.next_w_f32, f),
+                                     acc.y * load_norm_w(prm.next_w, prm.next_w_f32, f + 1));
+                  pk.y = pack_bf16x2(acc.z * load_norm_w(prm.next_w, prm.next_w_f32, f + 2),
+                                     acc.w * load_norm_w(prm.next_w, prm.next_w_f32, f + 3));
+                  *reinterpret_cast<uint2*>(rbrow + 4 * gq) = pk;
+                }
               }
             }
+            // this block's share of the row's sum of squares (the launcher only asks for it when every
+            // group is whole, so nothing is left to the loop below)
+            if (prm.ss_out != nullptr) prm.ss_out[(size_t)pp * prm.ss_parts + blockIdx.y * splits + rank] = ss_acc;
           }
         }
-        for (int gl = 0; gl < NLg; ++gl) {
+        for (int gl = 0; gl < NLg && !stored; ++gl) {
           const int gq = gl * splits + rank;
           if (gq >= kGroups || q0 + 4 * gq >= prm.Q) break;
           if (batched && q0 + 4 * gq + 3 < prm.Q) continue;      // done above
@@ -535,8 +631,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (prm.accumulate) {
           asm volatile("bar.sync 1, 128;" ::: "memory");
           const int jq = et * splits + rank;
-          if (et < NL && jq < BN && q0 + jq < prm.Q)
-            prm.ss_out[(size_t)(q0 + jq) * gridDim.x + blockIdx.x] =
+          if (prm.ss_out != nullptr && et < NL && jq < BN && q0 + jq < prm.Q)
+            prm.ss_out[(size_t)(q0 + jq) * prm.ss_parts + blockIdx.x] =
                 (ss_red[0][et] + ss_red[1][et]) + (ss_red[2][et] + ss_red[3][et]);
         }
       }
@@ -596,6 +692,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       bool stored = false;
       if constexpr (BN == 16 && sizeof(TOut) == 4) {
         if (prm.accumulate) {
+          const float nw = (prm.rb_out != nullptr && pp < prm.P) ? load_norm_w(prm.next_w, prm.next_w_f32, pp) : 0.f;
 #pragma unroll
           for (int jq = 0; jq < 16; ++jq) {
             if (jq >= cols) break;
@@ -603,13 +700,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             if (pp < prm.P) {
               r = old_c[jq] + stage[et * LD + jq];
               reinterpret_cast<float*>(C)[(long long)(q0 + jq) * prm.ldc + pp] = r;
+              if (prm.rb_out != nullptr) prm.rb_out[(long long)(q0 + jq) * prm.ldc + pp] = __float2bfloat16_rn(r * nw);
             }
             const float v = warp_sum(r * r);
             if (lane == 0) ss_red[ew][jq] = v;
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et < cols)
-            prm.ss_out[(size_t)(q0 + et) * gridDim.x + blockIdx.x] =
+          if (prm.ss_out != nullptr && et < cols)
+            prm.ss_out[(size_t)(q0 + et) * prm.ss_parts + blockIdx.x] =
                 (ss_red[0][et] + ss_red[1][et]) + (ss_red[2][et] + ss_red[3][et]);
           stored = true;
         }
@@ -657,11 +755,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   }
 }
 
+
+// The factor of the norm in front of a product for row p of its activations (1 without such a norm):
+// the parts of the row's sum of squares are added in their own order, whatever block wrote them.
+__device__ __forceinline__ float norm_row_factor(const GemmParams& prm, int p) {
+  if (prm.ss_in == nullptr || p >= prm.P) return 1.f;
+  float ss = 0.f;
+  for (int t = 0; t < prm.ss_in_parts; ++t) ss += prm.ss_in[(size_t)p * prm.ss_in_parts + t];
+  return rsqrtf(ss * prm.inv_width + prm.eps);
+}
+
 // 32 consecutive accumulators of tile row p (columns q .. q + 31) to C: plain, added into C
-// (accumulate), or as 16 silu(gate) * up values (swiglu).
+// (accumulate), or as 16 silu(gate) * up values (swiglu).  With ss_in the accumulators are first
+// multiplied by row_scale, the factor of the norm in front of this product for row p.  An
+// accumulating product with rb_out also writes bf16(new C * next_w) to rbrow and returns the sum
+// of squares of the new C values it stored (0 otherwise).
 template <typename TOut>
-__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], TOut* crow, int p, int q, const GemmParams& prm,
-                                            bool vec_ok) {
+__device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv_bfloat16* rbrow, int p, int q,
+                                             const GemmParams& prm, bool vec_ok, float row_scale) {
+  float ss = 0.f;
+  if (prm.ss_in != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * row_scale);
+  }
   if (prm.swiglu) {
     // columns are (gate_j, up_j) pairs: 16 outputs from these 32 accumulators
     if (p < prm.P && q < prm.Q) {
@@ -695,10 +811,27 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], TOut* crow,
 #pragma unroll
           for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(crow + q + 4 * j);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<float4*>(crow + q + 4 * j) =
-                make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
-                            old[j].z + __uint_as_float(r[4 * j + 2]), old[j].w + __uint_as_float(r[4 * j + 3]));
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
+                                         old[j].z + __uint_as_float(r[4 * j + 2]), old[j].w + __uint_as_float(r[4 * j + 3]));
+            *reinterpret_cast<float4*>(crow + q + 4 * j) = v;
+            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+            r[4 * j] = __float_as_uint(v.x); r[4 * j + 1] = __float_as_uint(v.y);
+            r[4 * j + 2] = __float_as_uint(v.z); r[4 * j + 3] = __float_as_uint(v.w);
+          }
+          if (rbrow != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float w[8];
+              load_norm_w8(prm.next_w, prm.next_w_f32, q + j, w);
+              uint4 pk;
+              pk.x = pack_bf16x2(__uint_as_float(r[j]) * w[0], __uint_as_float(r[j + 1]) * w[1]);
+              pk.y = pack_bf16x2(__uint_as_float(r[j + 2]) * w[2], __uint_as_float(r[j + 3]) * w[3]);
+              pk.z = pack_bf16x2(__uint_as_float(r[j + 4]) * w[4], __uint_as_float(r[j + 5]) * w[5]);
+              pk.w = pack_bf16x2(__uint_as_float(r[j + 6]) * w[6], __uint_as_float(r[j + 7]) * w[7]);
+              *reinterpret_cast<uint4*>(rbrow + q + j) = pk;
+            }
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
@@ -723,13 +856,17 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], TOut* crow,
         if (q + j < prm.Q) {
           float v = __uint_as_float(r[j]);
           if constexpr (sizeof(TOut) == 4) {
-            if (prm.accumulate) v += reinterpret_cast<const float*>(crow)[q + j];
+            if (prm.accumulate) {
+              v += reinterpret_cast<const float*>(crow)[q + j];
+              ss += v * v;
+              if (rbrow != nullptr) rbrow[q + j] = __float2bfloat16_rn(v * load_norm_w(prm.next_w, prm.next_w_f32, q + j));
+            }
           }
           store_out<TOut>(crow + q + j, v);
         }
     }
   }
-
+  return ss;
 }
 
 // ------------------------------------------------------------------ persistent kernel (many rows)
@@ -852,22 +989,26 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++i) {
       const int acc = i & 1;
       const int p0 = (t % tiles_p) * kBM, q0 = (t / tiles_p) * BN;
+      const int p = p0 + quad * 32 + lane;
+      const float row_scale = norm_row_factor(prm, p);     // read while the tile's main loop still runs
       if (!mbar_wait(&tfull_bar[acc], (i >> 1) & 1) || *(volatile int*)&abort_flag) {
         abort_flag = 1;
         atomicOr(prm.status, kStatusWaitExpired);
         break;
       }
       tc_fence_after();
-      const int p = p0 + quad * 32 + lane;
       TOut* crow = C + (long long)p * prm.ldc;
+      __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)p * prm.ldc : nullptr;
+      float ss = 0.f;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
         uint32_t r[32];
         SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int q = q0 + ch * 32;
-        store_chunk<TOut>(r, crow, p, q, prm, vec_ok);
+        ss += store_chunk<TOut>(r, crow, rbrow, p, q, prm, vec_ok, row_scale);
       }
+      if (prm.ss_out != nullptr && p < prm.P) prm.ss_out[(size_t)p * prm.ss_parts + t / tiles_p] = ss;
       // this accumulator may be overwritten once all four epilogue warps have read it
       tc_fence_before();
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1004,21 +1145,25 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
     for (int t = pair; t < n_tiles; t += n_pairs, ++i) {
       const int acc = i & 1;
       const int p0 = (t % tiles_p) * 2 * kBM + rank * kBM, q0 = (t / tiles_p) * BN;
+      const int p = p0 + quad * 32 + lane;
+      const float row_scale = norm_row_factor(prm, p);     // read while the tile's main loop still runs
       if (!mbar_wait(&tfull_bar[acc], (i >> 1) & 1) || *(volatile int*)&abort_flag) {
         abort_flag = 1;
         atomicOr(prm.status, kStatusWaitExpired);
         break;
       }
       tc_fence_after();
-      const int p = p0 + quad * 32 + lane;
       TOut* crow = C + (long long)p * prm.ldc;
+      __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)p * prm.ldc : nullptr;
+      float ss = 0.f;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
         uint32_t r[32];
         SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        store_chunk<TOut>(r, crow, p, q0 + ch * 32, prm, vec_ok);
+        ss += store_chunk<TOut>(r, crow, rbrow, p, q0 + ch * 32, prm, vec_ok, row_scale);
       }
+      if (prm.ss_out != nullptr && p < prm.P) prm.ss_out[(size_t)p * prm.ss_parts + t / tiles_p] = ss;
       tc_fence_before();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) mbar_arrive_even(&tempty_bar[acc]);
@@ -1168,55 +1313,108 @@ constexpr int kPairRows = 4096;
 // worth of splits per SM made a decode step 4-6% slower).
 constexpr int kSplitTarget = 1;
 
-// Returns 0 on launch, a cudaError_t on failure, and -1 when the shape is one this
-// unit does not take (the caller then uses the CUDA-core kernel).
-//   A [M,K], W [N,K] bf16 row-major; C [M,N] bf16 (out_f32 == 0) or float32.
-//   max_splits caps the split along K (1 = never split; at most 8, the portable cluster size).
-//   epilogue 1: W's rows are interleaved (gate_0, up_0, gate_1, up_1, ...) and C [M, N/2] bf16 receives
-//   silu(gate) * up (never split along K).
-//   epilogue 2: C [M,N] float32 += the product.  At most 16 rows: ss_out [M, ceil(N/128)] also receives, per
-//   block of 128 outputs, the sum of squares of the new C (what the rmsnorm that follows needs).  More than
-//   128 rows (the persistent kernel): the sum only.  17..128 rows: refused.
-//   resid != nullptr (at most 16 rows; A is not read): the activations are rmsnorm(resid [M,K] float32) *
-//   norm_w with eps, the sums of squares of the rows given in pieces as ss_in [M, ss_tiles].
-static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, int out_f32, int max_splits,
-                    int epilogue, int* status, int sm_count, void* stream, const float* resid, const float* ss_in,
-                    int ss_tiles, const void* norm_w, float eps, float* ss_out, int pair_mode) {
-  if (M <= 0 || N <= 0) return 0;
-  if (epilogue < 0 || epilogue > 2) return -1;
-  if (epilogue == 1 && (out_f32 || (N & 1))) return -1;
-  if (epilogue == 2 && (!out_f32 || (M <= 16 && ss_out == nullptr) || (M > 16 && M <= 128))) return -1;
-  if (resid != nullptr && epilogue == 2) return -1;
-  if (resid != nullptr && (M > 16 || ss_in == nullptr || norm_w == nullptr || ss_tiles <= 0)) return -1;
-  if (epilogue == 1) max_splits = 1;
-  if (K % 8 != 0 || K < 8) return -1;                       // TMA needs 16-byte row strides
-  if (resid != nullptr) A = W;                               // a valid (unused) operand for the tensor map
-  if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)resid | (uintptr_t)norm_w) & 15) return -1;
-  cudaStream_t s = (cudaStream_t)stream;
-  const bool swap = M <= 128;
-  const void* X = swap ? W : A;
-  const void* Y = swap ? A : W;
-  const int P = swap ? N : M, Q = swap ? M : N;
-  int BN;
-  if (swap) BN = Q <= 16 ? 16 : Q <= 32 ? 32 : Q <= 64 ? 64 : 128;
-  else BN = Q >= 256 ? 256 : 128;
-  CUtensorMap tmX, tmY;
-  if (!tensor_map(X, P, K, kBM, &tmX)) return -1;
-  if (resid != nullptr) tmY = tmX;
-  else if (!tensor_map(Y, Q, K, BN, &tmY)) return -1;
+// How a product of these sizes runs: orientation, tile width, split along K and kernel.
+struct GemmPlan {
+  bool swap;          // few rows: the weight on the MMA's row axis, the output written transposed
+  int P, Q, BN;
+  int splits, kbps;   // small kernel: blocks per output tile along K, k-blocks of 64 per block
+  int kernel;         // 0 small kernel, 1 small kernel as clusters in the plain orientation, 2 pairs of SMs, 3 persistent
+  int ss_parts;       // parts of a row's sum of squares an accumulating launch writes (0: it cannot)
+};
 
-  const int tiles = ((P + kBM - 1) / kBM) * ((Q + BN - 1) / BN);
+static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_count, int pair_mode, GemmPlan* out) {
+  GemmPlan g;
+  g.swap = M <= 128;
+  g.P = g.swap ? N : M;
+  g.Q = g.swap ? M : N;
+  if (g.swap) g.BN = g.Q <= 16 ? 16 : g.Q <= 32 ? 32 : g.Q <= 64 ? 64 : 128;
+  else g.BN = g.Q >= 256 ? 256 : 128;
+  if (epilogue == 1) max_splits = 1;
+  const int tiles = ((g.P + kBM - 1) / kBM) * ((g.Q + g.BN - 1) / g.BN);
   const int num_kb = (K + kBK - 1) / kBK;
   int splits = 1;
-  if (swap && tiles < kSplitTarget * sm_count) {
+  if (g.swap && tiles < kSplitTarget * sm_count) {
     splits = (kSplitTarget * sm_count + tiles - 1) / tiles;
     if (splits > 8) splits = 8;
     if (splits > max_splits) splits = max_splits;
     if (splits > num_kb / 4) splits = num_kb / 4;
     if (splits < 1) splits = 1;
   }
-  int kbps = (num_kb + splits - 1) / splits;
-  splits = (num_kb + kbps - 1) / kbps;
+  g.kbps = (num_kb + splits - 1) / splits;
+  g.splits = (num_kb + g.kbps - 1) / g.kbps;
+  g.kernel = g.swap ? 0 : 3;
+  g.ss_parts = 0;
+  if (g.swap) {
+    // 16-column tiles add with or without a split; wider ones only as clusters (the owner blocks add)
+    if (g.BN == 16 || g.splits > 1) g.ss_parts = (N + kBM - 1) / kBM;
+    else if (epilogue == 2) return false;
+  } else {
+    // Prompts of a few hundred tokens give the many-row orientation fewer tiles than there are SMs,
+    // and a tile's block then streams its weight rows alone, at a single SM's share of the bandwidth.
+    // Those products run on the small-batch kernel in this orientation instead: a cluster of blocks
+    // per 128 x 256 tile, each with a slice of K, partial sums joined through distributed shared memory.
+    if (g.BN == 256 && epilogue != 1 && tiles < sm_count) {
+      int sp = sm_count / tiles;              // one block to an SM (192 KB of pipeline stages): one wave
+      sp = sp >= 8 ? 8 : sp >= 4 ? 4 : sp >= 2 ? 2 : 1;      // clusters of 3, 5, 6 or 7 do not all find room at once
+      if (sp > max_splits) sp = max_splits;
+      if (sp > num_kb / 4) sp = num_kb / 4;
+      if (sp >= 2) {
+        const int per = (num_kb + sp - 1) / sp;
+        sp = (num_kb + per - 1) / per;
+        if (sp >= 2) {
+          g.kernel = 1;
+          g.splits = sp;
+          g.kbps = per;
+          g.ss_parts = N % 4 == 0 ? ((N + 255) / 256) * sp : 0;
+        }
+      }
+    }
+    if (g.kernel == 3) {
+      if (g.BN == 256 && sm_count >= 2 && (pair_mode >= 2 || (pair_mode == 1 && g.P >= kPairRows))) g.kernel = 2;
+      g.ss_parts = (N + g.BN - 1) / g.BN;
+    }
+  }
+  *out = g;
+  return true;
+}
+
+// Returns 0 on launch, a cudaError_t on failure, and -1 when the shape is one this
+// unit does not take (the caller then uses the CUDA-core kernel).
+//   A [M,K], W [N,K] bf16 row-major; C [M,N] bf16 (out_f32 == 0) or float32.
+//   max_splits caps the split along K (1 = never split; at most 8, the portable cluster size).
+//   epilogue 1: W's rows are interleaved (gate_0, up_0, gate_1, up_1, ...) and C [M, N/2] bf16 receives
+//   silu(gate) * up (never split along K).
+//   epilogue 2: C [M,N] float32 += the product.  With rb_out [M,N] bf16, next_w [N] and ss_out
+//   [M, ss_out_parts] it also leaves what the product after the next RMSNorm needs: bf16(new C * next_w)
+//   and the rows' sums of squares in ss_out_parts parts (siar_gemm_tc_ss_parts says how many; refused when
+//   that does not match).
+//   ss_in != nullptr: A is such an rb; the rows of the product are multiplied by
+//   rsqrt(sum(ss_in[row][0..ss_in_parts)) / K + eps) before the epilogue's activation and the store.
+static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, int out_f32, int max_splits,
+                    int epilogue, int* status, int sm_count, void* stream, const float* ss_in, int ss_in_parts,
+                    float eps, float* ss_out, int ss_out_parts, void* rb_out, const void* next_w, int next_w_f32,
+                    int pair_mode) {
+  if (M <= 0 || N <= 0) return 0;
+  if (epilogue < 0 || epilogue > 2) return -1;
+  if (epilogue == 1 && (out_f32 || (N & 1))) return -1;
+  if (epilogue == 2 && !out_f32) return -1;
+  if (ss_in != nullptr && (epilogue == 2 || ss_in_parts <= 0)) return -1;
+  if (epilogue != 2 && (ss_out != nullptr || rb_out != nullptr)) return -1;
+  if ((ss_out != nullptr) != (rb_out != nullptr) || (rb_out != nullptr && next_w == nullptr)) return -1;
+  if (K % 8 != 0 || K < 8) return -1;                       // TMA needs 16-byte row strides
+  if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)rb_out) & 15) return -1;
+  cudaStream_t s = (cudaStream_t)stream;
+  GemmPlan g;
+  if (!make_plan(M, N, K, epilogue, max_splits, sm_count, pair_mode, &g)) return -1;
+  if (ss_out != nullptr && (g.ss_parts == 0 || g.ss_parts != ss_out_parts || N % 8 != 0)) return -1;
+  const bool swap = g.swap;
+  const void* X = swap ? W : A;
+  const void* Y = swap ? A : W;
+  const int P = g.P, Q = g.Q, BN = g.BN;
+  CUtensorMap tmX, tmY;
+  if (!tensor_map(X, P, K, kBM, &tmX)) return -1;
+  if (!tensor_map(Y, Q, K, BN, &tmY)) return -1;
+  const int splits = g.splits;
 
   GemmParams prm;
   prm.C = C;
@@ -1225,41 +1423,27 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
   prm.ldc = epilogue == 1 ? N / 2 : N;
   prm.swiglu = epilogue == 1 ? 1 : 0;
   prm.transpose_out = swap ? 1 : 0;
-  prm.kb_per_split = kbps;
+  prm.kb_per_split = g.kbps;
   prm.x_is_weight = swap ? 1 : 0;
   prm.accumulate = epilogue == 2 ? 1 : 0;
   prm.ss_out = ss_out;
-  prm.y_resid = resid;
+  prm.ss_parts = ss_out_parts;
+  prm.rb_out = (__nv_bfloat16*)rb_out;
+  prm.next_w = next_w;
+  prm.next_w_f32 = next_w_f32;
   prm.ss_in = ss_in;
-  prm.norm_w = (const __nv_bfloat16*)norm_w;
+  prm.ss_in_parts = ss_in_parts;
+  prm.inv_width = 1.f / (float)K;
   prm.eps = eps;
-  prm.ss_tiles = ss_tiles;
-  prm.y_ld = K;
 #ifdef SIAR_TIMING
   prm.stamps = g_stamps;
 #endif
 
-  // Prompts of a few hundred tokens give the many-row orientation fewer tiles than there are SMs,
-  // and a tile's block then streams its weight rows alone, at a single SM's share of the bandwidth.
-  // Those products run on the small-batch kernel in this orientation instead: a cluster of blocks
-  // per 128 x 256 tile, each with a slice of K, partial sums joined through distributed shared memory.
-  if (!swap && BN == 256 && epilogue != 1 && tiles < sm_count) {
-    int sp = sm_count / tiles;              // one block to an SM (192 KB of pipeline stages): one wave
-    sp = sp >= 8 ? 8 : sp >= 4 ? 4 : sp >= 2 ? 2 : 1;      // clusters of 3, 5, 6 or 7 do not all find room at once
-    if (sp > max_splits) sp = max_splits;
-    if (sp > num_kb / 4) sp = num_kb / 4;
-    if (sp >= 2) {
-      const int per = (num_kb + sp - 1) / sp;
-      sp = (num_kb + per - 1) / per;
-      prm.kb_per_split = per;
-      prm.x_is_weight = 2;
-      if (sp >= 2)
-        return out_f32 ? launch<256, 4, float>(tmX, tmY, prm, sp, s) : launch<256, 4, __nv_bfloat16>(tmX, tmY, prm, sp, s);
-      prm.kb_per_split = kbps;
-      prm.x_is_weight = 0;
-    }
+  if (g.kernel == 1) {
+    prm.x_is_weight = 2;
+    return out_f32 ? launch<256, 4, float>(tmX, tmY, prm, splits, s) : launch<256, 4, __nv_bfloat16>(tmX, tmY, prm, splits, s);
   }
-  if (!swap && BN == 256 && sm_count >= 2 && (pair_mode >= 2 || (pair_mode == 1 && P >= kPairRows))) {
+  if (g.kernel == 2) {
     CUtensorMap tmY2;
     if (tensor_map(Y, Q, K, 128, &tmY2))
       return out_f32 ? launch_pair<6, float>(tmX, tmY2, prm, sm_count, s)
@@ -1289,15 +1473,25 @@ extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, i
                                  int max_splits, int epilogue, int* status, int sm_count, void* stream,
                                  int pair_mode) {
   if (epilogue == 2) return -1;
-  return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, nullptr, nullptr, 0,
-                  nullptr, 0.f, nullptr, pair_mode);
+  return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, nullptr, 0, 0.f, nullptr,
+                  0, nullptr, nullptr, 0, pair_mode);
 }
 
-// The same product inside a float32 residual stream, for at most 16 rows (see run_gemm).
+// Parts of a row's sum of squares that siar_gemm_tc_bf16_fused writes to ss_out for an accumulating
+// product (epilogue 2) of these sizes; 0 when such a launch cannot leave them.
+extern "C" int siar_gemm_tc_ss_parts(int M, int N, int K, int max_splits, int sm_count, int pair_mode) {
+  GemmPlan g;
+  if (M <= 0 || N <= 0 || K % 8 != 0 || K < 8 || N % 8 != 0) return 0;
+  if (!make_plan(M, N, K, 2, max_splits, sm_count, pair_mode, &g)) return 0;
+  return g.ss_parts;
+}
+
+// The same product inside a float32 residual stream (see run_gemm and GemmParams).
 extern "C" int siar_gemm_tc_bf16_fused(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
                                        int max_splits, int epilogue, int* status, int sm_count, void* stream,
-                                       const float* resid, const float* ss_in, int ss_tiles, const void* norm_w,
-                                       float eps, float* ss_out, int pair_mode) {
-  return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, resid, ss_in, ss_tiles,
-                  norm_w, eps, ss_out, pair_mode);
+                                       const float* ss_in, int ss_in_parts, float eps, float* ss_out,
+                                       int ss_out_parts, void* rb_out, const void* next_w, int next_w_f32,
+                                       int pair_mode) {
+  return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, ss_in, ss_in_parts, eps,
+                  ss_out, ss_out_parts, rb_out, next_w, next_w_f32, pair_mode);
 }

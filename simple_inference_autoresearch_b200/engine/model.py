@@ -66,6 +66,8 @@ class StepContext:
         self.cache = cache
         self.options = options
         self.residual = None      # set by a block: the stream a sublayer's last product may add into
+        self.next_norm = None     # set by a block: ops.NormHint of the norm after the running sublayer
+        self.norm_after_block = None      # set by the model: the hint of the norm the next block (or the model) applies first
 
 
 class DecoderModel:
@@ -156,12 +158,19 @@ class DecoderModel:
         residual = ops.embed(meta.tokens, self.embedding)
         self.position.at_embedding(ctx, residual)
         pending = None
-        for e in self.schedule:
+        # the final norm's inputs can only come from the last block's product when every row is wanted
+        last_hint = self.final_norm.hint() if (meta.want_is_identity and meta.n_want > 0) else None
+        for i, e in enumerate(self.schedule):
+            nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            ctx.norm_after_block = last_hint if nxt is None else nxt.first_norm_hint()
             residual, pending = self.layers[e.layer].forward(ctx, residual, pending, cache.entry(e.cache_entry),
                                                              e.writes_cache)
         if meta.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         if isinstance(pending, ops.Added):      # the last sublayer added itself
+            if meta.want_is_identity and pending.ss_parts is not None:
+                return ops.linear(self.final_norm.deferred(ctx, residual, pending), self.head, torch.float32,
+                                  options=options)
             pending = None
         if not meta.want_is_identity:
             residual = ops.gather_rows(residual, meta.want_rows)

@@ -39,11 +39,24 @@ def _bind_fused():
         f = build.load_unit("gemm_tc").siar_gemm_tc_bf16_fused
         c = ctypes
         f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
-                      c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_float,
-                      c.c_void_p, c.c_int]
+                      c.c_void_p, c.c_int, c.c_void_p,
+                      c.c_void_p, c.c_int, c.c_float,                         # ss_in, its parts, eps
+                      c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_int,   # ss_out, its parts, rb_out, next_w, next_w_f32
+                      c.c_int]
         f.restype = c.c_int
         _fn_fused = f
     return _fn_fused
+
+
+def ss_parts(m: int, n: int, k: int, device, options: KernelOptions = DEFAULT) -> int:
+    """Parts per row of the sum of squares that an adding product [m, k] x [n, k]^T leaves for the norm
+    that follows (the second dimension of ``ss_out``); 0 when a product of these sizes cannot."""
+    if not options.use_tc_gemm:
+        return 0
+    f = build.load_unit("gemm_tc").siar_gemm_tc_ss_parts
+    f.argtypes = [ctypes.c_int] * 6
+    f.restype = ctypes.c_int
+    return int(f(m, n, k, options.max_splits, _device_state(torch.device(device))["sms"], options.pair_mode))
 
 
 def _device_state(device: torch.device):
@@ -55,15 +68,16 @@ def _device_state(device: torch.device):
     return st
 
 
-def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=None, ss_out=None,
-               options: KernelOptions = DEFAULT) -> bool:
+def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=None, ss_out=None, rb_out=None,
+               next_w=None, options: KernelOptions = DEFAULT) -> bool:
     """out[M, N] = x[M, K] @ w[N, K]^T; False when the shape is refused (nothing launched).
     ``epilogue=1``: w's rows alternate (gate, up) and out[M, N/2] = silu(gate) * up.
-    ``epilogue=2``: out (float32) += the product; for at most 16 rows ``ss_out`` [M, ceil(N/128)]
-    also receives partial sums of squares of the new rows of out (more than 128 rows: no sums;
-    17..128 rows are refused).
-    ``normed`` (an ``ops.NormedResidual`` of at most 16 rows; x is None): the kernel makes the
-    activations rmsnorm(residual) * weight itself.
+    ``epilogue=2``: out (float32) += the product.  With ``ss_out`` [M, ss_parts(...)] float32, ``rb_out``
+    [M, N] bfloat16 and ``next_w`` [N] (the weight of the RMSNorm that follows) the kernel also leaves
+    the rows' sums of squares of the new ``out`` in parts and bf16(out * next_w): what the product
+    after that norm needs in place of the normed activations.
+    ``normed`` (an ``ops.NormedResidual`` whose ``scaled`` is such a tensor; x is None): the product's
+    rows are multiplied by the norm's factors rsqrt(mean square + eps) on the accumulators.
     ``options``: ``use_tc_gemm`` False refuses everything; ``max_splits`` and ``pair_mode`` as in ``KernelOptions``."""
     if not options.use_tc_gemm:
         return False
@@ -75,19 +89,25 @@ def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=
     status = ops.status_word(dev).data_ptr()
     stream = torch.cuda.current_stream().cuda_stream
     if normed is not None or epilogue == 2:
+        consumer = (None, 0, 0.0)
+        producer = (None, 0, None, None, 0)
         if normed is not None:
-            m, k = normed.residual.shape
-            assert k == w.shape[1] and normed.ss_parts.shape[0] == m and normed.ss_parts.is_contiguous()
-            extra = (normed.residual.data_ptr(), normed.ss_parts.data_ptr(), normed.ss_parts.shape[1],
-                     normed.weight.data_ptr(), float(normed.eps))
-            xp = None
-        else:
-            m, k = x.shape
-            extra = (None, None, 0, None, 0.0)
-            xp = x.data_ptr()
-        err = _bind_fused()(xp, w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
-                            options.max_splits, int(epilogue), status, st["sms"], stream, *extra,
-                            None if ss_out is None else ss_out.data_ptr(), options.pair_mode)
+            x = normed.scaled
+            assert x.dtype == torch.bfloat16 and x.is_contiguous() and normed.ss_parts.is_contiguous()
+            assert normed.ss_parts.shape[0] == x.shape[0] and normed.ss_parts.dtype == torch.float32
+            consumer = (normed.ss_parts.data_ptr(), normed.ss_parts.shape[1], float(normed.eps))
+        m, k = x.shape
+        assert k == w.shape[1]
+        if ss_out is not None:
+            assert rb_out is not None and next_w is not None and next_w.numel() == n and next_w.is_contiguous()
+            assert ss_out.dtype == torch.float32 and ss_out.shape[0] == m and ss_out.is_contiguous()
+            assert rb_out.dtype == torch.bfloat16 and rb_out.shape == (m, n) and rb_out.is_contiguous()
+            assert next_w.dtype in (torch.float32, torch.bfloat16) and next_w.data_ptr() % 16 == 0
+            producer = (ss_out.data_ptr(), ss_out.shape[1], rb_out.data_ptr(), next_w.data_ptr(),
+                        int(next_w.dtype == torch.float32))
+        err = _bind_fused()(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
+                            options.max_splits, int(epilogue), status, st["sms"], stream, *consumer, *producer,
+                            options.pair_mode)
     else:
         m, k = x.shape
         err = _bind()(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),

@@ -189,29 +189,44 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     return out
 
 
+class NormHint:
+    """What a sublayer's last product is told of the RMSNorm that follows it, so that it can leave
+    that norm's inputs behind: the norm's weight (and eps, for the record)."""
+
+    __slots__ = ("weight", "eps")
+
+    def __init__(self, weight: torch.Tensor, eps: float):
+        self.weight, self.eps = weight, eps
+
+
 class Added:
     """Stands for a sublayer output that the product kernel has already added into the residual
-    stream.  ``ss_parts`` [rows, pieces] float32 holds, for every row, partial sums of squares of
-    the updated residual: what the rmsnorm that follows needs instead of a pass over the row
-    (None when the kernel only added: the norm then runs as a kernel, without an add)."""
+    stream.  When the product knew the norm that follows (``NormHint``) it also left
+    ``ss_parts`` [rows, parts] float32, partial sums of squares of every row of the updated residual,
+    and ``scaled`` [rows, H] bfloat16 = residual * ``weight`` (that norm's weight): with
+    rmsnorm(r) W^T = rsqrt(mean(r^2) + eps) * ((r * w) W^T) the next product takes ``scaled`` as its
+    operand and applies the row factors to its accumulators, and no norm kernel runs.  All three are
+    None when the kernel only added (the norm then runs as a kernel, without an add)."""
 
-    __slots__ = ("ss_parts",)
+    __slots__ = ("ss_parts", "scaled", "weight")
 
-    def __init__(self, ss_parts: torch.Tensor):
-        self.ss_parts = ss_parts
+    def __init__(self, ss_parts: Optional[torch.Tensor] = None, scaled: Optional[torch.Tensor] = None,
+                 weight: Optional[torch.Tensor] = None):
+        self.ss_parts, self.scaled, self.weight = ss_parts, scaled, weight
 
 
 class NormedResidual:
     """``rmsnorm(residual) * weight`` that has not been computed: ``linear`` and ``linear_swiglu``
-    take it in place of their input and, where their kernel can, make the normed activations
-    themselves from the float32 residual and the sums of squares an ``Added`` carried.  Anything
-    else calls ``materialize``."""
+    take it in place of their input and, where their kernel can, multiply ``scaled`` (see ``Added``)
+    with their weight and the result's rows with the norm's factors.  Anything else calls
+    ``materialize``."""
 
-    __slots__ = ("residual", "ss_parts", "weight", "eps", "dtype")
+    __slots__ = ("residual", "ss_parts", "scaled", "weight", "eps", "dtype")
 
-    def __init__(self, residual: torch.Tensor, ss_parts: torch.Tensor, weight: torch.Tensor, eps: float,
-                 dtype: torch.dtype):
-        self.residual, self.ss_parts, self.weight, self.eps, self.dtype = residual, ss_parts, weight, eps, dtype
+    def __init__(self, residual: torch.Tensor, ss_parts: torch.Tensor, scaled: torch.Tensor, weight: torch.Tensor,
+                 eps: float, dtype: torch.dtype):
+        self.residual, self.ss_parts, self.scaled = residual, ss_parts, scaled
+        self.weight, self.eps, self.dtype = weight, eps, dtype
 
     @property
     def shape(self):
@@ -224,19 +239,20 @@ class NormedResidual:
 def _fused_input(x: "NormedResidual", w: torch.Tensor, out: torch.Tensor, epilogue: int,
                  options: KernelOptions) -> bool:
     if not (options.fuse_residual_stream and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and x.weight.dtype == torch.bfloat16 and x.residual.shape[0] <= 16):
+            and x.scaled is not None):
         return False
     from . import gemm_tc
     return gemm_tc.try_linear(None, w, out, epilogue=epilogue, normed=x, options=options)
 
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Tensor] = None,
-           options: KernelOptions = DEFAULT):
+           next_norm: Optional[NormHint] = None, options: KernelOptions = DEFAULT):
     """y[M, N] = x[M, K] @ w[N, K]^T with 32-bit accumulation.
 
     ``x`` may be a ``NormedResidual``.  With ``add_to`` (the float32 residual [M, N]) the kernel may
     add y into it instead of returning it; the result is then an ``Added``, otherwise y as always
-    (the caller adds it later)."""
+    (the caller adds it later).  ``next_norm`` names the RMSNorm that follows the add: the kernel then
+    also leaves that norm's inputs for the next product (see ``Added``)."""
     if isinstance(x, NormedResidual):
         if add_to is None and out_dtype in (torch.float32, x.dtype):
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=w.device)
@@ -252,12 +268,17 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype, add_to: Optional[torch.Te
         raise TypeError(f"linear: output dtype {out_dtype} with input dtype {x.dtype}")
     if x.dtype == torch.bfloat16:
         from . import gemm_tc
-        if (add_to is not None and options.fuse_residual_stream and out_dtype == torch.float32 and (m <= 16 or m > 128)
+        if (add_to is not None and options.fuse_residual_stream and out_dtype == torch.float32
                 and add_to.dtype == torch.float32 and add_to.shape == (m, n) and add_to.is_contiguous()):
-            # few rows: with the sums of squares for the norm that follows; many rows: the sum only
-            ss = torch.empty((m, (n + 127) // 128), dtype=torch.float32, device=x.device) if m <= 16 else None
-            if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss, options=options):
-                return Added(ss)
+            parts = gemm_tc.ss_parts(m, n, k, x.device, options) if next_norm is not None else 0
+            if parts > 0:
+                ss = torch.empty((m, parts), dtype=torch.float32, device=x.device)
+                rb = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+                if gemm_tc.try_linear(x, w, add_to, epilogue=2, ss_out=ss, rb_out=rb, next_w=next_norm.weight,
+                                      options=options):
+                    return Added(ss, rb, next_norm.weight)
+            if gemm_tc.try_linear(x, w, add_to, epilogue=2, options=options):
+                return Added()
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     if x.dtype == torch.bfloat16:
         if gemm_tc.try_linear(x, w, out, options=options):

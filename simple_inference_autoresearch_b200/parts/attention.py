@@ -77,4 +77,5 @@ class GroupedQueryAttention(Mixer):
         attn = ops.rope_and_attention(qkv, rotary, cache_entry, ctx.meta,
                                       self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
                                       write_kv=writes_cache, window=self.window, options=ctx.options)
-        return ops.linear(attn, self.w_o, torch.float32, add_to=ctx.residual, options=ctx.options)
+        return ops.linear(attn, self.w_o, torch.float32, add_to=ctx.residual, next_norm=ctx.next_norm,
+                          options=ctx.options)

@@ -146,6 +146,11 @@ class Norm(Part):
         """residual += delta (in place, 32-bit), then return normed(residual)."""
         raise NotImplementedError
 
+    def hint(self):
+        """What the product in front of this norm may be told of it (``ops.NormHint``) so that it leaves
+        the norm's inputs behind, or None for a norm the product kernels cannot take over."""
+        return None
+
     def deferred(self, ctx, residual: torch.Tensor, added):
         """normed(residual) for a consumer that ``takes_deferred_norm``, after a sublayer whose
         output is already in ``residual`` (``added``: an ``ops.Added``).  A norm whose arithmetic
@@ -199,6 +204,11 @@ class Block(Part):
     the residual the same way, model/block.py:120-183)."""
 
     def cache_need(self):
+        return None
+
+    def first_norm_hint(self):
+        """``hint()`` of the norm this block applies first, when its consumer takes a deferred norm
+        (the model tells the block in front, through ``ctx.norm_after_block``); None otherwise."""
         return None
 
     def forward(self, ctx, residual, pending, cache_entry, writes_cache: bool):

@@ -71,10 +71,17 @@ class PreNormBlock(Block):
             return norm.norm(ctx, residual)
         return norm.add_norm(ctx, residual, pending)
 
+    def first_norm_hint(self):
+        return self.mixer_norm.hint() if self.mixer.takes_deferred_norm else None
+
     def forward(self, ctx, residual, pending, cache_entry, writes_cache: bool = True):
         ctx.residual = residual       # where a sublayer's last product may add its output itself
         h = self._normed(self.mixer_norm, self.mixer, ctx, residual, pending)
+        # the norm that follows each sublayer, for a last product that can leave that norm's inputs behind
+        ctx.next_norm = self.ffn_norm.hint() if self.ffn.takes_deferred_norm else None
         a = self.mixer.forward(ctx, h, cache_entry, writes_cache)
         h = self._normed(self.ffn_norm, self.ffn, ctx, residual, a)
+        ctx.next_norm = getattr(ctx, "norm_after_block", None)
         m = self.ffn.forward(ctx, h)
+        ctx.next_norm = None
         return residual, m

@@ -52,4 +52,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x):
         f = ops.linear_swiglu(x, self.w_gate_up, options=ctx.options)
-        return ops.linear(f, self.w_down, torch.float32, add_to=ctx.residual, options=ctx.options)
+        return ops.linear(f, self.w_down, torch.float32, add_to=ctx.residual, next_norm=ctx.next_norm,
+                          options=ctx.options)

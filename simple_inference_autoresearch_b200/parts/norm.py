@@ -47,5 +47,10 @@ class RMSNorm(Norm):
     def add_norm(self, ctx, residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype)
 
+    def hint(self):
+        return ops.NormHint(self.weight, self.eps)
+
     def deferred(self, ctx, residual: torch.Tensor, added):
-        return ops.NormedResidual(residual, added.ss_parts, self.weight, self.eps, ctx.dtype)
+        if added.scaled is None or added.weight is not self.weight:      # the product knew no norm, or another one
+            return self.norm(ctx, residual)
+        return ops.NormedResidual(residual, added.ss_parts, added.scaled, self.weight, self.eps, ctx.dtype)

@@ -43,7 +43,7 @@ def add_rmsnorm(residual, delta, weight, eps, out_dtype):
     return (residual * torch.rsqrt(var + eps) * weight.to(torch.float32)).to(out_dtype)
 
 
-def linear(x, w, out_dtype, add_to=None, options=None):
+def linear(x, w, out_dtype, add_to=None, next_norm=None, options=None):
     return (x.to(torch.float32) @ w.to(torch.float32).T).to(out_dtype)
 
 

@@ -520,47 +520,73 @@ def test_tensor_core_rows_do_not_depend_on_batch_within_an_orientation():
 
 
 # ----------------------------------------------------------------------------- products inside the residual stream
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 4096, 14336), (8, 256, 128), (16, 384, 512), (5, 200, 72),
-                                   (3, 128, 4096), (16, 2048, 8192)])
-def test_product_adds_into_the_residual_and_leaves_sums_of_squares(m, n, k):
-    """epilogue 2: residual += x @ w^T in float32, and the per-piece sums of squares of the new
-    rows add up to the rows' sums of squares (split along K or not, ragged last piece)."""
+# rows x outputs x inner size: every kernel that can add (16-column tiles with and without a split along K,
+# wider tiles as clusters, clusters in the plain orientation, the persistent kernel and pairs of SMs)
+ADDING_SHAPES = [(1, 4096, 4096), (8, 4096, 14336), (8, 256, 128), (16, 384, 512), (5, 200, 72), (3, 128, 4096),
+                 (16, 2048, 8192), (17, 4096, 4096), (24, 320, 520), (40, 256, 344), (64, 4096, 14336), (70, 256, 1024),
+                 (100, 4096, 4096), (128, 2048, 8192), (129, 256, 256), (300, 520, 136), (2048, 4096, 512),
+                 (1000, 331 * 4, 264), (300, 520, 4096), (256, 4096, 4096), (192, 1000, 14336), (500, 331 * 4, 1024),
+                 (200, 336, 2048), (4100, 512, 256)]
+
+
+@pytest.mark.parametrize("m,n,k", ADDING_SHAPES)
+@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
+def test_product_adds_into_the_residual_and_leaves_the_next_norms_inputs(m, n, k, w_dtype):
+    """epilogue 2 with a hint of the norm that follows: residual += x @ w^T in float32, the parts of
+    every row's sum of squares add up to the row's sum of squares, and the scaled copy is
+    bf16(residual * norm weight); through ``ops.linear`` the same, as an ``Added``."""
     from simple_inference_autoresearch_b200.kernels import gemm_tc
-    x = rnd(m, k, dtype=torch.bfloat16, seed=1)
-    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    norm_w = (1.0 + rnd(n, seed=5, scale=0.1)).to(w_dtype).to(DEV)
     res0 = rnd(m, n, seed=3)
-    want = res0.double() + x.double() @ w.double().T
+    want = res0.double() + x.cpu().double() @ w.cpu().double().T
+    parts = gemm_tc.ss_parts(m, n, k, DEV)
     res = res0.to(DEV)
-    ss = torch.full((m, (n + 127) // 128), float("nan"), dtype=torch.float32, device=DEV)
-    assert gemm_tc.try_linear(x.to(DEV), w.to(DEV), res, epilogue=2, ss_out=ss), "shape refused"
+    out = ops.linear(x, w, torch.float32, add_to=res, next_norm=ops.NormHint(norm_w, 1e-5))
     ops.check_status(DEV)
+    if parts == 0:        # a shape whose kernel cannot add: the product comes back and the caller adds
+        assert isinstance(out, torch.Tensor) or out.ss_parts is None
+        return
+    assert isinstance(out, ops.Added) and out.ss_parts.shape == (m, parts) and out.weight is norm_w
     bound = 1e-5 * k ** 0.5 + 1e-4
-    assert (res.cpu().double() - want).abs().max().item() <= bound
-    got_ss = ss.cpu().double()
-    assert not torch.isnan(got_ss).any()
-    for t in range(got_ss.shape[1]):
-        piece = res.cpu().double()[:, t * 128:(t + 1) * 128].pow(2).sum(1)
-        torch.testing.assert_close(got_ss[:, t], piece, rtol=1e-5, atol=1e-6)
-    # through ops.linear: the mark instead of a tensor, and the same residual
+    got = res.cpu().double()
+    assert (got - want).abs().max().item() <= bound
+    ss = out.ss_parts.cpu().double()
+    assert torch.isfinite(ss).all()
+    torch.testing.assert_close(ss.sum(1), got.pow(2).sum(1), rtol=1e-5, atol=1e-6)
+    scaled = (res.cpu() * norm_w.cpu().float()).to(torch.bfloat16)
+    assert out.scaled.dtype == torch.bfloat16 and out.scaled.shape == (m, n)
+    # the kernel multiplies in float32 and rounds once, as the line above does: equal but for products on a rounding edge
+    assert (out.scaled.cpu().float() - scaled.float()).abs().max().item() <= 2e-2 * scaled.float().abs().max().item() / 4
+    assert (out.scaled.cpu() != scaled).float().mean().item() < 1e-3
+    # the same residual as the product alone followed by the add, and as an add without a hint
     res2 = res0.to(DEV)
-    out = ops.linear(x.to(DEV), w.to(DEV), torch.float32, add_to=res2)
-    assert isinstance(out, ops.Added) and torch.equal(res2, res) and torch.equal(out.ss_parts, ss)
+    plain = ops.linear(x, w, torch.float32, add_to=res2)
+    assert isinstance(plain, ops.Added) and plain.ss_parts is None and plain.scaled is None
+    assert torch.equal(res2, res)
+    if m > 16:            # one kernel, one order of addition: the product alone gives the same numbers
+        assert torch.equal(res, res0.to(DEV) + ops.linear(x, w, torch.float32))
 
 
 @pytest.mark.parametrize("m,n,k,pieces", [(1, 6144, 4096, 32), (8, 28672, 4096, 32), (8, 256, 128, 1), (16, 384, 520, 5),
-                                          (5, 200, 72, 1), (3, 1024, 14336, 112)])
+                                          (5, 200, 72, 1), (3, 1024, 14336, 112), (24, 640, 320, 3), (64, 28672, 4096, 32),
+                                          (100, 6144, 4096, 7), (128, 500, 256, 2), (129, 512, 256, 2), (300, 1040, 320, 6),
+                                          (2048, 6144, 1024, 4), (640, 28672, 512, 16), (4200, 512, 256, 1)])
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_product_makes_its_own_normed_input(m, n, k, pieces, swiglu):
-    """The activation operand made inside the kernel from the float32 residual, the sums of squares
-    given in pieces, against add_rmsnorm followed by the plain product."""
+def test_product_applies_the_norm_in_front_to_its_rows(m, n, k, pieces, swiglu):
+    """A ``NormedResidual`` as the input: the product of bf16(residual * norm weight) with the rows
+    multiplied by rsqrt(mean square + eps) on the accumulators, the sums of squares given in parts,
+    against add_rmsnorm followed by the plain product, at every number of rows."""
     eps = 1e-5
     resid = rnd(m, k, seed=4, scale=2.0).to(DEV)
     norm_w = (1.0 + rnd(k, seed=5, scale=0.1)).to(torch.bfloat16).to(DEV)
     w = rnd(n, k, dtype=torch.bfloat16, seed=6, scale=0.05).to(DEV)
-    # any split of the rows' sums of squares into pieces will do
+    # any split of the rows' sums of squares into parts will do
     cols = [resid[:, (k * i) // pieces:(k * (i + 1)) // pieces].double().pow(2).sum(1) for i in range(pieces)]
     ss = torch.stack(cols, 1).float().contiguous()
-    lazy = ops.NormedResidual(resid, ss, norm_w, eps, torch.bfloat16)
+    scaled = (resid * norm_w.float()).to(torch.bfloat16)
+    lazy = ops.NormedResidual(resid, ss, scaled, norm_w, eps, torch.bfloat16)
     x = ops.add_rmsnorm(resid.clone(), None, norm_w, eps, torch.bfloat16)
     if swiglu:
         got = ops.linear_swiglu(lazy, w)
@@ -569,44 +595,36 @@ def test_product_makes_its_own_normed_input(m, n, k, pieces, swiglu):
         got = ops.linear(lazy, w, torch.float32)
         ref = ops.linear(x, w, torch.float32)
     ops.check_status(DEV)
-    # the normed activations are rounded to bfloat16 in both; the sums of squares differ in their
-    # order of addition only, which may move single activations by one rounding step
-    plain = emu.add_rmsnorm(resid.cpu().clone(), None, norm_w.cpu(), eps, torch.bfloat16)
-    assert (x.cpu().float() - plain.float()).abs().max() <= 2e-2
-    scale = ref.float().abs().max().item()
-    assert (got.float() - ref.float()).abs().max().item() <= 4e-3 * scale + 1e-4, (m, n, k)
+    # both round the activations to bfloat16 once (before or after the row factor); against the exact product
+    exact = (resid.double() * torch.rsqrt(resid.double().pow(2).mean(1, keepdim=True) + eps) * norm_w.double()) @ w.double().T
+    if swiglu:
+        exact = exact[:, 0::2] * torch.sigmoid(exact[:, 0::2]) * exact[:, 1::2]
+    scale = exact.abs().max().item()
+    err_fused = (got.double() - exact).abs().max().item()
+    err_plain = (ref.double() - exact).abs().max().item()
+    assert err_fused <= 2 * err_plain + 4e-3 * scale, (m, n, k, err_fused, err_plain, scale)
+    assert (got.float() - ref.float()).abs().max().item() <= 1.2e-2 * scale + 1e-4, (m, n, k)
+    # without the fused stream the same call computes the norm first
+    off = ops.linear_swiglu(lazy, w, options=OPTS.but(fuse_residual_stream=False)) if swiglu else \
+        ops.linear(lazy, w, torch.float32, options=OPTS.but(fuse_residual_stream=False))
+    assert torch.equal(off, ref)
 
 
-@pytest.mark.parametrize("m,n,k", [(129, 256, 256), (300, 520, 136), (2048, 4096, 512), (1000, 331 * 4, 264),
-                                   (300, 520, 4096), (256, 4096, 4096), (192, 1000, 14336), (500, 331 * 4, 1024),
-                                   (200, 330, 2048)])
-def test_product_of_many_rows_adds_into_the_residual(m, n, k):
-    """residual += x @ w^T (no sums of squares), whole and ragged tiles: the persistent kernel's epilogue,
-    and for few tiles over a long K the cluster of blocks that shares a tile's K."""
-    x = rnd(m, k, dtype=torch.bfloat16, seed=1).to(DEV)
-    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
-    res0 = rnd(m, n, seed=3)
-    res = res0.to(DEV)
-    out = ops.linear(x, w, torch.float32, add_to=res)
-    ops.check_status(DEV)
-    assert isinstance(out, ops.Added) and out.ss_parts is None
-    want = res0.double() + x.cpu().double() @ w.cpu().double().T
-    assert (res.cpu().double() - want).abs().max().item() <= 1e-5 * k ** 0.5 + 1e-4
-    # the same numbers as the product alone followed by the add
-    delta = ops.linear(x, w, torch.float32)
-    assert torch.equal(res, res0.to(DEV) + delta)
-
-
-def test_fused_residual_stream_is_refused_from_17_to_128_rows_and_can_be_switched_off():
-    x = rnd(17, 256, dtype=torch.bfloat16, seed=1).to(DEV)            # 17..128 rows: neither kernel adds
+def test_fused_residual_stream_can_be_switched_off_and_wide_tiles_without_a_split_do_not_add():
+    x = rnd(8, 256, dtype=torch.bfloat16, seed=1).to(DEV)
     w = rnd(128, 256, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
-    res = rnd(17, 128, seed=3).to(DEV)
+    res = rnd(8, 128, seed=3).to(DEV)
     before = res.clone()
-    out = ops.linear(x, w, torch.float32, add_to=res)
-    assert isinstance(out, torch.Tensor) and torch.equal(res, before)       # the caller adds later
-    out8 = ops.linear(x[:8].contiguous(), w, torch.float32, add_to=res[:8].contiguous(),
-                      options=OPTS.but(fuse_residual_stream=False))
-    assert isinstance(out8, torch.Tensor)
+    out8 = ops.linear(x, w, torch.float32, add_to=res, options=OPTS.but(fuse_residual_stream=False))
+    assert isinstance(out8, torch.Tensor) and torch.equal(res, before)       # the caller adds later
+    # 40 rows on 64-column tiles with so many outputs that nothing is split along K: that kernel does not add
+    x = rnd(40, 64, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rnd(148 * 128, 64, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    res = rnd(40, 148 * 128, seed=3).to(DEV)
+    before = res.clone()
+    out = ops.linear(x, w, torch.float32, add_to=res, next_norm=ops.NormHint(torch.ones(148 * 128, device=DEV), 1e-5))
+    assert isinstance(out, torch.Tensor) and torch.equal(res, before)
+    torch.testing.assert_close(out.cpu(), emu.linear(x.cpu(), w.cpu(), torch.float32), rtol=1e-4, atol=1e-4)
 
 
 # ----------------------------------------------------------------------------- tensor-core attention

@@ -121,29 +121,34 @@ def test_float32_path_two_of_32_layers_of_the_8b_shape_in_every_way_of_cutting_t
 def test_captured_decode_steps_across_a_length_bucket_equal_eager_steps():
     """Greedy decoding at the 8B layer shapes from a 2,040-token prompt: the captured step (graphs per
     512-key bucket, products inside the residual stream, attention with the rotary fused) crosses
-    the 2,048-key bucket and draws the same tokens as eager steps."""
+    the 2,048-key bucket and draws the same tokens as eager steps (up to ties within rounding: the eager
+    step cuts the keys by the exact length, the captured one by its bucket)."""
     cfg = two_layers("llama-3.1-8b")
     loaded = siar.init_random(siar.build_model(cfg, torch.bfloat16, "cuda"), seed=3)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (2040, 1500)]
-    outs = []
+    outs, rows = [], [[], []]
+    greedy = siar.SamplingParams(temperature=0.0)
     for graph in (True, False):
         eng = siar.Engine(loaded.model, max_batch=2, max_seq_len=4096, use_cuda_graph=graph)
-        outs.append(eng.generate(prompts, siar.SamplingParams(temperature=0.0), max_new_tokens=24, ignore_eos=True))
+        outs.append(generate_checked(eng, prompts, greedy, 24, [0, 1], rows[len(outs)]))
         if graph:
             assert len(eng._graphs) >= 2          # one per bucket crossed
         del eng
-    assert outs[0] == outs[1]
     assert all(len(o) == 24 for o in outs[0])
+    same_greedy_tokens_up_to_ties(outs[1], outs[0], rows[0], "eager steps against captured steps")
 
 
-def generate_checked(eng, prompts, params, new, ids):
+def generate_checked(eng, prompts, params, new, ids, rows=None):
     """The generation loop's steps made by hand, so that every step's logits can be looked at:
     each drawn token must be what the plain sampler draws from the engine's own logits of that
-    step with the uniform of (seed, request id, token number)."""
+    step with the uniform of (seed, request id, token number).  ``rows`` (a list) receives, per
+    request, the logits rows its tokens were drawn from."""
     reqs = generation.make_requests(prompts, params, new, ids)
     for r in reqs:
         r.slot = eng.open()
+    if rows is not None:
+        rows.extend([] for _ in reqs)
     feed = [list(r.prompt) for r in reqs]
     for n in range(new):
         drawn = eng.run(reqs, feed)
@@ -152,10 +157,27 @@ def generate_checked(eng, prompts, params, new, ids):
             u = plain_llama.counter_uniform(request_seed(params.seed, r.request_id), n)
             plain_check_draw(logits[j], params, u, tok, f"request {r.request_id} token {n}")
             r.output.append(tok)
+            if rows is not None:
+                rows[j].append(logits[j].clone())
         feed = [[t] for t in drawn]
     for r in reqs:
         eng.close(r.slot)
     return [r.output for r in reqs]
+
+
+def same_greedy_tokens_up_to_ties(got, ref, ref_rows, what):
+    """Two greedy runs of the same requests whose logits differ by rounding (other tile widths, other
+    cuts of the keys): equal tokens, or, at the first place where they part, two candidates whose
+    logits in the reference run lie within the bfloat16 tolerance of each other (after that the
+    sequences are different sequences)."""
+    for i, (a, b) in enumerate(zip(got, ref)):
+        if a == b:
+            continue
+        n = next(k for k in range(len(b)) if a[k] != b[k])
+        row = ref_rows[i][n]
+        gap = (row[b[n]] - row[a[n]]).item()
+        assert 0 <= gap <= REL_TOL[torch.bfloat16] * row.abs().max().item(), \
+            f"{what}: request {i} parts at token {n} ({a[n]} vs {b[n]}) with logits {gap:.3e} apart"
 
 
 @pytest.mark.parametrize("preset,batch,lo,hi,new,temperature", [
@@ -177,11 +199,11 @@ def test_unequal_batches_of_long_prompts_at_real_layer_shapes(preset, batch, lo,
     params = siar.SamplingParams(temperature=temperature, top_k=50 if temperature else 0, top_p=0.9 if temperature else 1.0,
                                  seed=11)
     ids = list(range(100, 100 + batch))
-    runs = []
+    runs, rows = [], [[], []]
     for graph in (True, False, True):
         eng = siar.Engine(loaded.model, max_batch=batch, max_seq_len=hi + 64, use_cuda_graph=graph)
         if len(runs) < 2:
-            runs.append(generate_checked(eng, prompts, params, new, ids))
+            runs.append(generate_checked(eng, prompts, params, new, ids, rows[len(runs)] if temperature == 0.0 else None))
         else:
             runs.append(eng.generate(prompts, params, max_new_tokens=new, ignore_eos=True, request_ids=ids))
             alone = generate_checked(eng, prompts[3:4], params, new, ids[3:4])
@@ -189,5 +211,7 @@ def test_unequal_batches_of_long_prompts_at_real_layer_shapes(preset, batch, lo,
     assert all(len(o) == new for o in runs[0])
     assert runs[0] == runs[2]                       # same seed and ids, same tokens (by hand and through generate)
     if temperature == 0.0:
-        assert runs[0] == runs[1]                   # captured steps == eager steps
-        assert alone[0] == runs[0][3]               # a request alone == the same request in the batch
+        # captured steps against eager steps, and a request alone against the same request in the batch:
+        # other cuts of the keys and other tile widths, so equal up to ties within rounding
+        same_greedy_tokens_up_to_ties(runs[1], runs[0], rows[0], "eager steps against captured steps")
+        same_greedy_tokens_up_to_ties(alone, runs[0][3:4], rows[0][3:4], "alone against in the batch")
