@@ -884,7 +884,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
   constexpr uint32_t kXBytes = kBM * kBK * 2;
   constexpr uint32_t kYBytes = BN * kBK * 2;
   constexpr uint32_t kStageBytes = kXBytes + kYBytes;
-  constexpr uint32_t kTmemCols = 2 * BN;               // two accumulators
+  constexpr uint32_t kTmemCols = 2 * BN <= 256 ? 256 : 512;   // two accumulators (an allocation is a power of two)
+  static_assert(BN % 32 == 0 && BN <= 256, "the epilogue stores 32 columns at a time");
 
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -1322,7 +1323,33 @@ struct GemmPlan {
   int ss_parts;       // parts of a row's sum of squares an accumulating launch writes (0: it cannot)
 };
 
-static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_count, int pair_mode, GemmPlan* out) {
+// Tile width of a many-row product on the persistent kernel: tiles are handed out in waves of one per
+// SM, and the last wave is as long as the others however few tiles it holds, so a width that makes
+// the waves come out even can beat the widest one.  A 128 x BN tile loads 128 + BN operand rows per
+// k-block, and that traffic, not the arithmetic, sets its time (measured on B200 at 1,024 to 4,096 rows
+// with the Llama-3.1-8B products: the time of a wave goes as 128 + BN to within a few per cent), so the
+// estimate is waves * (128 + BN); a narrower tile is taken only when that is 3% below the widest
+// one's.  At 2,048 rows the widest tile wins for all four products; at 1,024 rows 224 columns take
+// 8% off the gate/up product (7 waves either way) and 192 columns 9% off the query/key/value product.
+static int many_row_tile_width(int M, int N, int sm_count, int forced) {
+  if (N < 256) return 128;
+  if (forced == 256 || forced == 224 || forced == 192 || forced == 160 || forced == 128) return forced;
+  const long long tiles_p = (M + kBM - 1) / kBM;
+  auto cost = [&](int bn) {
+    const long long tiles = tiles_p * ((N + bn - 1) / bn);
+    return (double)((tiles + sm_count - 1) / sm_count) * (kBM + bn);
+  };
+  int best = 256;
+  double best_cost = cost(256) * 0.97;
+  for (int bn = 224; bn >= 128; bn -= 32) {
+    const double c = cost(bn);
+    if (c < best_cost) { best_cost = c; best = bn; }
+  }
+  return best;
+}
+
+static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_count, int pair_mode, int tile_n,
+                      GemmPlan* out) {
   GemmPlan g;
   g.swap = M <= 128;
   g.P = g.swap ? N : M;
@@ -1371,6 +1398,7 @@ static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_
     }
     if (g.kernel == 3) {
       if (g.BN == 256 && sm_count >= 2 && (pair_mode >= 2 || (pair_mode == 1 && g.P >= kPairRows))) g.kernel = 2;
+      else g.BN = many_row_tile_width(M, N, sm_count, tile_n);
       g.ss_parts = (N + g.BN - 1) / g.BN;
     }
   }
@@ -1393,7 +1421,7 @@ static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_
 static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, int out_f32, int max_splits,
                     int epilogue, int* status, int sm_count, void* stream, const float* ss_in, int ss_in_parts,
                     float eps, float* ss_out, int ss_out_parts, void* rb_out, const void* next_w, int next_w_f32,
-                    int pair_mode) {
+                    int pair_mode, int tile_n) {
   if (M <= 0 || N <= 0) return 0;
   if (epilogue < 0 || epilogue > 2) return -1;
   if (epilogue == 1 && (out_f32 || (N & 1))) return -1;
@@ -1405,7 +1433,7 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
   if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)rb_out) & 15) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   GemmPlan g;
-  if (!make_plan(M, N, K, epilogue, max_splits, sm_count, pair_mode, &g)) return -1;
+  if (!make_plan(M, N, K, epilogue, max_splits, sm_count, pair_mode, tile_n, &g)) return -1;
   if (ss_out != nullptr && (g.ss_parts == 0 || g.ss_parts != ss_out_parts || N % 8 != 0)) return -1;
   const bool swap = g.swap;
   const void* X = swap ? W : A;
@@ -1450,11 +1478,17 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
                      : launch_pair<6, __nv_bfloat16>(tmX, tmY2, prm, sm_count, s);
   }
   if (!swap) {
-    if (BN == 256)
-      return out_f32 ? launch_persistent<256, 4, float>(tmX, tmY, prm, sm_count, s)
-                     : launch_persistent<256, 4, __nv_bfloat16>(tmX, tmY, prm, sm_count, s);
-    return out_f32 ? launch_persistent<128, 6, float>(tmX, tmY, prm, sm_count, s)
-                   : launch_persistent<128, 6, __nv_bfloat16>(tmX, tmY, prm, sm_count, s);
+#define SIAR_PERSISTENT(BN_, ST_)                                                                   \
+  return out_f32 ? launch_persistent<BN_, ST_, float>(tmX, tmY, prm, sm_count, s)                   \
+                 : launch_persistent<BN_, ST_, __nv_bfloat16>(tmX, tmY, prm, sm_count, s)
+    switch (BN) {            // stages: what fits in shared memory
+      case 256: SIAR_PERSISTENT(256, 4);
+      case 224: SIAR_PERSISTENT(224, 5);
+      case 192: SIAR_PERSISTENT(192, 5);
+      case 160: SIAR_PERSISTENT(160, 6);
+      default: SIAR_PERSISTENT(128, 6);
+    }
+#undef SIAR_PERSISTENT
   }
 #define SIAR_GO(BN_, ST_)                                                                      \
   return out_f32 ? launch<BN_, ST_, float>(tmX, tmY, prm, splits, s)                           \
@@ -1471,18 +1505,18 @@ static int run_gemm(const void* A, const void* W, void* C, int M, int N, int K, 
 
 extern "C" int siar_gemm_tc_bf16(const void* A, const void* W, void* C, int M, int N, int K, int out_f32,
                                  int max_splits, int epilogue, int* status, int sm_count, void* stream,
-                                 int pair_mode) {
+                                 int pair_mode, int tile_n) {
   if (epilogue == 2) return -1;
   return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, nullptr, 0, 0.f, nullptr,
-                  0, nullptr, nullptr, 0, pair_mode);
+                  0, nullptr, nullptr, 0, pair_mode, tile_n);
 }
 
 // Parts of a row's sum of squares that siar_gemm_tc_bf16_fused writes to ss_out for an accumulating
 // product (epilogue 2) of these sizes; 0 when such a launch cannot leave them.
-extern "C" int siar_gemm_tc_ss_parts(int M, int N, int K, int max_splits, int sm_count, int pair_mode) {
+extern "C" int siar_gemm_tc_ss_parts(int M, int N, int K, int max_splits, int sm_count, int pair_mode, int tile_n) {
   GemmPlan g;
   if (M <= 0 || N <= 0 || K % 8 != 0 || K < 8 || N % 8 != 0) return 0;
-  if (!make_plan(M, N, K, 2, max_splits, sm_count, pair_mode, &g)) return 0;
+  if (!make_plan(M, N, K, 2, max_splits, sm_count, pair_mode, tile_n, &g)) return 0;
   return g.ss_parts;
 }
 
@@ -1491,7 +1525,7 @@ extern "C" int siar_gemm_tc_bf16_fused(const void* A, const void* W, void* C, in
                                        int max_splits, int epilogue, int* status, int sm_count, void* stream,
                                        const float* ss_in, int ss_in_parts, float eps, float* ss_out,
                                        int ss_out_parts, void* rb_out, const void* next_w, int next_w_f32,
-                                       int pair_mode) {
+                                       int pair_mode, int tile_n) {
   return run_gemm(A, W, C, M, N, K, out_f32, max_splits, epilogue, status, sm_count, stream, ss_in, ss_in_parts, eps,
-                  ss_out, ss_out_parts, rb_out, next_w, next_w_f32, pair_mode);
+                  ss_out, ss_out_parts, rb_out, next_w, next_w_f32, pair_mode, tile_n);
 }

@@ -27,7 +27,7 @@ def _bind():
         f = lib.siar_gemm_tc_bf16
         c = ctypes
         f.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
-                      c.c_void_p, c.c_int, c.c_void_p, c.c_int]
+                      c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_int]
         f.restype = c.c_int
         _fn = f
     return _fn
@@ -42,7 +42,7 @@ def _bind_fused():
                       c.c_void_p, c.c_int, c.c_void_p,
                       c.c_void_p, c.c_int, c.c_float,                         # ss_in, its parts, eps
                       c.c_void_p, c.c_int, c.c_void_p, c.c_void_p, c.c_int,   # ss_out, its parts, rb_out, next_w, next_w_f32
-                      c.c_int]
+                      c.c_int, c.c_int]
         f.restype = c.c_int
         _fn_fused = f
     return _fn_fused
@@ -54,9 +54,10 @@ def ss_parts(m: int, n: int, k: int, device, options: KernelOptions = DEFAULT) -
     if not options.use_tc_gemm:
         return 0
     f = build.load_unit("gemm_tc").siar_gemm_tc_ss_parts
-    f.argtypes = [ctypes.c_int] * 6
+    f.argtypes = [ctypes.c_int] * 7
     f.restype = ctypes.c_int
-    return int(f(m, n, k, options.max_splits, _device_state(torch.device(device))["sms"], options.pair_mode))
+    return int(f(m, n, k, options.max_splits, _device_state(torch.device(device))["sms"], options.pair_mode,
+                 options.tile_n))
 
 
 def _device_state(device: torch.device):
@@ -107,11 +108,11 @@ def try_linear(x, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, normed=
                         int(next_w.dtype == torch.float32))
         err = _bind_fused()(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
                             options.max_splits, int(epilogue), status, st["sms"], stream, *consumer, *producer,
-                            options.pair_mode)
+                            options.pair_mode, options.tile_n)
     else:
         m, k = x.shape
         err = _bind()(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, int(out.dtype == torch.float32),
-                      options.max_splits, int(epilogue), status, st["sms"], stream, options.pair_mode)
+                      options.max_splits, int(epilogue), status, st["sms"], stream, options.pair_mode, options.tile_n)
     if err == -1:
         return False
     if err != 0:

@@ -34,8 +34,13 @@ class KernelOptions:
     max_splits: int = 8
     #: products of many rows on pairs of SMs (cta_group::2): 0 never, 1 from 4,096 rows on, 2 always
     pair_mode: int = 1
+    #: output columns per tile of products of many rows (the persistent kernel): 0 = the width whose
+    #: waves of tiles come out most even, or one of 128, 160, 192, 224, 256
+    tile_n: int = 0
 
     def __post_init__(self):
+        if self.tile_n not in (0, 128, 160, 192, 224, 256):
+            raise ValueError(f"tile_n must be 0 or one of 128, 160, 192, 224, 256, got {self.tile_n}")
         if not 1 <= self.max_splits <= 8:
             raise ValueError(f"max_splits must be 1..8, got {self.max_splits}")
         if self.pair_mode not in (0, 1, 2):

@@ -500,6 +500,32 @@ def test_two_sms_on_one_tile_give_the_one_sm_kernels_numbers(m, n, k):
         assert torch.equal(u, v)
 
 
+@pytest.mark.parametrize("tile_n", [128, 160, 192, 224])
+@pytest.mark.parametrize("m,n,k", [(300, 1000, 264), (2048, 6144, 512), (1024, 28672 // 4, 256), (640, 736, 1024)])
+def test_every_tile_width_of_the_many_row_kernel_gives_the_same_numbers(m, n, k, tile_n):
+    """The persistent kernel with narrower tiles (chosen when they make the waves of tiles come out more
+    even): the same k order per output, so the same numbers as the 256-column tile; plain, SwiGLU and adding
+    epilogues with the next norm's inputs, whole and ragged tiles."""
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1).to(DEV)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05).to(DEV)
+    norm_w = (1.0 + rnd(n, seed=5, scale=0.1)).to(torch.bfloat16).to(DEV)
+    outs = []
+    for tn in (tile_n, 256):
+        o = OPTS.but(tile_n=tn, pair_mode=0, max_splits=1)        # max_splits 1: no clusters for few tiles either
+        a = ops.linear(x, w, torch.float32, options=o)
+        b = ops.linear_swiglu(x, w, options=o)
+        res = torch.ones(m, n, device=DEV)
+        added = ops.linear(x, w, torch.float32, add_to=res, next_norm=ops.NormHint(norm_w, 1e-5), options=o)
+        assert isinstance(added, ops.Added) and added.ss_parts.shape[1] == -(-n // tn)
+        ops.check_status(DEV)
+        outs.append((a.cpu(), b.float().cpu(), res.cpu(), added.scaled.float().cpu(), added.ss_parts.sum(1).cpu()))
+    ref = x.cpu().double() @ w.cpu().double().T
+    assert (outs[0][0].double() - ref).abs().max().item() <= 1e-5 * k ** 0.5 + 1e-4
+    for u, v in list(zip(*outs))[:4]:
+        assert torch.equal(u, v)
+    torch.testing.assert_close(outs[0][4], outs[1][4], rtol=1e-5, atol=1e-5)      # the parts differ, their sums agree
+
+
 def test_tensor_core_linear_refuses_unaligned_k():
     from simple_inference_autoresearch_b200.kernels import gemm_tc
     x, w = rnd(4, 20, dtype=torch.bfloat16).to(DEV), rnd(8, 20, dtype=torch.bfloat16).to(DEV)
