@@ -877,6 +877,14 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
 // tile i + 1, and the TMA thread runs ahead through the shared-memory ring.  The epilogue
 // stores straight from registers: each thread owns one tile row and writes 32 consecutive
 // outputs at a time with 16-byte stores.
+// Tried and not kept: sharing out the k-blocks of the last, partial wave of tiles among all SMs
+// ("stream-K": partial tiles through a float32 workspace, flags, the finishing block adding them in the
+// order of their k-blocks).  At 2,048 rows of the Llama-3.1-8B products, where the last wave holds 88
+// or 108 tiles for 148 SMs, it was slower, not faster: the query/key/value product 121 us against 95,
+// the output product 112 against 80, the down product 226 against 208.  The blocks of a wave read the
+// same operand tiles at about the same time (16 blocks share a weight tile, 9 or 10 an activation
+// tile); with every block at another place in K that is lost, and the kernel is bound by what L2
+// delivers (a wave's time goes as 128 + BN, the operand rows a tile loads per k-block).
 template <int BN, int STAGES, typename TOut>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
