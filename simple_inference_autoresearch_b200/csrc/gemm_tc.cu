@@ -129,6 +129,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   __shared__ int abort_flag;
   __shared__ float ss_red[4][kSsSlots];
   __shared__ float inv_s[BN < 128 ? BN : 128];     // row factors of the norm in front, by tile column (few rows)
+  // 16-column tiles split along K: the partials of this block's outputs arrive here from the cluster's
+  // blocks (float recv16[sender][owned output][128 tile rows]) and are counted on recv_bar
+  __shared__ __align__(16) float recv16[BN == 16 ? 24 * kBM : 4];
+  __shared__ __align__(8) uint64_t recv_bar;
 
   const uint32_t dyn = smem_u32(smem_dyn);
   unsigned char* tiles = smem_dyn + ((1024u - (dyn & 1023u)) & 1023u);   // 1024-byte aligned for the swizzle
@@ -150,6 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full_bar, 1);
+    mbar_init(&recv_bar, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -157,6 +162,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // 16-column tiles in a cluster: every block's barrier exists before anyone sends to it (the wait that
+  // belongs to this arrival comes just before the hand-over, long after)
+  if (BN == 16 && splits > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
   // A block that starts after another one has reported an expired wait does no work:
   // a broken launch then ends after one wave instead of one second per block.
@@ -345,17 +353,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   // ---------------- write-out
   if (splits > 1) {
     // split-K: the blocks of a cluster hold partial tiles of the same outputs.  Output jq of
-    // the tile belongs to the block of rank jq % splits.  Barrier 1: every block's main loop is
-    // done, so its pipeline memory is free.  Then each block sends its partials to their owners
-    // (remote shared-memory stores into slot [sender rank]).  Barrier 2: all partials have
-    // arrived; each owner adds them in rank order, so the sum has one order, and stores.
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (threadIdx.x == 64) { SIAR_STAMP(5); }
+    // the tile belongs to the block of rank jq % splits.  Each block sends its partials to their owners
+    // (remote shared-memory stores into slot [sender rank]); each owner adds them in rank order, so the
+    // sum has one order, and stores.
+    // Wide tiles receive in the pipeline's memory: barrier 1, every block's main loop is done and its
+    // memory free; the stores; barrier 2, all partials have arrived.
+    // 16-column tiles (the decode step's products) receive in a buffer of their own and count the
+    // arriving bytes on an mbarrier (st.async), so no block waits for the slowest block's main loop
+    // before it sends, nor for all hand-overs before it adds: the only cluster barrier left is the
+    // one that keeps a block alive until nobody can send to it any more, and its wait comes last.
     const int rank = (int)blockIdx.z;
     const int NL = (BN + splits - 1) / splits;          // outputs per owner
     const int et = threadIdx.x - 64;                    // epilogue thread = tile row p
-    const uint32_t recv = smem_u32(tiles);              // float recv[splits][NL][128]
+    constexpr bool kAsync = BN == 16;
+    if (kAsync) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");     // of the arrival at the start
+      if (threadIdx.x == 64) {
+        const int owned = (BN - rank + splits - 1) / splits;                     // outputs jq = rank, rank + splits, ...
+        mbar_expect_tx(&recv_bar, (uint32_t)(owned * splits * kBM * 4));
+      }
+    } else {
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    if (threadIdx.x == 64) { SIAR_STAMP(5); }
+    const uint32_t recv = kAsync ? smem_u32(recv16) : smem_u32(tiles);          // float recv[splits][NL][128]
     // Tiles of 32 and more columns hand over groups of four columns: group gq belongs to rank
     // gq % splits, and a thread sends a group as one 16-byte remote store
     // (float4 recv[sender][group slot][128 tile rows]).
@@ -419,18 +441,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             const uint32_t local = recv + (uint32_t)(((rank * NL + push_jl) * 128 + tr) * 4);
             uint32_t remote;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(push_owner));
-            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(r[j]) : "memory");
+            if (kAsync) {
+              uint32_t remote_bar;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(&recv_bar)), "r"(push_owner));
+              asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
+                           ::"r"(remote), "r"(r[j]), "r"(remote_bar) : "memory");
+            } else {
+              asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(r[j]) : "memory");
+            }
             if (++push_owner == splits) { push_owner = 0; ++push_jl; }
           }
         }
       }
     }
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (kAsync) {
+      // this block's outputs are complete when all their bytes have been counted
+      if (warp >= 2 && !dead && !mbar_wait(&recv_bar, 0)) {
+        abort_flag = 1;
+        atomicOr(prm.status, kStatusWaitExpired);
+      }
+    } else {
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     if (warp >= 2 && !dead) {
       const int pp = p0 + et;
       const int ew = et >> 5;
-      const float* mine = reinterpret_cast<const float*>(tiles);
+      const float* mine = kAsync ? recv16 : reinterpret_cast<const float*>(tiles);
       bool stored = false;
       if constexpr (BN == 16 && sizeof(TOut) == 4) {
         if (prm.accumulate) {
@@ -745,6 +782,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
     }
   }
+  // a block of 16-column tiles in a cluster stays until every block has sent what it had to send
+  if (BN == 16 && splits > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   SIAR_TRACE(10, 1);
