@@ -93,7 +93,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "sm_mhz_min": min(sm) if sm else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def main() -> int:
@@ -152,14 +152,32 @@ def main() -> int:
     except FileNotFoundError as e:
         print(f"bench.py: {e}")
         return 2
-    cfg = dataclasses.replace(full, num_hidden_layers=args.layers) if args.layers else full
+    if args.layers:
+        if not (dataclasses.is_dataclass(full) and hasattr(full, "num_hidden_layers")):
+            print("bench.py: --layers needs a configuration with num_hidden_layers")
+            return 2
+        cfg = dataclasses.replace(full, num_hidden_layers=args.layers)
+    else:
+        cfg = full
     pk, pk_src = peaks()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
 
     loaded = siar.init_random(siar.build_model(cfg, torch.bfloat16, dev), seed=0)
     model = loaded.model
-    kv_token_bytes = 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * (cfg.head_dim or cfg.hidden_size // cfg.num_attention_heads) * 2
+    # Sizes the arithmetic below needs, taken from the model itself (its tensors, its cache needs and its
+    # mixers), so that another registered architecture's configuration runs through the same lines.
+    from simple_inference_autoresearch_b200.parts.base import KVNeed
+    spec = model.spec
+    h, v, L = spec.hidden_size, spec.vocab_size, len(model.schedule)
+    kv_token_bytes = sum(n.n_kv_heads * (n.head_dim + (n.v_head_dim or n.head_dim)) * 2       # bfloat16 keys and values
+                         for n in model.cache_needs if isinstance(n, KVNeed))
+    matrix_params = sum(t.shape[0] * t.shape[1] for t in model.tensor_specs() if t.role == "matrix" and len(t.shape) == 2)
+    table_params = v * h * (1 if spec.head_name is None else 2)          # embedding table (and the head when untied)
+    layer_matrix_params = (matrix_params - table_params) * L // max(len(model.layers), 1)     # per run of the schedule
+    attn_flops_per_token_pair = sum(4 * getattr(model.layers[e.layer].mixer, "n_heads", 0) *
+                                    getattr(model.layers[e.layer].mixer, "head_dim", 0)
+                                    for e in model.schedule if hasattr(model.layers[e.layer], "mixer"))
     if not args.no_points and 64 * CONTEXT * kv_token_bytes > 100e9:
         print(f"bench.py: the batch 1 / 64 points are left out: 64 sequences of {CONTEXT:,} tokens would hold "
               f"{64 * CONTEXT * kv_token_bytes / 1e9:.0f} GB of keys and values", file=sys.stderr)
@@ -167,7 +185,7 @@ def main() -> int:
     max_b = max(args.batch, 1 if args.no_points else 64)
     engine = siar.Engine(model, max_batch=max_b, max_seq_len=CONTEXT, use_cuda_graph=True)
     gen = torch.Generator().manual_seed(0)
-    rand_tokens = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()  # noqa: E731
+    rand_tokens = lambda n: torch.randint(0, v, (n,), generator=gen).tolist()  # noqa: E731
 
     # ---------------------------------------------------------------- prefill, one prompt
     def prefill_once():
@@ -189,18 +207,16 @@ def main() -> int:
     prefill_ms = statistics.median(prefill_once() for _ in range(3))
     if args.cuda_profiler_range == "prefill":
         torch.cuda.profiler.stop()
-    h, i, v, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
-    qkv_n = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
-    lin_params = L * (qkv_n * h + h * cfg.num_attention_heads * cfg.head_dim + 3 * h * i)
     T = PROMPT_TOKENS
-    prefill_flops = 2 * T * lin_params + L * 4 * cfg.num_attention_heads * cfg.head_dim * T * T / 2 + 2 * v * h
+    # the layers' products on every token, causal attention (half of T x T), the head on the one wanted row
+    prefill_flops = 2 * T * layer_matrix_params + attn_flops_per_token_pair * T * T / 2 + 2 * v * h
     prefill = {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---------------------------------------------------------------- decode at a batch size
-    kv_token_bytes = L * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
     embed_bytes = v * h * 2
-    weight_bytes = model.weight_bytes() - embed_bytes * (0 if cfg.tie_word_embeddings else 1)
+    # every weight a step uses, once: the embedding table is only read as the head, when the two are tied
+    weight_bytes = model.weight_bytes() - embed_bytes * (0 if spec.head_name is None else 1)
 
     def decode_at(batch, steps, warmup, e2e):
         slots_reqs = []
@@ -260,13 +276,19 @@ def main() -> int:
     head = decode_at(args.batch, args.steps, args.warmup, e2e=True)
 
     # ---------------------------------------------------------------- end to end through Engine.generate
-    # The public call: host token lists in, host token lists out.  Two runs on the same prompts,
-    # one that stops after the first new token and one that decodes `steps` more; the difference
-    # is `steps` decode steps, each with its pinned host->device token copy and device->host read.
+    # The public call: host token lists in, host token lists out.  Every decode step inside it copies
+    # its input tokens from pinned host memory, runs, reads the drawn tokens back and synchronises;
+    # the call's own statistics time each of those steps with the host clock (the reference's
+    # generate_with_stats reports decode tok/s the same way, generate.py:193-237).  The value is the
+    # median of three calls that decode `steps` tokens after the first.  As a cross-check, the
+    # difference between such a call and one that stops after the first token (`by_difference`:
+    # it also carries what the two prefills differ by, a few milliseconds at the power cap).
     prompts = [rand_tokens(PROMPT_TOKENS) for _ in range(args.batch)]
     greedy = siar.SamplingParams(temperature=0.0)
     engine.generate(prompts, greedy, max_new_tokens=1 + args.warmup, ignore_eos=True)      # warm-up
-    diffs = []
+    diffs, in_call = [], []
+    e2e_clock = ClockSampler()               # the clocks the decode steps of these calls run at (read-only sampling)
+    e2e_clock.start()
     for _ in range(3):                       # the median of three pairs: one pair alone moves by a few per cent
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -279,11 +301,33 @@ def main() -> int:
         t2 = time.perf_counter()
         assert all(len(o) == 1 + args.steps for o in outs)
         diffs.append((t2 - t1) - (t1 - t0))
-    generate_tok_s = args.batch * args.steps / max(sorted(diffs)[1], 1e-9)
+        in_call.append(gen_stats["decode_tok_s"])
+    e2e_clock.stop()
+    e2e_clocks = e2e_clock.summary()
+    generate_tok_s = sorted(in_call)[1]
+    by_difference = args.batch * args.steps / max(sorted(diffs)[1], 1e-9)
     points = {}
     if not args.no_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(decode_at(b, max(8, args.steps // 2), args.warmup, e2e=False)["tok_s"], 1)
+
+    def config_record():
+        """Every size of the run, flat and at most 20 keys: the run's own numbers, then the configuration's
+        keys as config.json names them (a nested block such as rope_scaling becomes one string)."""
+        rec = {"model": f"{args.model} shape", "global_batch": args.batch, "seq_len": CONTEXT,
+               "prompt_tokens": PROMPT_TOKENS, "parallelism": "single GPU", "layers": L,
+               "layers_of_full_model": getattr(full, "num_hidden_layers", L)}
+        skip = {"architectures", "model_type", "bos_token_id", "eos_token_id", "torch_dtype", "hidden_act", "attention_bias",
+                "mlp_bias", "num_hidden_layers", "initializer_range", "max_position_embeddings", "norm_weight_init"}
+        for key, val in cfg.to_dict().items():
+            if key in skip or isinstance(val, (list, tuple)) or len(rec) >= 18:
+                continue
+            if isinstance(val, dict):
+                val = " ".join(f"{k}={x}" for k, x in val.items())
+            rec[key] = val
+        rec["l2"] = "inputs larger than L2 (weights + cache read every step)"
+        rec["peaks"] = pk_src
+        return rec
 
     achieved = head["bytes"] / (head["ms"] * 1e-3) / 1e9
     line = {
@@ -293,19 +337,13 @@ def main() -> int:
         "warmup": args.warmup, "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
         "impl": "ours",
-        "config": {
-            "model": f"{args.model} shape", "global_batch": args.batch, "seq_len": CONTEXT,
-            "prompt_tokens": PROMPT_TOKENS, "parallelism": "single GPU", "layers": L,
-            "layers_of_full_model": full.num_hidden_layers, "hidden_size": h, "intermediate_size": i,
-            "vocab_size": v, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-            "head_dim": cfg.head_dim, "rope_theta": cfg.rope_theta, "rope_scaling": "llama3 factor 8",
-            "rms_norm_eps": cfg.rms_norm_eps, "tied_embeddings": cfg.tie_word_embeddings,
-            "l2": "inputs larger than L2 (weights + cache read every step)", "peaks": pk_src,
-        },
+        "config": config_record(),
         "e2e": {"value": round(generate_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * args.batch,
-                "d2h_bytes_per_step": 4 * args.batch + 4, "via": "Engine.generate (difference of two runs, median of 3 pairs)",
+                "d2h_bytes_per_step": 4 * args.batch + 4, "via": "Engine.generate: its decode steps timed by the call's own statistics (host clock around every step), median of 3 calls",
+                "by_difference": round(by_difference, 1),
                 "step_ms_first16": gen_stats["tpot_ms_first16"], "step_ms_last16": gen_stats["tpot_ms_last16"],
                 "note": "the steps right after the prompts run at the clocks the prefill left (power cap)",
+                "sm_mhz": e2e_clocks["sm_mhz"], "sm_mhz_min": e2e_clocks.get("sm_mhz_min"),       # over the calls: prompts and decode steps
                 "step_call": round(head["e2e_tok_s"], 1)},
         "gpu_launches": head["launches"],
         "prefill": prefill,
