@@ -105,3 +105,20 @@ def test_plain_sampler_options():
     assert plain_llama.sample(logits, 1.0, 0, 1.0, 0.0) == 0
     assert 0 <= plain_llama.counter_uniform(123, 0) < 1
     assert plain_llama.counter_uniform(123, 0) != plain_llama.counter_uniform(123, 1)
+
+
+def test_plain_sampler_keeps_what_the_reference_sampler_keeps():
+    """The probabilities the reference's own ``sample`` draws from (recorded on the CPU by
+    tests/golden/make_sampler_golden.py: temperature, top-k taken before the temperature, nucleus
+    with the crossing token kept, every combination) against ``kept_probabilities``, on rows without
+    equal logits (where logits tie the plain sampler keeps the tied tokens together; the reference
+    leaves it to its sort)."""
+    with safe_open(str(GOLDEN / "sampler.safetensors"), framework="pt") as f:
+        cases = json.loads(f.metadata()["cases"])
+        t = {k: f.get_tensor(k) for k in f.keys()}
+    for ci, (temperature, top_k, top_p) in enumerate(cases):
+        for ri in range(t["logits"].shape[0]):
+            mine = plain_llama.kept_probabilities(t["logits"][ri], temperature, top_k, top_p).float()
+            ref = t[f"probs{ci}"][ri]
+            assert torch.equal(mine > 0, ref > 0), (temperature, top_k, top_p, ri)
+            torch.testing.assert_close(mine, ref, rtol=1e-5, atol=1e-7)
