@@ -6,17 +6,20 @@ Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with a
 2,048-token prompt in a cache sized for 4,096 tokens per sequence, timed on the
 device with CUDA events around K replays of the captured decode step; ``e2e`` is
 the same through ``Engine.generate`` (host token lists in and out; each step copies
-its input tokens from pinned host memory and reads the sampled tokens back), taken
-as the difference of a run that decodes K more tokens and one that stops after the
-first; ``e2e.step_call`` times the per-step call underneath it (``Engine.run``).  ``prefill`` is one
+its input tokens from pinned host memory and reads the sampled tokens back), from
+the call's own per-step timings of a run that decodes K tokens after the first
+(``e2e.by_difference``: against a run that stops after the first; ``e2e.sm_mhz``: the
+clocks sampled during those calls; ``e2e.step_call``: the per-step call underneath,
+``Engine.run``, once the clocks are back up).  ``prefill`` is one
 2,048-token prompt; ``points`` hold decode at batch 1 and 64; ``roofline`` compares
 the decode step with the bytes it has to read (each weight it uses once, plus the
 keys and values of the live sequences).  Weights are seeded random values of the
 real shape (there is no checkpoint offline); inputs exceed L2, so nothing stays
 cached between steps.
 
-Other workloads than the default run's: ``--model llama-3.2-1b|llama-3.2-3b`` takes
-another preset's layer sizes, ``--prompt-tokens N`` (with ``--context C``) other prompt
+Other workloads than the default run's: ``--model NAME`` takes another shipped or
+registered configuration's layer sizes (``llama-3.2-1b``, ``llama-3.2-3b``; whatever
+architecture its config.json names), ``--prompt-tokens N`` (with ``--context C``) other prompt
 and cache lengths, ``--batch B`` another batch; the line then names them in ``metric``
 and ``config``.
 """

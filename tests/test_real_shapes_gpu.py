@@ -215,3 +215,39 @@ def test_unequal_batches_of_long_prompts_at_real_layer_shapes(preset, batch, lo,
         # other cuts of the keys and other tile widths, so equal up to ties within rounding
         same_greedy_tokens_up_to_ties(runs[1], runs[0], rows[0], "eager steps against captured steps")
         same_greedy_tokens_up_to_ties(alone, runs[0][3:4], rows[0][3:4], "alone against in the batch")
+
+
+def test_bfloat16_path_against_the_32_bit_path_at_the_full_depth_of_the_8b_shape():
+    """All 32 layers of the Llama-3.1-8B shape with random weights: the bfloat16 path against the
+    library's own true 32-bit path on the same (bfloat16-representable) weights; two prompts of
+    unequal lengths in one step, then two single tokens each.  (The 32-bit path is tied to the plain
+    implementation at this shape by the two-layer test above and at every depth by the tiny
+    configurations; 32 layers of the plain implementation on the CPU would take minutes.)  Rounding of
+    the activations at every product and of P in attention adds up over the depth: the stated bound
+    is 8e-2 of the largest |logit|; the distance measured is printed."""
+    cfg = LlamaConfig.from_json(preset_path("llama-3.1-8b"))
+    g = torch.Generator().manual_seed(4)
+    reqs = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (70, 33)]
+    outs = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        built = siar.build_model(cfg, dtype, "cuda")
+        specs = built.model.tensor_specs()
+        tensors = {}
+        for ts in specs:                                       # one tensor at a time: the 32-bit copy is 32 GB
+            t = random_tensors([ts], 2, torch.bfloat16, "cuda")[ts.name]
+            tensors[ts.name] = t if dtype == torch.bfloat16 else t.to(dtype)
+        built.model.load(tensors)
+        del tensors
+        eng = siar.Engine(built.model, max_batch=2, max_seq_len=128, use_cuda_graph=False)
+        slots = [eng.open() for _ in reqs]
+        o = [eng.step([StepEntry(s, r[:-2], [0, len(r) - 3]) for s, r in zip(slots, reqs)])]
+        for k in range(2):
+            o.append(eng.step([StepEntry(s, [r[len(r) - 2 + k]], [0]) for s, r in zip(slots, reqs)]))
+        outs[dtype] = torch.cat(o).float().cpu()
+        del eng, built
+        torch.cuda.empty_cache()
+    ref, got = outs[torch.float32], outs[torch.bfloat16]
+    assert torch.isfinite(got).all() and torch.isfinite(ref).all()
+    rel = (got - ref).abs().max().item() / ref.abs().max().item()
+    print(f"full depth: max |bf16 - fp32| / max |logit| = {rel:.3e}")
+    assert rel <= 8e-2, rel
