@@ -887,9 +887,36 @@ __device__ __forceinline__ float norm_row_factor(const GemmParams& prm, int p) {
 // multiplied by row_scale, the factor of the norm in front of this product for row p.  An
 // accumulating product with rb_out also writes bf16(new C * next_w) to rbrow and returns the sum
 // of squares of the new C values it stored (0 otherwise).
+// What an accumulating chunk adds to and multiplies by, asked for one chunk ahead: the 32 old values of
+// C and (for rb_out with bfloat16 norm weights) the 32 weights of the next norm.
+struct ChunkAhead {
+  float4 old[8];
+  uint4 w[4];
+  bool have;      // the values above are those of this chunk
+};
+template <typename TOut>
+__device__ __forceinline__ void fetch_ahead(ChunkAhead& a, const TOut* crow, const __nv_bfloat16* rbrow, int p, int q,
+                                            const GemmParams& prm, bool vec_ok) {
+  a.have = false;
+  if constexpr (sizeof(TOut) == 4) {
+    if (prm.accumulate && !prm.swiglu && vec_ok && p < prm.P && q + 32 <= prm.Q) {
+      a.have = true;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a.old[j] = ld_f32x4_here(reinterpret_cast<const float*>(crow) + q + 4 * j);
+      if (rbrow != nullptr && !prm.next_w_f32) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 v = ld_f32x4_here(reinterpret_cast<const float*>(reinterpret_cast<const __nv_bfloat16*>(prm.next_w) + q + 8 * j));
+          a.w[j] = make_uint4(__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w));
+        }
+      }
+    }
+  }
+}
 template <typename TOut>
 __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv_bfloat16* rbrow, int p, int q,
-                                             const GemmParams& prm, bool vec_ok, float row_scale) {
+                                             const GemmParams& prm, bool vec_ok, float row_scale,
+                                             const ChunkAhead* ahead = nullptr) {
   float ss = 0.f;
   if (prm.ss_in != nullptr) {
 #pragma unroll
@@ -925,8 +952,9 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
       if constexpr (sizeof(TOut) == 4) {
         if (prm.accumulate) {          // C += D: the product adds itself into the residual stream
           float4 old[8];
+          const bool got = ahead != nullptr && ahead->have;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(crow + q + 4 * j);
+          for (int j = 0; j < 8; ++j) old[j] = got ? ahead->old[j] : *reinterpret_cast<const float4*>(crow + q + 4 * j);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float4 v = make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
@@ -940,7 +968,16 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float w[8];
-              load_norm_w8(prm.next_w, prm.next_w_f32, q + j, w);
+              if (got && !prm.next_w_f32) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&ahead->w[j >> 3]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __bfloat1622float2(h[e]);
+                  w[2 * e] = f.x; w[2 * e + 1] = f.y;
+                }
+              } else {
+                load_norm_w8(prm.next_w, prm.next_w_f32, q + j, w);
+              }
               uint4 pk;
               pk.x = pack_bf16x2(__uint_as_float(r[j]) * w[0], __uint_as_float(r[j + 1]) * w[1]);
               pk.y = pack_bf16x2(__uint_as_float(r[j + 2]) * w[2], __uint_as_float(r[j + 3]) * w[3]);
@@ -1117,22 +1154,28 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       const int p0 = (t % tiles_p) * kBM, q0 = (t / tiles_p) * BN;
       const int p = p0 + quad * 32 + lane;
       const float row_scale = norm_row_factor(prm, p);     // read while the tile's main loop still runs
+      TOut* crow = C + (long long)p * prm.ldc;
+      __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)p * prm.ldc : nullptr;
+      ChunkAhead ahead;
+      fetch_ahead<TOut>(ahead, crow, rbrow, p, q0, prm, vec_ok);      // nobody else writes this row's outputs
       if (!mbar_wait(&tfull_bar[acc], (i >> 1) & 1) || *(volatile int*)&abort_flag) {
         abort_flag = 1;
         atomicOr(prm.status, kStatusWaitExpired);
         break;
       }
       tc_fence_after();
-      TOut* crow = C + (long long)p * prm.ldc;
-      __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)p * prm.ldc : nullptr;
       float ss = 0.f;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
+        // what this chunk adds to was asked for a chunk ago (the first chunk's before the tile was
+        // complete); the next chunk's is asked for now, so that its trip to L2 runs under this chunk
+        const ChunkAhead cur = ahead;
+        fetch_ahead<TOut>(ahead, crow, rbrow, p, q0 + (ch + 1) * 32, prm, vec_ok && ch + 1 < BN / 32);
         uint32_t r[32];
         SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int q = q0 + ch * 32;
-        ss += store_chunk<TOut>(r, crow, rbrow, p, q, prm, vec_ok, row_scale);
+        ss += store_chunk<TOut>(r, crow, rbrow, p, q, prm, vec_ok, row_scale, &cur);
       }
       if (prm.ss_out != nullptr && p < prm.P) prm.ss_out[(size_t)p * prm.ss_parts + t / tiles_p] = ss;
       // this accumulator may be overwritten once all four epilogue warps have read it
@@ -1273,21 +1316,25 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       const int p0 = (t % tiles_p) * 2 * kBM + rank * kBM, q0 = (t / tiles_p) * BN;
       const int p = p0 + quad * 32 + lane;
       const float row_scale = norm_row_factor(prm, p);     // read while the tile's main loop still runs
+      TOut* crow = C + (long long)p * prm.ldc;
+      __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)p * prm.ldc : nullptr;
+      ChunkAhead ahead;
+      fetch_ahead<TOut>(ahead, crow, rbrow, p, q0, prm, vec_ok);      // nobody else writes this row's outputs
       if (!mbar_wait(&tfull_bar[acc], (i >> 1) & 1) || *(volatile int*)&abort_flag) {
         abort_flag = 1;
         atomicOr(prm.status, kStatusWaitExpired);
         break;
       }
       tc_fence_after();
-      TOut* crow = C + (long long)p * prm.ldc;
-      __nv_bfloat16* rbrow = prm.rb_out != nullptr ? prm.rb_out + (long long)p * prm.ldc : nullptr;
       float ss = 0.f;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
+        const ChunkAhead cur = ahead;              // asked for a chunk ago; the next chunk's is asked for now
+        fetch_ahead<TOut>(ahead, crow, rbrow, p, q0 + (ch + 1) * 32, prm, vec_ok && ch + 1 < BN / 32);
         uint32_t r[32];
         SIAR_TMEM_LD_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + ch * 32), r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        ss += store_chunk<TOut>(r, crow, rbrow, p, q0 + ch * 32, prm, vec_ok, row_scale);
+        ss += store_chunk<TOut>(r, crow, rbrow, p, q0 + ch * 32, prm, vec_ok, row_scale, &cur);
       }
       if (prm.ss_out != nullptr && p < prm.P) prm.ss_out[(size_t)p * prm.ss_parts + t / tiles_p] = ss;
       tc_fence_before();
