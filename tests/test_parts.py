@@ -17,8 +17,8 @@ from simple_inference_autoresearch_b200.engine.model import DecoderModel, ModelS
 from simple_inference_autoresearch_b200.architectures.llama import llama_model_spec
 from simple_inference_autoresearch_b200.cache import SequenceCache
 from simple_inference_autoresearch_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS,
-                                                      FeedForward, Mixer, PartSpec, PositionEncoding, StateNeed,
-                                                      TensorSpec)
+                                                      Block, FeedForward, Mixer, Norm, PartSpec, PositionEncoding,
+                                                      StateNeed, TensorSpec)
 from simple_inference_autoresearch_b200.weights import random_tensors
 from tests import emulated_kernels, plain_llama, tiny_configs
 
@@ -400,6 +400,155 @@ def test_toy_routed_feed_forward_and_learned_positions(device):
     finally:
         FEED_FORWARDS.unregister("routed")
         POSITION_ENCODINGS.unregister("learned")
+
+
+# ----------------------------------------------------------------------------- a toy norm and a toy arrangement of a block
+class BiasedLayerNorm(Norm):
+    """y = (x - mean(x)) * rsqrt(var(x) + eps) * w + b, all in 32-bit.  Torch ops; it stands for a norm
+    the product kernels cannot take over (it gives no hint, so nothing is deferred to a product)."""
+
+    def __init__(self, prefix, hidden_size, eps):
+        super().__init__(prefix)
+        self.h, self.eps = hidden_size, eps
+        self.w = self.b = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix + "w", (self.h,), role="vector", init="ones_plus_normal", std=0.1),
+                TensorSpec(self.prefix + "b", (self.h,), role="vector", init="normal", std=0.1)]
+
+    def load(self, tensors):
+        self.w, self.b = tensors[self.prefix + "w"], tensors[self.prefix + "b"]
+
+    def norm(self, ctx, residual):
+        x = residual.float()
+        x = x - x.mean(-1, keepdim=True)
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.w.float() + self.b.float()
+        return y.to(ctx.dtype)
+
+    def add_norm(self, ctx, residual, delta):
+        residual.add_(delta.float())
+        return self.norm(ctx, residual)
+
+
+class ParallelBlock(Block):
+    """x += mixer(norm(x)) + ffn(norm(x)): one norm, both sublayers read the same normed input."""
+
+    def __init__(self, prefix, position, mixer, feed_forward, norm):
+        super().__init__(prefix)
+        at = lambda spec: PartSpec(spec.kind, {**spec.params, "prefix": prefix + spec.params.get("prefix", "")})  # noqa: E731
+        self.norm_part = NORMS.build(at(norm))
+        self.mixer = MIXERS.build(at(mixer), position=position)
+        self.ffn = FEED_FORWARDS.build(at(feed_forward))
+        self._parts = [self.norm_part, self.mixer, self.ffn]
+
+    def tensor_specs(self):
+        return [s for p in self._parts for s in p.tensor_specs()]
+
+    def load(self, tensors):
+        for p in self._parts:
+            p.load(tensors)
+
+    def extension_units(self, dtype=None):
+        units = ()
+        for p in self._parts:
+            units += tuple(p.extension_units(dtype))
+        return units
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, ctx, residual, pending, cache_entry, writes_cache=True):
+        from simple_inference_autoresearch_b200.kernels import ops
+        ctx.residual, ctx.next_norm = residual, None
+        if pending is None or isinstance(pending, ops.Added):       # nothing to add, or already added by its product
+            h = self.norm_part.norm(ctx, residual)
+        else:
+            h = self.norm_part.add_norm(ctx, residual, pending)
+        for out in (self.mixer.forward(ctx, h, cache_entry, writes_cache), self.ffn.forward(ctx, h)):
+            if not isinstance(out, ops.Added):                       # a product that did not add itself
+                residual.add_(out.float())
+        return residual, None
+
+
+def parallel_spec(cfg_like, **_):
+    h, v, d = cfg_like.hidden_size, cfg_like.vocab_size, cfg_like.head_dim
+    ln = lambda p: PartSpec("layernorm_bias", {"prefix": p, "hidden_size": h, "eps": 1e-3})  # noqa: E731
+    attn = PartSpec("gqa_attention", {"prefix": "attn.", "hidden_size": h, "n_heads": 2, "n_kv_heads": 1, "head_dim": d})
+    ffn = PartSpec("swiglu", {"prefix": "ffn.", "hidden_size": h, "intermediate_size": 3 * h // 2})
+    par = lambda i: PartSpec("parallel", {"prefix": f"l{i}.", "mixer": attn, "feed_forward": ffn, "norm": ln("ln.")})  # noqa: E731
+    pre = PartSpec("prenorm", {"prefix": "l1.", "mixer": attn, "feed_forward": ffn,
+                               "mixer_norm": PartSpec("rmsnorm", {"prefix": "n1.", "hidden_size": h, "eps": 1e-5}),
+                               "ffn_norm": ln("n2.")})
+    return ModelSpec(architecture="ParallelForCausalLM", vocab_size=v, hidden_size=h, max_position=256,
+                     embedding_name="emb", head_name=None,
+                     position=PartSpec("rotary", {"head_dim": d, "theta": 10000.0, "scaling": None}),
+                     layers=(par(0), pre, par(2)), final_norm=ln("nf."))
+
+
+def parallel_plain(w, h, d, tokens):
+    """The model of ``parallel_spec`` written out plainly, whole sequence."""
+    w = {k: v.float() for k, v in w.items()}
+
+    def ln(x, p):
+        x = x - x.mean(-1, keepdim=True)
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-3) * w[p + "w"] + w[p + "b"]
+
+    c = {"H": h, "Hq": 2, "Hkv": 1, "D": d}
+    inv = plain_llama.rope_inv_freq(d, 10000.0, None)
+    x = w["emb"][torch.tensor(tokens)]
+    for i in (0, 1, 2):
+        p = f"l{i}."
+        if i == 1:
+            x = x + plain_llama.attention_block(plain_llama.rmsnorm(x, w[p + "n1.weight"], 1e-5), w, p + "attn.", c, inv)
+            x = x + plain_llama.swiglu_mlp(ln(x, p + "n2."), w, p + "ffn.")
+        else:
+            hn = ln(x, p + "ln.")
+            x = x + plain_llama.attention_block(hn, w, p + "attn.", c, inv) + plain_llama.swiglu_mlp(hn, w, p + "ffn.")
+    return ln(x, "nf.") @ w["emb"].T
+
+
+@pytest.mark.parametrize("dtype,hidden,head_dim", [(torch.float32, 40, 16), (torch.bfloat16, 128, 64)])
+def test_toy_norm_and_toy_block_arrangement_register_build_and_step(device, dtype, hidden, head_dim):
+    """A norm the product kernels know nothing of and a block that arranges its parts another way,
+    both defined here, beside the library's own block in the middle layer: the products that add
+    themselves into the residual and leave a norm's inputs behind must fall back where the norm
+    that follows is not theirs."""
+    NORMS.register("layernorm_bias")(BiasedLayerNorm)
+    BLOCKS.register("parallel")(ParallelBlock)
+    registry.register_architecture("ParallelForCausalLM", ("parallel_toy",), config_cls=LlamaConfig, spec_builder=parallel_spec)
+    try:
+        class Cfg:
+            hidden_size, vocab_size = hidden, 70
+        Cfg.head_dim = head_dim
+        arch = registry.resolve({"architectures": ["ParallelForCausalLM"]})
+        model = DecoderModel(arch.spec_builder(Cfg), dtype, device)
+        w = random_tensors(model.tensor_specs(), 11, torch.float32)
+        w = {k: v.to(dtype).float() for k, v in w.items()}           # what the model holds, exactly
+        model.load({k: (v if v.dim() == 1 else v.to(dtype)).to(device) for k, v in w.items()})
+        eng = siar.Engine(model, max_batch=3, max_seq_len=256, use_cuda_graph=False)
+        g = torch.Generator().manual_seed(6)
+        reqs = [torch.randint(0, 70, (n,), generator=g).tolist() for n in (150, 9, 41)]
+        tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=4e-2, atol=4e-2)
+        for rounds in range(2):
+            slots = [eng.open() for _ in reqs]
+            heads = [len(r) - 4 for r in reqs]
+            got = [[] for _ in reqs]
+            out = eng.step([StepEntry(s, r[:h], range(h)) for s, r, h in zip(slots, reqs, heads)])
+            o = 0
+            for i, h in enumerate(heads):
+                got[i].append(out[o:o + h]); o += h
+            for k in range(4):
+                out = eng.step([StepEntry(s, [r[h + k]], [0]) for s, r, h in zip(slots, reqs, heads)])
+                for i in range(len(reqs)):
+                    got[i].append(out[i:i + 1])
+            for i, r in enumerate(reqs):
+                torch.testing.assert_close(torch.cat(got[i]).cpu(), parallel_plain(w, hidden, head_dim, r), **tol)
+            for s in slots:
+                eng.close(s)
+    finally:
+        NORMS.unregister("layernorm_bias")
+        BLOCKS.unregister("parallel")
+        registry.unregister_architecture("ParallelForCausalLM")
 
 
 # ----------------------------------------------------------------------------- rotary layouts that are not Llama's
