@@ -102,6 +102,19 @@ __device__ __forceinline__ float4 ld_f32x4_here(const float* p) {
   asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
   return v;
 }
+// 32 bytes a thread and instruction (sm_100): a whole sector, where a float4 fills half of one
+__device__ __forceinline__ void ld_f32x8_here(const float* p, float4& a, float4& b) {
+  asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_f32x8(float* p, const float4& a, const float4& b) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y), "f"(b.z), "f"(b.w) : "memory");
+}
+__device__ __forceinline__ void st_b32x8(void* p, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
 __device__ __forceinline__ float load_norm_w_here(const void* w, int is_f32, long long i) {
   if (is_f32) return ld_f32_here(reinterpret_cast<const float*>(w) + i);
   unsigned short v;
@@ -901,8 +914,14 @@ __device__ __forceinline__ void fetch_ahead(ChunkAhead& a, const TOut* crow, con
   if constexpr (sizeof(TOut) == 4) {
     if (prm.accumulate && !prm.swiglu && vec_ok && p < prm.P && q + 32 <= prm.Q) {
       a.have = true;
+      const float* src = reinterpret_cast<const float*>(crow) + q;
+      if ((reinterpret_cast<uintptr_t>(src) & 31) == 0) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) a.old[j] = ld_f32x4_here(reinterpret_cast<const float*>(crow) + q + 4 * j);
+        for (int j = 0; j < 8; j += 2) ld_f32x8_here(src + 4 * j, a.old[j], a.old[j + 1]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a.old[j] = ld_f32x4_here(src + 4 * j);
+      }
       if (rbrow != nullptr && !prm.next_w_f32) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -927,6 +946,8 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
     if (p < prm.P && q < prm.Q) {
       TOut* orow = crow + (q >> 1);
       if (vec_ok && q + 32 <= prm.Q && sizeof(TOut) == 2) {
+        const bool wide = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;
+        uint4 keep_pk = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int j = 0; j < 32; j += 16) {
           uint4 pk;
@@ -938,7 +959,9 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
                              swiglu_f(__uint_as_float(r[j + 10]), __uint_as_float(r[j + 11])));
           pk.w = pack_bf16x2(swiglu_f(__uint_as_float(r[j + 12]), __uint_as_float(r[j + 13])),
                              swiglu_f(__uint_as_float(r[j + 14]), __uint_as_float(r[j + 15])));
-          *reinterpret_cast<uint4*>(orow + (j >> 1)) = pk;
+          if (!wide) *reinterpret_cast<uint4*>(orow + (j >> 1)) = pk;
+          else if (j) st_b32x8(orow, keep_pk, pk);
+          keep_pk = pk;
         }
       } else {
 #pragma unroll
@@ -955,16 +978,22 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
           const bool got = ahead != nullptr && ahead->have;
 #pragma unroll
           for (int j = 0; j < 8; ++j) old[j] = got ? ahead->old[j] : *reinterpret_cast<const float4*>(crow + q + 4 * j);
+          const bool wide = (reinterpret_cast<uintptr_t>(crow + q) & 31) == 0;
+          float4 keep = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float4 v = make_float4(old[j].x + __uint_as_float(r[4 * j]), old[j].y + __uint_as_float(r[4 * j + 1]),
                                          old[j].z + __uint_as_float(r[4 * j + 2]), old[j].w + __uint_as_float(r[4 * j + 3]));
-            *reinterpret_cast<float4*>(crow + q + 4 * j) = v;
+            if (!wide) *reinterpret_cast<float4*>(crow + q + 4 * j) = v;
+            else if (j & 1) st_f32x8(reinterpret_cast<float*>(crow) + q + 4 * (j - 1), keep, v);
+            keep = v;
             ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
             r[4 * j] = __float_as_uint(v.x); r[4 * j + 1] = __float_as_uint(v.y);
             r[4 * j + 2] = __float_as_uint(v.z); r[4 * j + 3] = __float_as_uint(v.w);
           }
           if (rbrow != nullptr) {
+            const bool wide_rb = (reinterpret_cast<uintptr_t>(rbrow + q) & 31) == 0;
+            uint4 keep_pk = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float w[8];
@@ -983,17 +1012,30 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
               pk.y = pack_bf16x2(__uint_as_float(r[j + 2]) * w[2], __uint_as_float(r[j + 3]) * w[3]);
               pk.z = pack_bf16x2(__uint_as_float(r[j + 4]) * w[4], __uint_as_float(r[j + 5]) * w[5]);
               pk.w = pack_bf16x2(__uint_as_float(r[j + 6]) * w[6], __uint_as_float(r[j + 7]) * w[7]);
-              *reinterpret_cast<uint4*>(rbrow + q + j) = pk;
+              if (!wide_rb) *reinterpret_cast<uint4*>(rbrow + q + j) = pk;
+              else if (j & 8) st_b32x8(rbrow + q + j - 8, keep_pk, pk);
+              keep_pk = pk;
             }
           }
         } else {
+          const bool wide = (reinterpret_cast<uintptr_t>(crow + q) & 31) == 0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(crow + q + j) =
-                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                            __uint_as_float(r[j + 3]));
+          for (int j = 0; j < 32; j += 8) {
+            const float4 a = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                         __uint_as_float(r[j + 3]));
+            const float4 b = make_float4(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]), __uint_as_float(r[j + 6]),
+                                         __uint_as_float(r[j + 7]));
+            if (wide) {
+              st_f32x8(reinterpret_cast<float*>(crow) + q + j, a, b);
+            } else {
+              *reinterpret_cast<float4*>(crow + q + j) = a;
+              *reinterpret_cast<float4*>(crow + q + j + 4) = b;
+            }
+          }
         }
       } else {
+        const bool wide = (reinterpret_cast<uintptr_t>(crow + q) & 31) == 0;
+        uint4 keep_pk = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
           uint4 pk;
@@ -1001,7 +1043,9 @@ __device__ __forceinline__ float store_chunk(uint32_t (&r)[32], TOut* crow, __nv
           pk.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
           pk.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
           pk.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-          *reinterpret_cast<uint4*>(crow + q + j) = pk;
+          if (!wide) *reinterpret_cast<uint4*>(crow + q + j) = pk;
+          else if (j & 8) st_b32x8(crow + q + j - 8, keep_pk, pk);
+          keep_pk = pk;
         }
       }
     } else {
