@@ -317,8 +317,61 @@ def rotary_layout(rotary, head_dim: int):
     return inv_freq, rotary_dim, interleaved
 
 
+def check_batch(kv, meta, n_rows: int, writes: bool, window: Optional[int] = None) -> None:
+    """The index arithmetic of the attention and cache-write kernels, done on the host for one launch:
+    raises ``ValueError`` naming the first value with which a kernel would leave its tensors.
+    ``kv``: the cache entry (``k``, ``v`` pools [pages, kv heads, page_tokens, head_dim], ``block_table``
+    [slots, pages per sequence]); ``meta``: the batch description; ``n_rows``: rows of the qkv tensor;
+    ``writes``: the launch stores the new tokens' keys and values (they are read in any case);
+    ``window``: keys older than that may have given their pages back (cell -1).  Plain torch on whatever device the tensors live on."""
+    b = int(meta.n_seqs)
+    table = kv.block_table
+    n_slots, max_pages = table.shape
+    n_pages, page = int(kv.k.shape[0]), int(kv.page_tokens)
+    slot = meta.slot_ids[:b].to(torch.int64).cpu()
+    start = meta.q_start[:b + 1].to(torch.int64).cpu()
+    base = meta.base_len[:b].to(torch.int64).cpu()
+    for name, t in (("slot_ids", meta.slot_ids), ("q_start", meta.q_start), ("base_len", meta.base_len),
+                    ("block_table", table)):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous int32 tensor, got {t.dtype}")
+    bad = ((slot < 0) | (slot >= n_slots)).nonzero()
+    if len(bad):
+        i = int(bad[0])
+        raise ValueError(f"slot_ids[{i}] = {int(slot[i])} is no row of the block table ({n_slots} slots)")
+    q_len = start[1:] - start[:-1]
+    if int(start[0]) < 0 or bool((q_len <= 0).any()) or int(start[-1]) > n_rows:
+        raise ValueError(f"q_start {start.tolist()} does not cut the {n_rows} rows into non-empty runs")
+    if int(q_len.max()) > meta.max_q_len:
+        raise ValueError(f"a sequence brings {int(q_len.max())} tokens, the launch is sized for max_q_len = {meta.max_q_len}")
+    end = base + q_len
+    if bool((base < 0).any()) or int(end.max()) > max_pages * page:
+        i = int(((base < 0) | (end > max_pages * page)).nonzero()[0])
+        raise ValueError(f"sequence {i}: keys {int(base[i])} + {int(q_len[i])} do not fit the block table's "
+                         f"{max_pages} pages of {page} tokens")
+    if int(end.max()) > meta.max_kv_len:
+        raise ValueError(f"a sequence holds {int(end.max())} keys, the launch is sized for max_kv_len = {meta.max_kv_len}")
+    rows = table.to(torch.int64).cpu()
+    for i in range(b):
+        used = rows[int(slot[i]), :-(-int(end[i]) // page)]
+        first_seen = 0 if window is None else max(0, int(base[i]) - window + 1) // page
+        if bool((used >= n_pages).any()) or bool((used < -1).any()):
+            j = int(((used >= n_pages) | (used < -1)).nonzero()[0])
+            raise ValueError(f"block_table[{int(slot[i])}, {j}] = {int(used[j])} is no page of the pool ({n_pages} pages)")
+        held = used[first_seen:]              # every page a query of this launch reads, or a new token is stored in
+        if bool((held < 0).any()):
+            j = first_seen + int((held < 0).nonzero()[0])
+            raise ValueError(f"sequence {i} (slot {int(slot[i])}) holds no page for keys {j * page}..{(j + 1) * page - 1} "
+                             f"(block_table[{int(slot[i])}, {j}] = {int(used[j])})")
+
+
+def _check_if_asked(options: KernelOptions, kv, meta, n_rows: int, writes: bool, window: Optional[int] = None) -> None:
+    if options.check_arguments and not (kv.k.is_cuda and torch.cuda.is_current_stream_capturing()):
+        check_batch(kv, meta, n_rows, writes, window)
+
+
 def rope_kv_write(qkv: torch.Tensor, rotary, kv, meta, n_heads: int, n_kv_heads: int,
-                  head_dim: int, write_kv: bool = True) -> None:
+                  head_dim: int, write_kv: bool = True, options: KernelOptions = DEFAULT) -> None:
     """Rotates the q (in place) and k heads of the fused ``qkv`` rows by their
     positions and writes k and v into the pages of ``kv`` (a cache entry).  ``rotary``: see
     ``rotary_layout``; every layout it describes is taken."""
@@ -329,6 +382,7 @@ def rope_kv_write(qkv: torch.Tensor, rotary, kv, meta, n_heads: int, n_kv_heads:
     assert qkv.dtype == kv.k.dtype and n == meta.n_tokens
     assert kv.k.shape[1:] == (n_kv_heads, kv.page_tokens, head_dim) and kv.v.shape == kv.k.shape, \
         "the attention kernels take keys and values of one width"
+    _check_if_asked(options, kv, meta, n, write_kv)
     _launch("elementwise", "siar_rope_kv_write", _is_bf16(qkv.dtype), _ptr(qkv), _ptr(inv_freq), _ptr(kv.k),
             _ptr(kv.v), _ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len), n,
             meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1],
@@ -425,11 +479,12 @@ def rope_and_attention(qkv: torch.Tensor, rotary, kv, meta, n_heads: int, n_kv_h
     plain_layout = inv_freq is None or (rotary_dim == head_dim and not interleaved)
     if window is not None or not plain_layout or not decode_fuses_rope(meta, qkv.dtype, n_heads, n_kv_heads, head_dim,
                                                                        kv.page_tokens, options):
-        rope_kv_write(qkv, rotary, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv)
+        rope_kv_write(qkv, rotary, kv, meta, n_heads, n_kv_heads, head_dim, write_kv=write_kv, options=options)
         return attention(qkv, kv, meta, n_heads, n_kv_heads, head_dim, scale, window=window, options=options)
     _need_cuda(qkv, kv.k, inv_freq)
     check_attention_sizes(n_heads, n_kv_heads, head_dim)
     assert qkv.is_contiguous() and qkv.shape == (meta.n_seqs, (n_heads + 2 * n_kv_heads) * head_dim)
+    _check_if_asked(options, kv, meta, qkv.shape[0], write_kv)
     out = torch.empty((meta.n_seqs, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     sms = _sm_count(qkv.device)
     f = _fn("attention_mma", "siar_attn_mma_decode_scratch_floats")
@@ -455,6 +510,7 @@ def attention(qkv: torch.Tensor, kv, meta, n_heads: int, n_kv_heads: int, head_d
     _need_cuda(qkv, kv.k)
     check_attention_sizes(n_heads, n_kv_heads, head_dim)
     n = qkv.shape[0]
+    _check_if_asked(options, kv, meta, n, False, window)
     out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     common = (_ptr(kv.block_table), _ptr(meta.slot_ids), _ptr(meta.q_start), _ptr(meta.base_len))
     sizes = (meta.n_seqs, n_heads, n_kv_heads, head_dim, kv.page_tokens, kv.block_table.shape[1])

@@ -37,6 +37,11 @@ class KernelOptions:
     #: output columns per tile of products of many rows (the persistent kernel): 0 = the width whose
     #: waves of tiles come out most even, or one of 128, 160, 192, 224, 256
     tile_n: int = 0
+    #: a debugging mode: before every launch that follows the batch description and the block table
+    #: into the cache (rotary + cache write, attention), the host reads them back and checks every
+    #: index the kernels will form (slots, row ranges, lengths, pages) against the tensors' sizes, and
+    #: raises with the first offender.  It synchronises, so it is off while a step is captured.
+    check_arguments: bool = False
 
     def __post_init__(self):
         if self.tile_n not in (0, 128, 160, 192, 224, 256):

@@ -147,3 +147,43 @@ def test_a_window_group_keeps_its_own_pages_and_gives_back_what_no_query_can_see
     assert len(win.pages) == win.pages.n and len(full.pages) == full.pages.n
     with pytest.raises(CacheError, match="positive"):
         make([KVNeed(2, 16, window=0)])
+
+
+# ----------------------------------------------------------------------------- the argument checks of the debugging mode
+def _fake_launch(slot_ids, q_start, base_len, table, n_pages=6, page=4, max_q_len=None, max_kv_len=None):
+    from types import SimpleNamespace
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)  # noqa: E731
+    kv = SimpleNamespace(k=torch.zeros(n_pages, 2, page, 8), v=torch.zeros(n_pages, 2, page, 8),
+                         block_table=i32(table), page_tokens=page)
+    q_lens = [b - a for a, b in zip(q_start, q_start[1:])]
+    meta = SimpleNamespace(n_seqs=len(slot_ids), slot_ids=i32(slot_ids), q_start=i32(q_start), base_len=i32(base_len),
+                           max_q_len=max_q_len or max(q_lens + [1]),
+                           max_kv_len=max_kv_len or max([b + q for b, q in zip(base_len, q_lens)] + [1]))
+    return kv, meta
+
+
+def test_argument_checks_name_the_first_index_that_leaves_its_tensor():
+    from simple_inference_autoresearch_b200.kernels.ops import check_batch
+    table = [[0, 1, -1], [2, 3, 4], [-1, 5, -1]]
+    good = dict(slot_ids=[1, 0], q_start=[0, 3, 4], base_len=[6, 4], table=table)
+    check_batch(*_fake_launch(**good), n_rows=4, writes=True)                    # nothing to say
+    cases = [
+        (dict(good, slot_ids=[3, 0]), "slot_ids[0] = 3"),
+        (dict(good, q_start=[0, 3, 3]), "non-empty runs"),
+        (dict(good, q_start=[0, 3, 5]), "non-empty runs"),                        # more rows than the tensor has
+        (dict(good, base_len=[10, 4]), "do not fit the block table"),
+        (dict(good, base_len=[6, 8]), "holds no page for keys 8..11"),            # slot 0 has two pages
+        (dict(good, table=[[0, 1, -1], [2, 9, 4], [-1, 5, -1]]), "block_table[1, 1] = 9 is no page"),
+        (dict(good, max_kv_len=8), "sized for max_kv_len = 8"),
+        (dict(good, max_q_len=2), "sized for max_q_len = 2"),
+    ]
+    for args, message in cases:
+        with pytest.raises(ValueError, match=message.replace("[", r"\[").replace("]", r"\]")):
+            check_batch(*_fake_launch(**args), n_rows=4, writes=True)
+    # a window of keys: older pages may have been given back, the ones in sight may not
+    windowed = dict(slot_ids=[2], q_start=[0, 1], base_len=[6], table=table)
+    check_batch(*_fake_launch(**windowed), n_rows=1, writes=True, window=3)
+    with pytest.raises(ValueError, match="holds no page for keys 0..3"):
+        check_batch(*_fake_launch(**windowed), n_rows=1, writes=True, window=4)
+    with pytest.raises(ValueError, match="holds no page for keys 0..3"):
+        check_batch(*_fake_launch(**windowed), n_rows=1, writes=True)

@@ -262,6 +262,34 @@ def test_more_sequences_than_the_captured_buffers_hold(folders):
     assert drawn[True] == drawn[False]
 
 
+@pytest.mark.parametrize("name,dtype", [("B", torch.float32), ("D", torch.bfloat16)])
+def test_argument_checks_pass_what_the_engine_launches_and_stop_a_spoilt_block_table(folders, name, dtype):
+    """``KernelOptions(check_arguments=True)``: the host redoes the kernels' index arithmetic before
+    every launch that follows the block table.  What the engine itself launches passes (prompts of
+    unequal lengths, single tokens, slots used again) and draws the same tokens; a block-table cell
+    that points outside the pool, or a slot whose page is missing, raises before anything runs."""
+    vocab = tiny_configs.CONFIGS[name]["vocab_size"]
+    toks = prompts(vocab, [70, 9, 33], seed=12)
+    loaded = siar.load_model(folders[name], device="cuda", dtype=dtype)
+    checked = siar.Engine(loaded.model, max_batch=3, max_seq_len=256, use_cuda_graph=False,
+                          options=siar.KernelOptions(check_arguments=True))
+    plain = siar.Engine(loaded.model, max_batch=3, max_seq_len=256, use_cuda_graph=False)
+    for _ in range(2):
+        assert checked.generate(toks, GREEDY, max_new_tokens=6, ignore_eos=True) == \
+            plain.generate(toks, GREEDY, max_new_tokens=6, ignore_eos=True)
+    s = checked.open()
+    checked.step([StepEntry(s, toks[0])])
+    table = checked.cache.groups[0].block_table
+    keep = table[s, 0].item()
+    table[s, 0] = 10 ** 6
+    with pytest.raises(ValueError, match="is no page of the pool"):
+        checked.step([StepEntry(s, [1], [0])])
+    table[s, 0] = -1
+    with pytest.raises(ValueError, match="holds no page for keys 0..63"):
+        checked.step([StepEntry(s, [1], [0])])
+    table[s, 0] = keep
+
+
 def plain_check_draw(logits_row, params, u, tok, what=""):
     """The token the engine drew from ``logits_row`` must be the plain sampler's choice for the
     same uniform, or (the uniform within rounding of an edge of the cumulative distribution)
