@@ -660,6 +660,18 @@ def test_mma_attention_decode_groups_and_lengths(hq, hkv, d):
     run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 31, 127, 128, 129, 1000], q_lens=[1] * 6)
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(32, 8, 128), (6, 2, 128), (16, 4, 64)])
+@pytest.mark.parametrize("lens", [[0], [0, 0, 0], [5000], [63, 64, 65, 1, 0, 2047, 2048, 300, 129, 4000],
+                                  [700] * 37, [31, 2200] * 9])
+def test_mma_attention_decode_over_many_sequences_of_unequal_lengths(hq, hkv, d, lens):
+    """One new token for each of up to 37 sequences whose histories run from nothing to thousands of
+    keys: one chunk and many chunks per (sequence, kv head), chunks past a short sequence's end, more
+    blocks than the GPU holds at once, and a grid sized by the longest sequence."""
+    run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=lens, q_lens=[1] * len(lens),
+                       cache_size={"max_tokens": sum(lens) + 128 * len(lens) + 1024, "max_slots": len(lens) + 4,
+                                   "max_seq_len": max(max(lens) + 128, 256)})
+
+
 @pytest.mark.parametrize("hq,hkv,d", [(6, 2, 128), (16, 1, 64), (4, 4, 128), (32, 8, 128), (8, 4, 64)])
 def test_mma_attention_prefill_groups_and_lengths(hq, hkv, d):
     run_attention_case(torch.bfloat16, hq, hkv, d, lens_before=[0, 0, 300, 63], q_lens=[1, 200, 150, 66])
