@@ -82,6 +82,10 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+// Marks of the small kernel, one row of 16 per block: 0 block started, 1 first weight tiles asked for,
+// 2 dependency wait returned, 3 first stage landed, 4 accumulator complete, 5 cluster past its first
+// barrier, 7 hand-over complete, 10 owners' adding write-out done, 8 tile staged (no split), 9 write-out
+// done, 6 block about to leave.
 #define SIAR_STAMP(i) \
   if (prm.stamps) prm.stamps[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (i)] = gtime()
 #else
@@ -655,7 +659,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           }
         }
       }
-      if (threadIdx.x == 64) { SIAR_STAMP(3); }
+      if (threadIdx.x == 64) { SIAR_STAMP(10); }
       if constexpr (BN >= 32) {
         const float4* mine4 = reinterpret_cast<const float4*>(tiles);
         // Adding into the residual in the plain orientation: the old values of four groups are asked
