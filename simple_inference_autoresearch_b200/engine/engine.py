@@ -40,13 +40,17 @@ MAX_CAPTURED_STEPS = 64
 class Engine:
     def __init__(self, model: DecoderModel, max_batch: int = 8, max_seq_len: Optional[int] = None,
                  max_tokens: Optional[int] = None, max_slots: Optional[int] = None, page_tokens: int = DEFAULT_PAGE_TOKENS,
-                 use_cuda_graph: bool = True, options: KernelOptions = DEFAULT):
+                 use_cuda_graph: bool = True, options: KernelOptions = DEFAULT,
+                 beyond_trained_positions: bool = False):
+        """``beyond_trained_positions``: let ``max_seq_len`` exceed the configuration's
+        ``max_position_embeddings`` (nothing in the kernels depends on it: rotation angles are computed
+        from the position; it is the length the model was trained for, and the default refuses more)."""
         self.model = model
         self.options = options        # which kernel runs where there is a choice (this engine's steps only)
         self.device = model.device
         self._cuda = self.device.type == "cuda"   # kernels refuse anything else at their first launch
         max_seq_len = int(max_seq_len or model.spec.max_position)
-        if max_seq_len > model.spec.max_position:
+        if max_seq_len > model.spec.max_position and not beyond_trained_positions:
             raise ValueError(f"max_seq_len {max_seq_len} exceeds the model's max_position_embeddings "
                              f"{model.spec.max_position}")
         self.max_batch = int(max_batch)

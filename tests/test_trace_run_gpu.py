@@ -44,8 +44,8 @@ def check(got, ref, dtype):
     assert err <= tol * ref.abs().max().item(), err
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", "AB")
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"),
+                                        ("E", "bfloat16")])
 def test_trace_replay_modes(tmp_path, name, dtype):
     folder = tiny_configs.make_folder(tmp_path, name, seed=31)
     raw, w = tiny_configs.read_folder(folder)
@@ -116,3 +116,21 @@ def test_trace_replay_modes(tmp_path, name, dtype):
             rows.append(t[o:o + cnt])
             files[step][1] = o + cnt
         check(torch.cat(rows), ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_goes_beyond_the_configurations_trained_length(tmp_path, dtype):
+    """A request longer than ``max_position_embeddings`` (128 in configuration A): nothing in the
+    replay depends on that length, and the plain implementation has no such limit either."""
+    folder = tiny_configs.make_folder(tmp_path, "A", seed=5)
+    raw, w = tiny_configs.read_folder(folder)
+    vocab = raw["vocab_size"]
+    assert raw["max_position_embeddings"] == 128
+    (req,) = prompts(vocab, [200], seed=9)
+    ref = plain_llama.forward(w, raw, req)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": req[:170], "want": list(range(170))}], "end": []}]
+    steps += [{"step": 1 + j, "entries": [{"id": "a", "tokens": [t], "want": [0]}], "end": ["a"] if j == 29 else []}
+              for j, t in enumerate(req[170:])]
+    out = tmp_path / "long"
+    replay(folder, dtype, out, 256, steps)
+    check(torch.cat([read_logits(out, s, vocab) for s in range(31)]), ref, dtype)
