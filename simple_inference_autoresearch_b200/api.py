@@ -57,8 +57,7 @@ def load_model(model_dir, device="cuda", dtype=torch.bfloat16) -> LoadedModel:
     arch, config = registry.resolve_path(model_dir)
     loaded = build_model(config, dtype, device)
     m = loaded.model
-    ignorable = ("lm_head.weight",) if m.spec.head_name is None else ()
-    m.load(load_checkpoint(Path(model_dir), m.tensor_specs(), m.dtype, m.device, ignorable))
+    m.load(load_checkpoint(Path(model_dir), m.tensor_specs(), m.dtype, m.device, m.spec.ignorable_tensors))
     return loaded
 
 

@@ -49,4 +49,6 @@ def llama_model_spec(cfg: LlamaConfig, norm_weight_init: str = None) -> ModelSpe
         final_norm=norm("model.norm."),
         stop_token_ids=cfg.stop_token_ids,
         embedding_std=std,
+        # a tied model's checkpoint may still carry the head; every other extra tensor is an error
+        ignorable_tensors=("lm_head.weight",) if cfg.tie_word_embeddings else (),
     )

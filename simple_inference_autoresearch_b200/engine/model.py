@@ -49,6 +49,9 @@ class ModelSpec:
     schedule: Tuple[ScheduleEntry, ...] = ()
     stop_token_ids: Tuple[int, ...] = ()
     embedding_std: float = 0.02
+    #: tensors a checkpoint of this architecture may hold beside the ones the model reads: exact names,
+    #: or ``*suffix`` for every name that ends so (a tied model's stored head, buffers some writers save)
+    ignorable_tensors: Tuple[str, ...] = ()
 
     def resolved_schedule(self) -> Tuple[ScheduleEntry, ...]:
         if self.schedule:

@@ -77,15 +77,17 @@ def _shard_map(model_dir: Path) -> Dict[str, Path]:
 
 def load_checkpoint(model_dir, specs: Sequence[TensorSpec], compute_dtype: torch.dtype, device,
                     ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
-    """Reads exactly the tensors ``specs`` name.  ``ignorable`` names may be
-    present in the files without being an error (a tied model's stored head)."""
+    """Reads exactly the tensors ``specs`` name.  ``ignorable`` names (or, written ``*suffix``, every
+    name that ends so) may be present in the files without being an error (a tied model's stored head)."""
     from safetensors import safe_open
 
     model_dir = Path(model_dir)
     files = _shard_map(model_dir)
     wanted = {s.name: s for s in specs}
     missing = sorted(n for n in wanted if n not in files)
-    unexpected = sorted(n for n in files if n not in wanted and n not in set(ignorable))
+    exact = {n for n in ignorable if not n.startswith("*")}
+    suffixes = tuple(n[1:] for n in ignorable if n.startswith("*"))
+    unexpected = sorted(n for n in files if n not in wanted and n not in exact and not (suffixes and n.endswith(suffixes)))
     wrong_shape, wrong_kind = [], []
     by_file: Dict[Path, List[str]] = {}
     for name in wanted:

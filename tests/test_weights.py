@@ -95,6 +95,25 @@ def test_tied_model_may_carry_a_stored_head(tmp_path):
     siar.load_model(folder, device="cpu", dtype=torch.float32)
 
 
+def test_what_a_checkpoint_may_hold_beside_the_models_tensors_is_the_architectures_to_say(tmp_path):
+    """The model's spec names the tensors a checkpoint may hold beside the ones the model reads, by
+    name or by ``*suffix``; the loader takes the list as it is."""
+    from simple_inference_autoresearch_b200.weights.loader import load_checkpoint
+    folder = tiny_configs.make_folder(tmp_path, "B")
+    model = siar.load_model(folder, device="cpu", dtype=torch.float32).model
+    assert model.spec.ignorable_tensors == ()          # untied: nothing may be left over
+    w = load_file(str(folder / SINGLE_FILE))
+    for i in range(3):
+        w[f"model.layers.{i}.self_attn.rotary_emb.inv_freq"] = torch.ones(16)
+    w["extra.table"] = torch.ones(4)
+    save_file(w, str(folder / SINGLE_FILE))
+    with pytest.raises(WeightError) as e:
+        load_checkpoint(folder, model.tensor_specs(), torch.float32, "cpu", ("extra.table",))
+    assert e.value.unexpected == [f"model.layers.{i}.self_attn.rotary_emb.inv_freq" for i in range(3)]
+    got = load_checkpoint(folder, model.tensor_specs(), torch.float32, "cpu", ("extra.table", "*.rotary_emb.inv_freq"))
+    assert set(got) == {s.name for s in model.tensor_specs()}
+
+
 def test_sharded_checkpoint_with_index(tmp_path):
     folder = tiny_configs.make_folder(tmp_path, "A")
     w = load_file(str(folder / SINGLE_FILE))
