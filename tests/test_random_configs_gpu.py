@@ -85,3 +85,56 @@ def test_random_configuration_against_the_plain_implementation(case, tmp_path):
                 top2 = last.topk(2).values
                 if (top2[0] - top2[1]).item() > 2 * REL_TOL[dtype] * last.abs().max().item():
                     assert o[0] == int(last.argmax()), raw
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_random_batch_schedule_against_the_plain_implementation(case, tmp_path):
+    """17 to 70 requests of unequal lengths start together, go on by one token and end at different
+    times (some with their prompt); a second batch takes their slots and pages.  Eight requests of
+    each batch are compared with the plain implementation, in both dtypes."""
+    rng = random.Random(2000 + case)
+    d = rng.choice([32, 64, 128])
+    hkv = rng.choice([1, 2, 4])
+    raw = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": rng.choice([64, 100, 256]),
+           "intermediate_size": rng.choice([136, 250]), "num_hidden_layers": rng.choice([1, 2]),
+           "vocab_size": rng.choice([257, 500]), "num_attention_heads": hkv * rng.choice([1, 2, 3, 4]),
+           "num_key_value_heads": hkv, "head_dim": d, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+           "max_position_embeddings": 2048, "rope_scaling": None, "tie_word_embeddings": rng.choice([True, False]),
+           "bos_token_id": 0, "eos_token_id": 1, "torch_dtype": "bfloat16"}
+    folder = write_model_folder(tmp_path / "m", LlamaConfig.from_dict(raw), seed=case)
+    raw, w = tiny_configs.read_folder(folder)
+    gen = torch.Generator().manual_seed(case)
+    for dtype in (torch.float32, torch.bfloat16):
+        loaded = siar.load_model(folder, device="cuda", dtype=dtype)
+        nb = rng.choice([17, 40, 70])
+        eng = siar.Engine(loaded.model, max_batch=nb, max_seq_len=1024, max_tokens=nb * 320, use_cuda_graph=False)
+        for batch in range(2):
+            lens = [rng.choice([1, 2, 5, 33, 64, 65, 130, 200]) for _ in range(nb)]
+            tails = [rng.randint(0, min(n - 1, 12)) for n in lens]           # tokens fed one by one
+            toks = [torch.randint(0, raw["vocab_size"], (n,), generator=gen).tolist() for n in lens]
+            slots = [eng.open() for _ in toks]
+            heads = [n - t for n, t in zip(lens, tails)]
+            got = [[] for _ in toks]
+            out = eng.step([StepEntry(s, t[:h], range(h)) for s, t, h in zip(slots, toks, heads)])
+            o = 0
+            for i, h in enumerate(heads):
+                got[i].append(out[o:o + h])
+                o += h
+            for i in range(nb):
+                if tails[i] == 0:
+                    eng.close(slots[i])
+            live = [i for i in range(nb) if tails[i] > 0]
+            k = 0
+            while live:
+                out = eng.step([StepEntry(slots[i], [toks[i][heads[i] + k]], [0]) for i in live])
+                for j, i in enumerate(live):
+                    got[i].append(out[j:j + 1])
+                k += 1
+                for i in live:
+                    if tails[i] == k:
+                        eng.close(slots[i])
+                live = [i for i in live if tails[i] > k]
+            for i in rng.sample(range(nb), 8):
+                ref = plain_llama.forward(w, raw, toks[i])
+                err = (torch.cat(got[i]).float().cpu() - ref).abs().max().item()
+                assert err <= REL_TOL[dtype] * ref.abs().max().item(), (dtype, batch, i, lens[i], tails[i], err, raw)
