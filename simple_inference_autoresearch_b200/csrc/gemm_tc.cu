@@ -1535,9 +1535,16 @@ extern "C" void siar_gemm_tc_set_stamps(unsigned long long* p) { g_stamps = p; g
 // run near the clocks the power cap allows, so the third less traffic from L2 buys little).
 constexpr int kPairRows = 4096;
 
-// Products with fewer output tiles than this many per SM are split along K (two or three blocks'
-// worth of splits per SM made a decode step 4-6% slower).
-constexpr int kSplitTarget = 1;
+// Products with fewer output tiles than SMs are split along K into about this many blocks per two SMs
+// (three: 1.5 blocks an SM).  A block keeps five stages of 18 KB on their way; with one block an SM the
+// 160 blocks of the o and down products hold 14 MB in flight where 7 TB/s times the loaded latency wants
+// about 20.  Measured on the Llama-3.1-8B decode step: o and down cut 7 ways instead of 5 and qkv 5 ways
+// instead of 4 take 0.5-1.2% off a step at batch 1 to 16; 8 ways for o and down or 6 for qkv are 2-3%
+// slower, and so were two or three blocks an SM (4-6%).
+#ifndef SIAR_SPLIT_HALVES
+#define SIAR_SPLIT_HALVES 3
+#endif
+constexpr int kSplitHalves = SIAR_SPLIT_HALVES;
 
 // How a product of these sizes runs: orientation, tile width, split along K and kernel.
 struct GemmPlan {
@@ -1585,8 +1592,8 @@ static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_
   const int tiles = ((g.P + kBM - 1) / kBM) * ((g.Q + g.BN - 1) / g.BN);
   const int num_kb = (K + kBK - 1) / kBK;
   int splits = 1;
-  if (g.swap && tiles < kSplitTarget * sm_count) {
-    splits = (kSplitTarget * sm_count + tiles - 1) / tiles;
+  if (g.swap && tiles < sm_count) {
+    splits = (kSplitHalves * sm_count / 2 + tiles - 1) / tiles;
     if (splits > 8) splits = 8;
     if (splits > max_splits) splits = max_splits;
     if (splits > num_kb / 4) splits = num_kb / 4;
