@@ -1594,6 +1594,12 @@ static bool make_plan(int M, int N, int K, int epilogue, int max_splits, int sm_
   int splits = 1;
   if (g.swap && tiles < sm_count) {
     splits = (kSplitHalves * sm_count / 2 + tiles - 1) / tiles;
+    // ... but slices of fewer than eight k-blocks (little more than the five stages a block asks for before
+    // it has even waited for its input) only as far as it takes to give every SM a block (the 3,072-wide
+    // o product of the 3B shape: 7 ways, not 8, is 1% of a decode step)
+    const int by_length = num_kb / 8, one_each = (sm_count + tiles - 1) / tiles;
+    const int longest_cut = by_length > one_each ? by_length : one_each;
+    if (splits > longest_cut) splits = longest_cut;
     if (splits > 8) splits = 8;
     if (splits > max_splits) splits = max_splits;
     if (splits > num_kb / 4) splits = num_kb / 4;
